@@ -1,0 +1,91 @@
+/*
+ * C ABI of librbf_b200.so: fused RBF attention forward / backward on NVIDIA B200 (sm_100a).
+ *
+ * These entry points are what a foreign-function binding of the reference project's operator
+ * boundary would call in place of its Triton launchers. The reference registers four operators
+ * (file paths are inside the reference project):
+ *
+ *   rbf_attn_v5::scaled_fwd       rbf_attention.py:651-690    -> rbf_b200_fwd(softmax = 1)
+ *   rbf_attn_v5::scaled_bwd       rbf_attention.py:702-810    -> rbf_b200_bwd(softmax = 1)
+ *   rbf_attn_v5::non_softmax_fwd  rbf_attention.py:1355-1391  -> rbf_b200_fwd(softmax = 0)
+ *   rbf_attn_v5::non_softmax_bwd  rbf_attention.py:1399-1480  -> rbf_b200_bwd(softmax = 0)
+ *
+ * Conventions
+ *   - All tensors are (B, H, N, D) with unit stride on D; `*_strides` point at three element strides
+ *     for the dims (b, h, n), exactly what the reference passes to its kernels
+ *     (rbf_attention.py:671-682). D must be 64 or 128. Base addresses must be 16-byte aligned and the
+ *     strides multiples of 8 elements (TMA addressing).
+ *   - dtype: 0 = bfloat16, 1 = float16. Accumulation is fp32. `lse` and the workspace are fp32.
+ *   - The library never allocates device memory: the caller passes a workspace of at least
+ *     rbf_b200_workspace_bytes() bytes, 256-byte aligned, which the call may overwrite entirely.
+ *   - Launches go to `stream` (a cudaStream_t passed as void*; NULL = legacy default stream) on the
+ *     current device. No call synchronises except rbf_b200_read_device_status().
+ *   - Every function returns 0 on success or a positive rbf_b200 status code; nothing throws or aborts.
+ *     rbf_b200_last_error() returns a thread-local message for the last failing call.
+ */
+#ifndef RBF_B200_H_
+#define RBF_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RBF_B200_ABI_VERSION 1
+
+enum {
+  RBF_B200_OK = 0,
+  RBF_B200_ERR_BAD_ARGUMENT = 1,
+  RBF_B200_ERR_BAD_LAYOUT = 2,
+  RBF_B200_ERR_WORKSPACE = 3,
+  RBF_B200_ERR_TENSOR_MAP = 4,
+  RBF_B200_ERR_LAUNCH = 5,
+  RBF_B200_ERR_DEVICE = 6
+};
+
+/* ABI version of the loaded library (RBF_B200_ABI_VERSION at build time). */
+int rbf_b200_abi_version(void);
+
+/* Message describing the last error raised on the calling thread ("" if none). */
+const char* rbf_b200_last_error(void);
+
+/* Bytes of scratch the forward (backward = 0) or backward (backward = 1) call needs.
+ * Replaces the reference launchers' internal torch.empty calls for L-adjacent scratch
+ * (rbf_attention.py:716 `Delta`) and holds the pre-computed key / query norm bias. */
+size_t rbf_b200_workspace_bytes(int B, int H, int N, int D, int softmax, int backward);
+
+/* Forward. Replaces rbf_scaled_fwd (rbf_attention.py:651-690) when softmax = 1 and
+ * rbf_non_softmax_fwd (rbf_attention.py:1355-1391) when softmax = 0.
+ *   out : (B, H, N, D) in `dtype`, strides o_strides.
+ *   lse : (B, H, N) contiguous fp32, base-2 log-sum-exp of the base-2-scaled logits
+ *         (rbf_attention.py:217-219); ignored (may be NULL) when softmax = 0.
+ *   sm_scale : gamma; the reference always uses 1/sqrt(D) (rbf_attention.py:660). */
+int rbf_b200_fwd(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
+                 size_t workspace_bytes, int B, int H, int N, int D, const int64_t* q_strides,
+                 const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides, int dtype,
+                 int causal, int softmax, float sm_scale, void* stream);
+
+/* Backward. Replaces rbf_scaled_bwd (rbf_attention.py:702-810: _bwd_preprocess, dK/dV kernel, dQ kernel)
+ * when softmax = 1 and rbf_non_softmax_bwd (rbf_attention.py:1399-1480) when softmax = 0.
+ *   out, lse : the forward's results; ignored (may be NULL) when softmax = 0.
+ *   dq, dk, dv : (B, H, N, D) in `dtype`. dk includes the gradient through the key-norm term
+ *                (rbf_attention.py:447); for softmax = 0, dq includes the query-norm term (:1336). */
+int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, const float* lse, const void* dout,
+                 void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int B, int H, int N, int D,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const int64_t* o_strides, const int64_t* do_strides, const int64_t* dq_strides,
+                 const int64_t* dk_strides, const int64_t* dv_strides, int dtype, int causal, int softmax,
+                 float sm_scale, void* stream);
+
+/* Synchronises `stream` and reads the device status word that the last call using `workspace` left:
+ * 0 = ok, otherwise (site << 24 | block) of the bounded wait that ran out. Returns RBF_B200_ERR_DEVICE
+ * when the word is non-zero. No counterpart in the reference (its kernels have no device-side waits). */
+int rbf_b200_read_device_status(const void* workspace, void* stream, unsigned int* code);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* RBF_B200_H_ */

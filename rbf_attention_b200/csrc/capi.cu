@@ -1,0 +1,246 @@
+// C ABI of the library (see include/rbf_b200.h): argument validation, workspace carving, TMA tensor
+// maps, and the launch sequence of each call. No device memory is allocated here.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/rbf_b200.h"
+#include "common.cuh"
+#include "launch.h"
+#include "tmap.h"
+
+namespace {
+
+thread_local char g_last_error[512] = "";
+
+int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+constexpr size_t kStatusBytes = 256;
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+struct Workspace {
+  rbf::DeviceStatus* status;
+  float* ksq;
+  float* row_bias;   // query norms (non-softmax)
+  float* delta;      // backward only
+  size_t bytes;
+};
+
+Workspace carve(void* base, int B, int H, int N, int softmax, int backward) {
+  const size_t rows = static_cast<size_t>(B) * H * rbf::padded_rows(N);
+  const size_t vec = align256(rows * sizeof(float));
+  char* p = static_cast<char*>(base);
+  Workspace w{};
+  size_t off = 0;
+  w.status = reinterpret_cast<rbf::DeviceStatus*>(p + off);
+  off += kStatusBytes;
+  w.ksq = reinterpret_cast<float*>(p + off);
+  off += vec;
+  if (!softmax) {
+    w.row_bias = reinterpret_cast<float*>(p + off);
+    off += vec;
+  }
+  if (backward) {
+    w.delta = reinterpret_cast<float*>(p + off);
+    off += vec;
+  }
+  w.bytes = off;
+  return w;
+}
+
+int check_common(int B, int H, int N, int D, int dtype, float sm_scale) {
+  if (B <= 0 || H <= 0 || N <= 0) return fail(RBF_B200_ERR_BAD_ARGUMENT, "B, H, N must be positive (got %d, %d, %d)", B, H, N);
+  if (static_cast<long long>(B) * H > 65535) return fail(RBF_B200_ERR_BAD_ARGUMENT, "B*H = %lld exceeds 65535", static_cast<long long>(B) * H);
+  if (D != 64 && D != 128) return fail(RBF_B200_ERR_BAD_ARGUMENT, "head dim D = %d is not supported (64 or 128)", D);
+  if (dtype != 0 && dtype != 1) return fail(RBF_B200_ERR_BAD_ARGUMENT, "dtype %d is not supported (0 = bf16, 1 = fp16)", dtype);
+  if (!(sm_scale > 0.f) || !isfinite(sm_scale)) return fail(RBF_B200_ERR_BAD_ARGUMENT, "sm_scale must be positive and finite");
+  return 0;
+}
+
+int check_tensor(const char* name, const void* p, const int64_t* s, int B, int H, int N, int D) {
+  if (p == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "%s is NULL", name);
+  if (s == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "%s strides are NULL", name);
+  if (reinterpret_cast<uintptr_t>(p) % 16 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "%s base address is not 16-byte aligned", name);
+  const int ext[3] = {B, H, N};
+  for (int i = 0; i < 3; ++i) {
+    if (ext[i] == 1) continue;  // stride of an extent-1 dim is never used
+    if (s[i] <= 0 || s[i] % 8 != 0)
+      return fail(RBF_B200_ERR_BAD_LAYOUT, "%s stride[%d] = %lld must be a positive multiple of 8 elements", name, i,
+                  static_cast<long long>(s[i]));
+    if (s[i] >= (1ll << 38)) return fail(RBF_B200_ERR_BAD_LAYOUT, "%s stride[%d] is too large for TMA", name, i);
+  }
+  if (N > 1 && s[2] < D) return fail(RBF_B200_ERR_BAD_LAYOUT, "%s row stride %lld is smaller than D", name, static_cast<long long>(s[2]));
+  return 0;
+}
+
+int make_map(CUtensorMap* m, const char* name, const void* p, const int64_t* s, bool bf16, int B, int H, int N, int D) {
+  const int r = rbf::make_tmap_bhnd(m, p, bf16, B, H, N, D, s[0], s[1], s[2], rbf::kTile);
+  if (r != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for %s (code %d)", name, r);
+  return 0;
+}
+
+void set_strides(int64_t (&dst)[3], const int64_t* src) {
+  dst[0] = src[0]; dst[1] = src[1]; dst[2] = src[2];
+}
+
+}  // namespace
+
+extern "C" {
+
+int rbf_b200_abi_version(void) { return RBF_B200_ABI_VERSION; }
+
+const char* rbf_b200_last_error(void) { return g_last_error; }
+
+size_t rbf_b200_workspace_bytes(int B, int H, int N, int D, int softmax, int backward) {
+  (void)D;
+  if (B <= 0 || H <= 0 || N <= 0) return 0;
+  return carve(nullptr, B, H, N, softmax, backward).bytes;
+}
+
+int rbf_b200_fwd(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
+                 size_t workspace_bytes, int B, int H, int N, int D, const int64_t* q_strides,
+                 const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides, int dtype,
+                 int causal, int softmax, float sm_scale, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_common(B, H, N, D, dtype, sm_scale))) return rc;
+  if ((rc = check_tensor("q", q, q_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("k", k, k_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("v", v, v_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("out", out, o_strides, B, H, N, D))) return rc;
+  if (softmax && lse == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "lse is NULL");
+  if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL or not 256-byte aligned");
+  const Workspace ws = carve(workspace, B, H, N, softmax, 0);
+  if (workspace_bytes < ws.bytes)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, ws.bytes);
+
+  const bool bf16 = dtype == 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  rbf::FwdArgs a{};
+  if ((rc = make_map(&a.tm_q, "q", q, q_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_k, "k", k, k_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_v, "v", v, v_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_o, "out", out, o_strides, bf16, B, H, N, D))) return rc;
+
+  const int n_pad = rbf::padded_rows(N);
+  const float c = sm_scale * rbf::kLog2e;
+  rbf::RowReduceArgs r{};
+  r.x = k; r.y = nullptr; r.out = ws.ksq; r.B = B; r.H = H; r.N = N; r.n_pad = n_pad;
+  set_strides(r.xs, k_strides); set_strides(r.ys, k_strides);
+  r.scale = c; r.pad_value = INFINITY; r.status_to_clear = ws.status;
+  cudaError_t e = rbf::launch_row_reduce(r, bf16, D, stream);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "key-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+  if (!softmax) {
+    r.x = q; r.out = ws.row_bias; set_strides(r.xs, q_strides); r.pad_value = 0.f; r.status_to_clear = nullptr;
+    e = rbf::launch_row_reduce(r, bf16, D, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "query-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+  }
+
+  a.ksq = ws.ksq; a.qsq = ws.row_bias; a.lse = lse; a.status = ws.status;
+  a.B = B; a.H = H; a.N = N; a.n_pad = n_pad; a.causal = causal ? 1 : 0; a.scale2 = 2.f * c;
+  e = rbf::launch_fwd(a, bf16, D, softmax != 0, stream);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "forward launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, const float* lse, const void* dout,
+                 void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int B, int H, int N, int D,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const int64_t* o_strides, const int64_t* do_strides, const int64_t* dq_strides,
+                 const int64_t* dk_strides, const int64_t* dv_strides, int dtype, int causal, int softmax,
+                 float sm_scale, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_common(B, H, N, D, dtype, sm_scale))) return rc;
+  if ((rc = check_tensor("q", q, q_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("k", k, k_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("v", v, v_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("dout", dout, do_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("dq", dq, dq_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("dk", dk, dk_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("dv", dv, dv_strides, B, H, N, D))) return rc;
+  if (softmax) {
+    if ((rc = check_tensor("out", out, o_strides, B, H, N, D))) return rc;
+    if (lse == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "lse is NULL");
+  }
+  if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL or not 256-byte aligned");
+  const Workspace ws = carve(workspace, B, H, N, softmax, 1);
+  if (workspace_bytes < ws.bytes)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, ws.bytes);
+
+  const bool bf16 = dtype == 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  rbf::BwdArgs a{};
+  if ((rc = make_map(&a.tm_q, "q", q, q_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_k, "k", k, k_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_v, "v", v, v_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_do, "dout", dout, do_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_dq, "dq", dq, dq_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_dk, "dk", dk, dk_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_dv, "dv", dv, dv_strides, bf16, B, H, N, D))) return rc;
+
+  const int n_pad = rbf::padded_rows(N);
+  const float c = sm_scale * rbf::kLog2e;
+  rbf::RowReduceArgs r{};
+  r.B = B; r.H = H; r.N = N; r.n_pad = n_pad;
+  // key norms
+  r.x = k; r.y = nullptr; r.out = ws.ksq; set_strides(r.xs, k_strides); set_strides(r.ys, k_strides);
+  r.scale = c; r.pad_value = INFINITY; r.status_to_clear = ws.status;
+  cudaError_t e = rbf::launch_row_reduce(r, bf16, D, stream);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "key-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+  r.status_to_clear = nullptr;
+  if (softmax) {
+    // delta = rowsum(O * dO)
+    r.x = out; r.y = dout; r.out = ws.delta; set_strides(r.xs, o_strides); set_strides(r.ys, do_strides);
+    r.pad_value = 0.f;
+    e = rbf::launch_row_reduce(r, bf16, D, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "delta pre-pass launch failed: %s", cudaGetErrorString(e));
+  } else {
+    // query norms play the role of the row statistic; delta is identically zero
+    r.x = q; r.y = nullptr; r.out = ws.row_bias; set_strides(r.xs, q_strides); r.pad_value = INFINITY;
+    e = rbf::launch_row_reduce(r, bf16, D, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "query-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+    e = cudaMemsetAsync(ws.delta, 0, static_cast<size_t>(B) * H * n_pad * sizeof(float), stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "delta clear failed: %s", cudaGetErrorString(e));
+  }
+
+  a.ksq = ws.ksq;
+  a.row_bias = softmax ? lse : ws.row_bias;
+  a.row_bias_pitch = softmax ? N : n_pad;
+  a.delta = ws.delta;
+  a.status = ws.status;
+  a.B = B; a.H = H; a.N = N; a.n_pad = n_pad; a.causal = causal ? 1 : 0;
+  a.scale2 = 2.f * c; a.grad_scale = 2.f * sm_scale;
+  e = rbf::launch_bwd_dkdv(a, bf16, D, softmax != 0, stream);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
+  e = rbf::launch_bwd_dq(a, bf16, D, softmax != 0, stream);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned int* code) {
+  g_last_error[0] = 0;
+  if (workspace == nullptr || code == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "workspace or code is NULL");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  rbf::DeviceStatus st{};
+  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(st), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "status read failed: %s", cudaGetErrorString(e));
+  *code = st.code;
+  if (st.code != 0)
+    return fail(RBF_B200_ERR_DEVICE, "device-side wait ran out: site %u, block (%u, %u)", st.code >> 24,
+                st.code & 0xfffu, (st.code >> 12) & 0xfffu);
+  return RBF_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,53 @@
+// Host-side launch interfaces between the C ABI (capi.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace rbf {
+
+struct RowReduceArgs {
+  const void* x;
+  const void* y;          // nullptr: scaled squared norm of x rows; else dot(x, y) per row
+  float* out;             // (B*H, n_pad)
+  int B, H, N, n_pad;
+  int64_t xs[3], ys[3];   // element strides of dims b, h, n
+  float scale;
+  float pad_value;
+  DeviceStatus* status_to_clear;  // optional: zeroed by the first thread of the grid
+};
+cudaError_t launch_row_reduce(const RowReduceArgs& a, bool bf16, int D, cudaStream_t stream);
+
+// Forward pass. Tensor maps use a 64-element x 128-row box with the 128-byte swizzle.
+struct FwdArgs {
+  CUtensorMap tm_q, tm_k, tm_v, tm_o;
+  const float* ksq;       // (B*H, n_pad): gamma*log2(e)*|k|^2, +inf on padding rows
+  const float* qsq;       // (B*H, n_pad): same for q; non-softmax variant only
+  float* lse;             // (B, H, N) base-2 log-sum-exp; softmax variant only
+  DeviceStatus* status;
+  int B, H, N, n_pad;
+  int causal;
+  float scale2;           // 2 * gamma * log2(e)
+};
+cudaError_t launch_fwd(const FwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream);
+
+// Backward pass (two kernels: key-stationary dK/dV, query-stationary dQ).
+struct BwdArgs {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dq, tm_dk, tm_dv;
+  const float* ksq;       // (B*H, n_pad)
+  const float* row_bias;  // (B*H, n_pad): softmax: L (base-2 LSE, +inf on padding); non-softmax: c*|q|^2
+  int row_bias_pitch;     // row pitch of row_bias: N for L, n_pad for the query norms
+  const float* delta;     // (B*H, n_pad): rowsum(O*dO); all zero for the non-softmax variant
+  DeviceStatus* status;
+  int B, H, N, n_pad;
+  int causal;
+  float scale2;           // 2 * gamma * log2(e)
+  float grad_scale;       // 2 * gamma
+};
+cudaError_t launch_bwd_dkdv(const BwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream);
+cudaError_t launch_bwd_dq(const BwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream);
+
+}  // namespace rbf

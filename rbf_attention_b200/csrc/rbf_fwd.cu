@@ -1,0 +1,399 @@
+// Fused RBF attention forward for sm_100a.
+//
+//   softmax variant      O = softmax_j(2g q_i.k_j - g|k_j|^2) V,  L_i = log2 sum_j 2^(log2e * logit_ij)
+//   non-softmax variant  O = exp(-g|q_i - k_j|^2) V
+//
+// One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row tiles and walks the
+// key tiles (128 keys) once for both. Roles:
+//   warps 0-3 / 4-7  softmax group for query tile 0 / 1 (one thread per query row)
+//   warp 8           TMA producer: Q tiles once, then a ring of K and V tiles
+//   warp 9           tcgen05.mma issuer: S_t = Q_t K_j^T (smem x smem) and O_t += P_t V_j (TMEM x smem)
+// TMEM columns: [0,128) S_0, [128,256) S_1, then O_0 and O_1 (D columns each). P_t (16-bit) is written
+// back over the first 64 columns of S_t and consumed from there as the A operand of the second MMA.
+// The key-norm bias is applied in registers on the fp32 accumulator: s = acc * (2 g log2e) - ksq_j.
+// The running maximum is only raised (and O rescaled in TMEM) when it grew by more than 2^8, so the
+// rescale is rare; L and the final 1/l normalisation use the maximum actually applied.
+#include "common.cuh"
+#include "launch.h"
+
+namespace rbf {
+
+namespace fwd {
+
+static constexpr int kThreads = 320;
+static constexpr int kLoadWarp = 8;
+static constexpr int kMmaWarp = 9;
+static constexpr float kRescaleThreshold = 8.0f;
+
+template <int D>
+struct Smem {
+  static constexpr int kTileBytes = kTile * D * 2;          // one 128-row operand tile
+  static constexpr int kStages = (D == 64) ? 3 : 2;
+  static constexpr int kQ = 0;                              // 2 tiles
+  static constexpr int kK = kQ + 2 * kTileBytes;            // kStages tiles
+  static constexpr int kV = kK + kStages * kTileBytes;      // kStages tiles
+  static constexpr int kKsq = kV + kStages * kTileBytes;    // [2 groups][2 buffers][128] floats
+  static constexpr int kBars = kKsq + 2 * 2 * kTile * 4;
+  static constexpr int kNumBars = 2 + 4 * kStages + 8;
+  static constexpr int kMisc = kBars + kNumBars * 8;        // tmem base, abort flag
+  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kDynamic = kTotal + 1024;            // slack for 1024-byte alignment
+};
+
+enum Site : uint32_t {
+  kSiteQFull = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSFull, kSitePFull, kSiteODone,
+  kSiteODoneFinal, kSiteKsqSync
+};
+
+template <int D, bool kSoftmax, bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+               const float* __restrict__ ksq, const float* __restrict__ qsq, float* __restrict__ lse,
+               DeviceStatus* status, int H, int N, int n_pad, int causal, float scale2) {
+  using L = Smem<D>;
+  constexpr int kStages = L::kStages;
+  constexpr int kBoxes = D / 64;                 // 64-column TMA boxes per tile row
+  constexpr int kBoxBytes = kTile * 128;         // one box: 128 rows x 128 bytes
+  constexpr uint32_t kTileBytes = L::kTileBytes;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_q = smem + L::kQ;
+  uint8_t* s_k = smem + L::kK;
+  uint8_t* s_v = smem + L::kV;
+  float* s_ksq = reinterpret_cast<float*>(smem + L::kKsq);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint64_t* q_full = bars;                       // [2]
+  uint64_t* k_full = bars + 2;                   // [kStages]
+  uint64_t* k_empty = k_full + kStages;
+  uint64_t* v_full = k_empty + kStages;
+  uint64_t* v_empty = v_full + kStages;
+  uint64_t* s_full = v_empty + kStages;          // [2]
+  uint64_t* p_full = s_full + 2;                 // [2]
+  uint64_t* o_done = p_full + 2;                 // [2]
+  uint64_t* grp_sync = o_done + 2;               // [2] rendezvous of the 128 threads of a softmax group
+  uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / H, h = bh % H;
+  const int num_blocks = gridDim.x;
+  // heaviest causal blocks first
+  const int mb = causal ? (num_blocks - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
+  const int m0 = mb * 2 * kTile;
+  const int n_key_tiles_all = (N + kTile - 1) / kTile;
+  int nkt[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = m0 + t * kTile;
+    nkt[t] = (r0 >= N) ? 0 : (causal ? min(n_key_tiles_all, r0 / kTile + 1) : n_key_tiles_all);
+  }
+  const int nkt_max = max(nkt[0], nkt[1]);
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(&q_full[0], 1);
+    mbar_init(&q_full[1], 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], kTile);
+      mbar_init(&o_done[t], 1);
+      mbar_init(&grp_sync[t], kTile);
+    }
+    fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_base_s;
+  const uint32_t tmem_s[2] = {tmem, tmem + 128};
+  const uint32_t tmem_o[2] = {tmem + 256, tmem + 256 + D};
+
+  if (warp == kLoadWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      for (int t = 0; t < 2; ++t) {
+        if (nkt[t] == 0) continue;
+        mbar_arrive_expect_tx(&q_full[t], kTileBytes);
+        for (int x = 0; x < kBoxes; ++x)
+          tma_load_4d(s_q + t * kTileBytes + x * kBoxBytes, &tm_q, &q_full[t], x * 64, m0 + t * kTile, h, b);
+      }
+      for (int j = 0; j < nkt_max; ++j) {
+        const int st = j % kStages;
+        const uint32_t par = ((j / kStages) - 1) & 1;
+        if (j >= kStages && !mbar_wait(&k_empty[st], par, abort_flag, status, kSiteKEmpty)) break;
+        mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+        for (int x = 0; x < kBoxes; ++x)
+          tma_load_4d(s_k + st * kTileBytes + x * kBoxBytes, &tm_k, &k_full[st], x * 64, j * kTile, h, b);
+        if (j >= kStages && !mbar_wait(&v_empty[st], par, abort_flag, status, kSiteVEmpty)) break;
+        mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+        for (int x = 0; x < kBoxes; ++x)
+          tma_load_4d(s_v + st * kTileBytes + x * kBoxBytes, &tm_v, &v_full[st], x * 64, j * kTile, h, b);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(kTile, kTile, kBf16, false, false);   // S = Q K^T
+      constexpr uint32_t idesc_o = make_idesc(kTile, D, kBf16, false, true);        // O += P V (V is N-major)
+      const uint32_t q_addr = smem_u32(s_q), k_addr = smem_u32(s_k), v_addr = smem_u32(s_v);
+      auto issue_s = [&](int t, int st) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
+          umma_ss(tmem_s[t], make_sdesc_sw128(q_addr + t * kTileBytes + off, 16, 1024),
+                  make_sdesc_sw128(k_addr + st * kTileBytes + off, 16, 1024), idesc_s, kk > 0);
+        }
+        umma_commit(&s_full[t]);
+      };
+      auto issue_o = [&](int t, int st, bool accumulate) {
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          umma_ts(tmem_o[t], tmem_s[t] + kk * 8, make_sdesc_sw128(v_addr + st * kTileBytes + kk * 2048, kBoxBytes, 1024),
+                  idesc_o, (accumulate || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&o_done[t]);
+      };
+      bool ok = true;
+      for (int t = 0; t < 2 && ok; ++t)
+        if (nkt[t] > 0) ok = mbar_wait(&q_full[t], 0, abort_flag, status, kSiteQFull);
+      if (ok && nkt_max > 0) ok = mbar_wait(&k_full[0], 0, abort_flag, status, kSiteKFull);
+      if (ok) {
+        tc_fence_after_sync();
+        for (int t = 0; t < 2; ++t)
+          if (nkt[t] > 0) issue_s(t, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < nkt_max && ok; ++j) {
+        const int st = j % kStages;
+        const int st_next = (j + 1) % kStages;
+        ok = mbar_wait(&v_full[st], (j / kStages) & 1, abort_flag, status, kSiteVFull);
+        if (!ok) break;
+        bool next_k_ready = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= nkt[t]) continue;
+          ok = mbar_wait(&p_full[t], j & 1, abort_flag, status, kSitePFull);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_o(t, st, j > 0);
+          if (j + 1 < nkt[t]) {
+            if (!next_k_ready) {
+              ok = mbar_wait(&k_full[st_next], ((j + 1) / kStages) & 1, abort_flag, status, kSiteKFull);
+              if (!ok) break;
+              tc_fence_after_sync();
+              next_k_ready = true;
+            }
+            issue_s(t, st_next);
+          }
+        }
+        if (!ok) break;
+        umma_commit(&v_empty[st]);
+        if (j + 1 < nkt_max) umma_commit(&k_empty[st_next]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int t = warp >> 2;                         // query tile of this group
+    const int r = tid & (kTile - 1);                 // row within the tile == TMEM lane
+    const int r0 = m0 + t * kTile;
+    const int row = r0 + r;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int my_nkt = nkt[t];
+    float* ksq_buf = s_ksq + t * 2 * kTile;
+    const float* ksq_row = ksq + static_cast<int64_t>(bh) * n_pad;
+    float m_used = -INFINITY;
+    float l_sum = 0.f;
+    float row_bias = 0.f;
+    if (!kSoftmax && my_nkt > 0) row_bias = qsq[static_cast<int64_t>(bh) * n_pad + row];
+    bool ok = true;
+    uint32_t grp_phase = 0;
+    // Bounded rendezvous of the group's 128 threads (a named barrier could not be abandoned on abort).
+    auto group_sync = [&]() -> bool {
+      mbar_arrive(&grp_sync[t]);
+      const bool done = mbar_wait(&grp_sync[t], grp_phase & 1, abort_flag, status, kSiteKsqSync);
+      ++grp_phase;
+      return done;
+    };
+    if (my_nkt > 0) ksq_buf[r] = ksq_row[r];
+
+    for (int j = 0; j < my_nkt; ++j) {
+      float ksq_next = 0.f;
+      if (j + 1 < my_nkt) ksq_next = ksq_row[(j + 1) * kTile + r];
+      // all 128 threads of the group: publishes buffer j&1, retires buffer (j+1)&1
+      ok = group_sync() && mbar_wait(&s_full[t], j & 1, abort_flag, status, kSiteSFull);
+      if (!ok) break;
+      tc_fence_after_sync();
+
+      float s[kTile];
+      const float4* kb = reinterpret_cast<const float4*>(ksq_buf + (j & 1) * kTile);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[32];
+        tmem_ld_x32(tmem_s[t] + lane_sel + c * 32, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 kq = kb[c * 8 + i];
+          s[c * 32 + i * 4 + 0] = fmaf(__uint_as_float(raw[i * 4 + 0]), scale2, -kq.x);
+          s[c * 32 + i * 4 + 1] = fmaf(__uint_as_float(raw[i * 4 + 1]), scale2, -kq.y);
+          s[c * 32 + i * 4 + 2] = fmaf(__uint_as_float(raw[i * 4 + 2]), scale2, -kq.z);
+          s[c * 32 + i * 4 + 3] = fmaf(__uint_as_float(raw[i * 4 + 3]), scale2, -kq.w);
+        }
+      }
+      if (causal && j * kTile == r0) {
+        // diagonal tile: key (r0 + c) is visible to query (r0 + r) iff c <= r
+#pragma unroll
+        for (int c = 0; c < kTile; ++c)
+          if (c > r) s[c] = -INFINITY;
+      }
+
+      float sub;
+      if constexpr (kSoftmax) {
+        float mx = s[0];
+#pragma unroll
+        for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, s[c]);
+        const float m_new = fmaxf(m_used, mx);
+        const bool need = (m_new - m_used) > kRescaleThreshold;
+        float alpha = 1.f;
+        if (need) {
+          alpha = ex2_approx(m_used - m_new);
+          m_used = m_new;
+          l_sum *= alpha;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, need)) {
+          // O_t holds the sum over key tiles < j; wait until the last P V has landed, then rescale.
+          ok = mbar_wait(&o_done[t], (j - 1) & 1, abort_flag, status, kSiteODone);
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_x32(tmem_o[t] + lane_sel + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_x32(tmem_o[t] + lane_sel + c * 32, o);
+          }
+        }
+        sub = m_used;
+      } else {
+        sub = row_bias;
+      }
+
+      float psum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t packed[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = ex2_approx(s[c * 64 + 2 * i] - sub);
+          const float p1 = ex2_approx(s[c * 64 + 2 * i + 1] - sub);
+          psum += p0 + p1;
+          packed[i] = pack2<kBf16>(p0, p1);
+        }
+        tmem_st_x32(tmem_s[t] + lane_sel + c * 32, packed);
+      }
+      l_sum += psum;
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&p_full[t]);
+      if (j + 1 < my_nkt) ksq_buf[((j + 1) & 1) * kTile + r] = ksq_next;
+    }
+
+    if (ok && my_nkt > 0) {
+      ok = mbar_wait(&o_done[t], (my_nkt - 1) & 1, abort_flag, status, kSiteODoneFinal);
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv = kSoftmax ? (1.0f / l_sum) : 1.0f;
+        uint8_t* stage = s_q + t * kTileBytes;       // Q_t is dead once the last S_t MMA has completed
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_x32(tmem_o[t] + lane_sel + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              w[i] = pack2<kBf16>(__uint_as_float(o[g * 8 + 2 * i]) * inv, __uint_as_float(o[g * 8 + 2 * i + 1]) * inv);
+            const int col16 = c * 4 + g;             // 16-byte chunk index along D
+            *reinterpret_cast<uint4*>(stage + (col16 >> 3) * kBoxBytes + sw128_offset(r, col16 & 7)) =
+                make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        ok = group_sync();
+        if (ok && r == 0) {
+          for (int x = 0; x < kBoxes; ++x) tma_store_4d(&tm_o, stage + x * kBoxBytes, x * 64, r0, h, b);
+          tma_store_commit();
+          tma_store_wait_all();
+        }
+        if (kSoftmax && row < N) lse[static_cast<int64_t>(bh) * N + row] = m_used + log2f(l_sum);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // give copies and MMAs still in flight time to land before shared memory and TMEM are released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace fwd
+
+template <int D, bool kSoftmax, bool kBf16>
+static cudaError_t launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
+  auto kernel = fwd::rbf_fwd_kernel<D, kSoftmax, kBf16>;
+  constexpr int smem = fwd::Smem<D>::kDynamic;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid((a.N + 2 * kTile - 1) / (2 * kTile), a.B * a.H);
+  kernel<<<grid, fwd::kThreads, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.tm_o, a.ksq, a.qsq, a.lse, a.status, a.H,
+                                                a.N, a.n_pad, a.causal, a.scale2);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fwd(const FwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream) {
+#define RBF_FWD_CASE(DD, SM, BF) \
+  if (D == DD && softmax == SM && bf16 == BF) return launch_fwd_t<DD, SM, BF>(a, stream);
+  RBF_FWD_CASE(64, true, true)
+  RBF_FWD_CASE(64, false, true)
+  RBF_FWD_CASE(128, true, true)
+  RBF_FWD_CASE(128, false, true)
+  RBF_FWD_CASE(64, true, false)
+  RBF_FWD_CASE(64, false, false)
+  RBF_FWD_CASE(128, true, false)
+  RBF_FWD_CASE(128, false, false)
+#undef RBF_FWD_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace rbf

@@ -1,0 +1,255 @@
+"""Operator boundary: the four ``rbf_attn_v5`` custom operators of the reference, with the same
+schemas, fake kernels and autograd formulas, implemented by calls into ``librbf_b200.so``.
+
+Reference counterparts (paths inside the reference project):
+  rbf_attn_v5::scaled_fwd / scaled_bwd            rbf_attention.py:651-842
+  rbf_attn_v5::non_softmax_fwd / non_softmax_bwd  rbf_attention.py:1355-1511
+  run_triton_rbf / run_triton_non_softmax_rbf     rbf_attention.py:848-853
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+
+_DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1}
+
+
+def _validate(name: str, t: torch.Tensor, like: torch.Tensor | None = None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a tensor")
+    if t.dim() != 4:
+        raise ValueError(f"{name} must have shape (B, H, N, D), got {tuple(t.shape)}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: rbf_attention_b200 has no CPU path")
+    if like is not None:
+        if t.shape != like.shape:
+            raise ValueError(f"{name} shape {tuple(t.shape)} differs from q shape {tuple(like.shape)}")
+        if t.dtype != like.dtype:
+            raise ValueError(f"{name} dtype {t.dtype} differs from q dtype {like.dtype}")
+        if t.device != like.device:
+            raise ValueError(f"{name} is on {t.device}, q is on {like.device}")
+
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """Returns ``t`` if the TMA engine can address it in place (unit stride on D, 16-byte aligned base,
+    strides of dims b, h, n multiples of 8 elements), else a contiguous copy. The reference assumes
+    ``stride(-1) == 1`` without checking (rbf_attention.py:111-138)."""
+    B, H, N, D = t.shape
+    ok = t.stride(3) == 1 and t.data_ptr() % 16 == 0
+    for ext, s in zip((B, H, N), t.stride()[:3]):
+        if ext > 1 and (s <= 0 or s % 8 != 0):
+            ok = False
+    if N > 1 and t.stride(2) < D:
+        ok = False
+    return t if ok else t.contiguous()
+
+
+def _compute_dtype(q: torch.Tensor) -> torch.dtype:
+    if q.dtype in _DTYPE_CODE:
+        return q.dtype
+    if q.dtype == torch.float32:
+        # fp32 inputs run with 16-bit tensor-core operands and fp32 accumulation; the reference's
+        # Triton path uses TF32 for them (rbf_attention.py:183). bf16 keeps fp32's exponent range.
+        return torch.bfloat16
+    raise ValueError(f"unsupported dtype {q.dtype} (bfloat16, float16 or float32)")
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _workspace(B, H, N, D, softmax, backward, device) -> torch.Tensor:
+    lib = _lib.load()
+    nbytes = lib.rbf_b200_workspace_bytes(B, H, N, D, int(softmax), int(backward))
+    # torch's caching allocator returns 512-byte aligned blocks, which satisfies the 256-byte rule
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+
+def _forward(q, k, v, is_causal: bool, softmax: bool):
+    _validate("q", q)
+    _validate("k", k, q)
+    _validate("v", v, q)
+    B, H, N, D = q.shape
+    if D not in (64, 128):
+        raise ValueError(f"head dim {D} is not supported (64 or 128)")
+    lib = _lib.load()
+    cdt = _compute_dtype(q)
+    qc, kc, vc = (_tma_ready(t.to(cdt)) for t in (q, k, v))
+    out = torch.empty((B, H, N, D), dtype=cdt, device=q.device)
+    lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device) if softmax else None
+    ws = _workspace(B, H, N, D, softmax, False, q.device)
+    with torch.cuda.device(q.device):
+        rc = lib.rbf_b200_fwd(
+            qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+            lse.data_ptr() if softmax else None, ws.data_ptr(), ws.numel(),
+            B, H, N, D, _lib.strides3(qc), _lib.strides3(kc), _lib.strides3(vc), _lib.strides3(out),
+            _DTYPE_CODE[cdt], int(bool(is_causal)), int(softmax), 1.0 / math.sqrt(D), _stream_ptr(q.device),
+        )
+    _lib.check(rc, "rbf_b200_fwd")
+    if cdt != q.dtype:
+        out = out.to(q.dtype)
+    return out, lse
+
+
+def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax: bool):
+    _validate("q", q)
+    _validate("k", k, q)
+    _validate("v", v, q)
+    _validate("dout", dout, q)
+    B, H, N, D = q.shape
+    lib = _lib.load()
+    cdt = _compute_dtype(q)
+    qc, kc, vc, doc = (_tma_ready(t.to(cdt)) for t in (q, k, v, dout))
+    oc = _tma_ready(out.to(cdt)) if softmax else None
+    dq = torch.empty((B, H, N, D), dtype=cdt, device=q.device)
+    dk = torch.empty_like(dq)
+    dv = torch.empty_like(dq)
+    ws = _workspace(B, H, N, D, softmax, True, q.device)
+    z3 = (ctypes.c_int64 * 3)(0, 0, 0)
+    with torch.cuda.device(q.device):
+        rc = lib.rbf_b200_bwd(
+            qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+            oc.data_ptr() if softmax else None, lse.data_ptr() if softmax else None, doc.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel(),
+            B, H, N, D, _lib.strides3(qc), _lib.strides3(kc), _lib.strides3(vc),
+            _lib.strides3(oc) if softmax else z3, _lib.strides3(doc),
+            _lib.strides3(dq), _lib.strides3(dk), _lib.strides3(dv),
+            _DTYPE_CODE[cdt], int(bool(is_causal)), int(softmax), float(sm_scale), _stream_ptr(q.device),
+        )
+    _lib.check(rc, "rbf_b200_bwd")
+    if cdt != q.dtype:
+        dq, dk, dv = dq.to(q.dtype), dk.to(q.dtype), dv.to(q.dtype)
+    return dq, dk, dv
+
+
+# ---------------------------------------------------------------------------------------------
+# rbf_attn_v5::scaled_fwd / scaled_bwd  (rbf_attention.py:651-842)
+# ---------------------------------------------------------------------------------------------
+@torch.library.custom_op("rbf_attn_v5::scaled_fwd", mutates_args=())
+def rbf_scaled_fwd(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool
+) -> tuple[torch.Tensor, torch.Tensor]:
+    out, lse = _forward(q, k, v, is_causal, softmax=True)
+    return out, lse
+
+
+@rbf_scaled_fwd.register_fake
+def _(q, k, v, is_causal):
+    B, H, N_CTX, D_HEAD = q.shape
+    return (
+        torch.empty_like(q, memory_format=torch.contiguous_format),
+        torch.empty((B, H, N_CTX), device=q.device, dtype=torch.float32),
+    )
+
+
+@torch.library.custom_op("rbf_attn_v5::scaled_bwd", mutates_args=())
+def rbf_scaled_bwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    L: torch.Tensor,
+    dout: torch.Tensor,
+    is_causal: bool,
+    sm_scale: float,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _backward(q, k, v, out, L, dout, is_causal, sm_scale, softmax=True)
+
+
+@rbf_scaled_bwd.register_fake
+def _(q, k, v, out, L, dout, is_causal, sm_scale):
+    return (
+        torch.empty_like(q, memory_format=torch.contiguous_format),
+        torch.empty_like(k, memory_format=torch.contiguous_format),
+        torch.empty_like(v, memory_format=torch.contiguous_format),
+    )
+
+
+def _scaled_setup_context(ctx, inputs, output):
+    q, k, v, is_causal = inputs
+    out, L = output
+    ctx.save_for_backward(q, k, v, out, L)
+    ctx.is_causal = is_causal
+    ctx.sm_scale = 1.0 / math.sqrt(q.shape[-1])
+
+
+def _scaled_backward(ctx, dout, dL):
+    # the gradient of L is ignored, as in the reference (rbf_attention.py:830)
+    q, k, v, out, L = ctx.saved_tensors
+    dq, dk, dv = torch.ops.rbf_attn_v5.scaled_bwd(q, k, v, out, L, dout, ctx.is_causal, ctx.sm_scale)
+    return dq, dk, dv, None
+
+
+torch.library.register_autograd(
+    "rbf_attn_v5::scaled_fwd", _scaled_backward, setup_context=_scaled_setup_context
+)
+
+
+# ---------------------------------------------------------------------------------------------
+# rbf_attn_v5::non_softmax_fwd / non_softmax_bwd  (rbf_attention.py:1355-1511)
+# ---------------------------------------------------------------------------------------------
+@torch.library.custom_op("rbf_attn_v5::non_softmax_fwd", mutates_args=())
+def rbf_non_softmax_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool) -> torch.Tensor:
+    return _forward(q, k, v, is_causal, softmax=False)[0]
+
+
+@rbf_non_softmax_fwd.register_fake
+def _(q, k, v, is_causal):
+    return torch.empty_like(q, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op("rbf_attn_v5::non_softmax_bwd", mutates_args=())
+def rbf_non_softmax_bwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    dout: torch.Tensor,
+    is_causal: bool,
+    sm_scale: float,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _backward(q, k, v, None, None, dout, is_causal, sm_scale, softmax=False)
+
+
+@rbf_non_softmax_bwd.register_fake
+def _(q, k, v, dout, is_causal, sm_scale):
+    return (
+        torch.empty_like(q, memory_format=torch.contiguous_format),
+        torch.empty_like(k, memory_format=torch.contiguous_format),
+        torch.empty_like(v, memory_format=torch.contiguous_format),
+    )
+
+
+def _non_softmax_setup_context(ctx, inputs, output):
+    q, k, v, is_causal = inputs
+    ctx.save_for_backward(q, k, v)
+    ctx.is_causal = is_causal
+    ctx.sm_scale = 1.0 / math.sqrt(q.shape[-1])
+
+
+def _non_softmax_backward(ctx, dout):
+    q, k, v = ctx.saved_tensors
+    dq, dk, dv = torch.ops.rbf_attn_v5.non_softmax_bwd(q, k, v, dout, ctx.is_causal, ctx.sm_scale)
+    return dq, dk, dv, None
+
+
+torch.library.register_autograd(
+    "rbf_attn_v5::non_softmax_fwd", _non_softmax_backward, setup_context=_non_softmax_setup_context
+)
+
+
+# ---------------------------------------------------------------------------------------------
+# Wrappers with the reference's names (rbf_attention.py:848-853)
+# ---------------------------------------------------------------------------------------------
+def run_triton_rbf(q, k, v, is_causal=True):
+    """Softmax RBF attention. The name is the reference's; nothing here uses Triton."""
+    return torch.ops.rbf_attn_v5.scaled_fwd(q, k, v, is_causal)[0]
+
+
+def run_triton_non_softmax_rbf(q, k, v, is_causal=True):
+    """Non-softmax RBF attention ``exp(-g|q-k|^2) V``. The name is the reference's."""
+    return torch.ops.rbf_attn_v5.non_softmax_fwd(q, k, v, is_causal)
