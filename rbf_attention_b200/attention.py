@@ -1,0 +1,237 @@
+"""Host-side mirror of the reference's attention block and helper names, routed to the B200 kernels.
+
+Everything a caller of the reference imports from its ``rbf_attention`` module for the RBF path exists
+here under the same name and call signature (paths are inside the reference project):
+
+  CustomCausalAttention      rbf_attention.py:1608-1762   same constructor, forward, parameter names
+  run_triton_rbf             rbf_attention.py:848
+  run_triton_non_softmax_rbf rbf_attention.py:852
+  compute_rbf_logits         rbf_attention.py:1547-1553   (kept a module attribute: analysis scripts patch it)
+  get_unrotated_sinusoids    rbf_attention.py:1539-1544   SuSiE table
+  precompute_freqs_cis, rotate_half, apply_rotary_pos_emb   rbf_attention.py:1518-1536
+  get_causal_mask            rbf_attention.py:1559-1565
+  rbf_flex_attention         rbf_attention.py:1590-1605   name kept; served by the fused kernel here
+
+``attention_type`` values "rbf_triton" and "rbf_non_softmax" run the sm_100a kernels (the names are the
+reference's; nothing here uses Triton). "rbf_flex" also runs the fused kernel. The ``*_slow`` / "rbf_math" /
+"standard*" types are plain PyTorch and exist so that reference checkpoints and evaluation code keep
+working; they are comparators, not the product path.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .ops import run_triton_non_softmax_rbf, run_triton_rbf
+
+__all__ = [
+    "CustomCausalAttention",
+    "run_triton_rbf",
+    "run_triton_non_softmax_rbf",
+    "rbf_flex_attention",
+    "compute_rbf_logits",
+    "get_unrotated_sinusoids",
+    "precompute_freqs_cis",
+    "rotate_half",
+    "apply_rotary_pos_emb",
+    "get_causal_mask",
+]
+
+
+# ---------------------------------------------------------------------------------------------
+# positional tables
+# ---------------------------------------------------------------------------------------------
+def _inverse_frequencies(dim: int, theta: float, device=None) -> torch.Tensor:
+    # evaluated as 1 / theta^(2i/dim) in fp32, so the tables match the reference's bit for bit
+    exponent = torch.arange(0, dim, 2, device=device).float() / dim
+    return 1.0 / (theta**exponent)
+
+
+def precompute_freqs_cis(dim, end, theta=10000.0):
+    """(cos, sin) RoPE tables of shape (end, dim), the half-table repeated twice along the last dim."""
+    angles = torch.outer(torch.arange(end).float(), _inverse_frequencies(dim, theta)[: dim // 2])
+    angles = angles.repeat(1, 2)
+    return angles.cos(), angles.sin()
+
+
+def rotate_half(x):
+    half = x.shape[-1] // 2
+    return torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+
+
+def apply_rotary_pos_emb(q, k, cos, sin):
+    cos, sin = cos[None, None], sin[None, None]
+    return (q * cos + rotate_half(q) * sin).type_as(q), (k * cos + rotate_half(k) * sin).type_as(k)
+
+
+def get_unrotated_sinusoids(seq_len, dim, device, theta=10000.0):
+    """SuSiE table: (seq_len, dim) = [sin(t * w) | cos(t * w)] for dim/2 frequencies w."""
+    t = torch.arange(seq_len, device=device).float()
+    angles = torch.outer(t, _inverse_frequencies(dim, theta, device))
+    return torch.cat((angles.sin(), angles.cos()), dim=-1)
+
+
+# ---------------------------------------------------------------------------------------------
+# comparator math (plain PyTorch)
+# ---------------------------------------------------------------------------------------------
+def compute_rbf_logits(q, k):
+    """-|q - k|^2 / sqrt(D), evaluated in fp32 through the expanded form, cast back to q's dtype."""
+    qf, kf = q.float(), k.float()
+    sq_dist = qf.square().sum(-1, keepdim=True) + kf.square().sum(-1).unsqueeze(-2) - 2.0 * (qf @ kf.mT)
+    return (sq_dist * (-1.0 / math.sqrt(q.size(-1)))).to(q.dtype)
+
+
+_CAUSAL_MASKS: dict = {}
+
+
+def get_causal_mask(seq_len, device):
+    """Boolean (seq_len, seq_len) mask, True strictly above the diagonal (= hidden), cached per device."""
+    key = (seq_len, str(device))
+    mask = _CAUSAL_MASKS.get(key)
+    if mask is None:
+        mask = torch.ones(seq_len, seq_len, device=device, dtype=torch.bool).triu_(1)
+        _CAUSAL_MASKS[key] = mask
+    return mask
+
+
+def rbf_flex_attention(q, k, v, is_causal=True):
+    """The reference implements this comparator with torch's flex_attention; its result is the softmax RBF
+    attention, which the fused kernel computes directly."""
+    return run_triton_rbf(q, k, v, is_causal=is_causal)
+
+
+def _materialised_attention(logits, v, seq_len, device, softmax: bool):
+    logits = logits.masked_fill(get_causal_mask(seq_len, device), float("-inf"))
+    weights = F.softmax(logits, dim=-1) if softmax else torch.exp(logits)
+    return weights @ v, weights
+
+
+def _augmented_sdpa(q, k, v):
+    """Softmax RBF attention through SDPA on q' = [q, 1], k' = [k, -|k|^2 / 2] with scale 2/sqrt(D)."""
+    d = q.size(-1)
+    k_sq = k.float().square().sum(-1, keepdim=True).to(k.dtype)
+    q_aug = torch.cat([q, torch.ones_like(q[..., :1])], dim=-1)
+    k_aug = torch.cat([k, -0.5 * k_sq], dim=-1)
+    pad = (-q_aug.shape[-1]) % 8
+    if pad:
+        q_aug, k_aug = F.pad(q_aug, (0, pad)), F.pad(k_aug, (0, pad))
+    v_pad = q_aug.shape[-1] - d
+    v_aug = F.pad(v, (0, v_pad)) if v_pad else v
+    out = F.scaled_dot_product_attention(q_aug, k_aug, v_aug, is_causal=True, scale=2.0 / math.sqrt(d))
+    return out[..., :d]
+
+
+# ---------------------------------------------------------------------------------------------
+# the attention block
+# ---------------------------------------------------------------------------------------------
+class CustomCausalAttention(nn.Module):
+    """Causal multi-head self-attention block with the reference's constructor and state-dict layout:
+    ``qkv_proj``, ``proj``, and for RBF types with ``use_rope=True`` the SuSiE parameters ``pos_weight``
+    (1, H, 1, D/2) and, with register tokens, ``reg_pos_emb`` (1, H, R, D). ``forward(x)`` returns
+    ``(out, attn_weights)`` where ``attn_weights`` is None except for the ``*_slow`` types."""
+
+    def __init__(
+        self,
+        num_heads,
+        emb_dims,
+        max_seq_len=2048,
+        use_rope=True,
+        attention_type="standard",
+        use_qk_norm=False,
+        apply_xsa=False,
+        num_registers=0,
+    ):
+        super().__init__()
+        self.num_heads = num_heads
+        self.attention_type = attention_type
+        self.use_qk_norm = use_qk_norm
+        self.apply_xsa = apply_xsa
+        self.num_registers = num_registers
+        self.head_dim = emb_dims // num_heads
+
+        self.qkv_proj = nn.Linear(emb_dims, 3 * emb_dims)
+        self.proj = nn.Linear(emb_dims, emb_dims)
+
+        self.positional_encoding_type = "none"
+        if use_rope and attention_type.startswith("standard"):
+            self.positional_encoding_type = "rope"
+            cos, sin = precompute_freqs_cis(self.head_dim, max_seq_len)
+            self.register_buffer("cos", cos, persistent=False)
+            self.register_buffer("sin", sin, persistent=False)
+        elif use_rope and attention_type.startswith("rbf"):
+            self.positional_encoding_type = "susie"
+            self.pos_dim = self.head_dim
+            self.pos_weight = nn.Parameter(torch.full((1, num_heads, 1, self.pos_dim // 2), 0.5))
+            if num_registers > 0:
+                self.reg_pos_emb = nn.Parameter(torch.randn(1, num_heads, num_registers, self.pos_dim) * 0.02)
+            self.register_buffer(
+                "susie_cache", get_unrotated_sinusoids(max_seq_len, self.pos_dim, device="cpu"), persistent=False
+            )
+
+    # -- positions -------------------------------------------------------------------------------
+    def _susie_embedding(self, seq_len: int, like: torch.Tensor) -> torch.Tensor:
+        """(1, H, seq_len, D) additive position term: learned rows for the register tokens in front,
+        then sinusoid(t) * [w | w] for text position t (counted after the registers)."""
+        text_len = seq_len - self.num_registers
+        weight = self.pos_weight.repeat(1, 1, 1, 2).to(like.dtype)
+        table = self.susie_cache[:text_len].to(device=like.device, dtype=like.dtype)
+        emb = table[None, None] * weight
+        if self.num_registers > 0:
+            emb = torch.cat([self.reg_pos_emb.to(like.dtype), emb], dim=2)
+        return emb
+
+    def _rope(self, q, k, seq_len: int):
+        r = self.num_registers
+        text_len = seq_len - r
+        cos, sin = self.cos[:text_len], self.sin[:text_len]
+        if r == 0:
+            return apply_rotary_pos_emb(q, k, cos, sin)
+        q_text, k_text = apply_rotary_pos_emb(q[:, :, r:], k[:, :, r:], cos, sin)
+        return torch.cat([q[:, :, :r], q_text], dim=2), torch.cat([k[:, :, :r], k_text], dim=2)
+
+    # -- forward ---------------------------------------------------------------------------------
+    def forward(self, x):
+        bsz, seq_len, emb = x.shape
+        qkv = self.qkv_proj(x).view(bsz, seq_len, 3, self.num_heads, self.head_dim)
+        q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)      # each (B, H, S, D), views of the fused buffer
+
+        if self.use_qk_norm:
+            q = F.rms_norm(q, (self.head_dim,))
+            k = F.rms_norm(k, (self.head_dim,))
+        if self.positional_encoding_type == "susie":
+            pos = self._susie_embedding(seq_len, q)
+            q, k = q + pos, k + pos
+        elif self.positional_encoding_type == "rope":
+            q, k = self._rope(q, k, seq_len)
+
+        attn_weights = None
+        kind = self.attention_type
+        if kind in ("rbf_triton", "rbf_flex"):
+            out = run_triton_rbf(q, k, v, is_causal=True)
+        elif kind == "rbf_non_softmax":
+            out = run_triton_non_softmax_rbf(q, k, v, is_causal=True)
+        elif kind == "standard":
+            out = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        elif kind == "standard_slow":
+            out, attn_weights = _materialised_attention(
+                (q @ k.mT) / math.sqrt(q.size(-1)), v, seq_len, x.device, softmax=True
+            )
+        elif kind == "rbf_slow":
+            out, attn_weights = _materialised_attention(compute_rbf_logits(q, k), v, seq_len, x.device, softmax=True)
+        elif kind == "rbf_non_softmax_slow":
+            out, attn_weights = _materialised_attention(compute_rbf_logits(q, k), v, seq_len, x.device, softmax=False)
+        elif kind == "rbf_math":
+            out = _augmented_sdpa(q, k, v)
+        else:
+            raise ValueError(f"unknown attention_type {kind!r}")
+
+        if self.apply_xsa:
+            v_hat = F.normalize(v, dim=-1)
+            out = out - (out * v_hat).sum(dim=-1, keepdim=True) * v_hat
+
+        out = out.transpose(1, 2).reshape(bsz, seq_len, emb)
+        return self.proj(out), attn_weights

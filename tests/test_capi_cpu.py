@@ -1,0 +1,63 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the header declares, and rejects bad
+arguments before any CUDA work."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from rbf_attention_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "rbf_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(rbf_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    lib = ctypes.CDLL(built_library)
+    names = _declared_symbols()
+    assert "rbf_b200_fwd" in names and "rbf_b200_bwd" in names
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/rbf_b200.h but not exported"
+    # and the ctypes table of the package covers the same set
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_abi_version_and_workspace_size(built_library):
+    lib = _lib.load()
+    assert lib.rbf_b200_abi_version() == _lib.ABI_VERSION
+    # status block + key norms (+ query norms for the non-softmax variant) (+ delta for the backward)
+    rows = 2 * 3 * 256 * 4  # N = 200 pads to 256 rows
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 0) == 256 + rows
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 0) == 256 + 2 * rows
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 1) == 256 + 2 * rows
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 1) == 256 + 3 * rows
+    assert lib.rbf_b200_workspace_bytes(0, 3, 200, 64, 1, 0) == 0
+
+
+def _call_fwd(lib, *, q=0x1000, B=1, H=1, N=128, D=64, dtype=0, strides=(8192, 8192, 64), ws=0x10000, ws_bytes=1 << 20):
+    s = (ctypes.c_int64 * 3)(*strides)
+    return lib.rbf_b200_fwd(q, 0x2000, 0x3000, 0x4000, 0x5000, ws, ws_bytes, B, H, N, D, s, s, s, s, dtype, 1, 1,
+                            0.125, None)
+
+
+def test_bad_arguments_are_rejected_before_any_launch(built_library):
+    lib = _lib.load()
+    assert _call_fwd(lib, D=48) == 1 and b"head dim" in lib.rbf_b200_last_error()
+    assert _call_fwd(lib, N=0) == 1
+    assert _call_fwd(lib, dtype=7) == 1
+    assert _call_fwd(lib, q=0) == 1 and b"q is NULL" in lib.rbf_b200_last_error()
+    assert _call_fwd(lib, q=0x1004) == 2 and b"16-byte" in lib.rbf_b200_last_error()
+    assert _call_fwd(lib, N=256, strides=(8192, 8192, 60)) == 2      # row stride not a multiple of 8 elements
+    assert _call_fwd(lib, N=256, strides=(8192, 8192, 32)) == 2      # rows overlap
+    assert _call_fwd(lib, ws=0) == 3
+    assert _call_fwd(lib, ws_bytes=16) == 3 and b"needed" in lib.rbf_b200_last_error()
+    with pytest.raises(ValueError):
+        _lib.check(1, "x")
+    with pytest.raises(RuntimeError):
+        _lib.check(3, "x")

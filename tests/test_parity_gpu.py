@@ -1,0 +1,283 @@
+"""Parity of the sm_100a kernels with the CPU oracle, through the C ABI and through the operator boundary.
+
+Stated tolerances (bf16 operands, fp32 accumulation, against the fp32/fp64 oracle evaluated on the same
+bf16-valued inputs):  O: max-abs <= 2e-2 and relative L2 <= 6e-3;  dQ, dK, dV: relative L2 <= 6e-3 and
+max-abs <= 2e-2 * max|ref|.  fp16 operands: relative L2 <= 1e-3.  The reference's own parity script accepts
+atol 1e-2 (fp16) / 3e-2 (fp32 inputs) with rtol 1e-3 (test_equivalence.py:87-103); that case is replayed below.
+"""
+
+import ctypes
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import rbf_oracle as oracle
+from rbf_attention_b200 import _lib, attention, ops
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+REL_L2 = {torch.bfloat16: 6e-3, torch.float16: 1e-3}
+
+
+def _s3(t):
+    return (ctypes.c_int64 * 3)(*t.stride()[:3])
+
+
+def cabi_forward(q, k, v, causal, softmax):
+    """Calls rbf_b200_fwd directly with raw pointers, as a foreign binding would."""
+    lib = _lib.load()
+    B, H, N, D = q.shape
+    out = torch.empty((B, H, N, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    nbytes = lib.rbf_b200_workspace_bytes(B, H, N, D, int(softmax), 0)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    rc = lib.rbf_b200_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), ws.data_ptr(),
+                          nbytes, B, H, N, D, _s3(q), _s3(k), _s3(v), _s3(out), 0 if q.dtype == torch.bfloat16 else 1,
+                          int(causal), int(softmax), 1.0 / math.sqrt(D), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.rbf_b200_last_error()
+    code = ctypes.c_uint(0)
+    assert lib.rbf_b200_read_device_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream,
+                                           ctypes.byref(code)) == 0, lib.rbf_b200_last_error()
+    return out, (lse if softmax else None)
+
+
+def cabi_backward(q, k, v, out, lse, do, causal, softmax):
+    lib = _lib.load()
+    B, H, N, D = q.shape
+    dq, dk, dv = (torch.empty((B, H, N, D), dtype=q.dtype, device=q.device) for _ in range(3))
+    nbytes = lib.rbf_b200_workspace_bytes(B, H, N, D, int(softmax), 1)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    rc = lib.rbf_b200_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr() if softmax else None,
+                          lse.data_ptr() if softmax else None, do.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                          dv.data_ptr(), ws.data_ptr(), nbytes, B, H, N, D, _s3(q), _s3(k), _s3(v), _s3(out),
+                          _s3(do), _s3(dq), _s3(dk), _s3(dv), 0 if q.dtype == torch.bfloat16 else 1, int(causal),
+                          int(softmax), 1.0 / math.sqrt(D), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.rbf_b200_last_error()
+    code = ctypes.c_uint(0)
+    assert lib.rbf_b200_read_device_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream,
+                                           ctypes.byref(code)) == 0, lib.rbf_b200_last_error()
+    return dq, dk, dv
+
+
+def check(name, got, ref, rel_l2, max_frac=2e-2):
+    rep = oracle.error_report(got, ref)
+    assert not torch.isnan(got).any(), f"{name}: NaN"
+    assert rep["rel_l2"] <= rel_l2, f"{name}: {rep}"
+    assert rep["max_abs"] <= max_frac * max(1.0, ref.abs().max().item()), f"{name}: {rep}"
+    return rep
+
+
+CASES = [
+    # B, H, N, D, causal, softmax
+    (1, 1, 128, 64, True, True),
+    (1, 2, 77, 64, True, True),          # shorter than one tile
+    (2, 3, 1000, 64, True, True),        # ragged last tile
+    (2, 3, 1000, 64, False, True),
+    (1, 2, 1028, 64, True, True),        # 1024 text tokens + 4 register tokens
+    (1, 2, 512, 128, True, True),
+    (1, 2, 1000, 128, False, True),
+    (1, 2, 640, 64, True, False),
+    (1, 2, 1000, 128, False, False),
+    (1, 1, 1, 64, True, True),           # single row
+]
+
+
+@pytest.mark.parametrize("B,H,N,D,causal,softmax", CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_forward_backward_parity_through_c_abi(B, H, N, D, causal, softmax, dtype):
+    std = 1.0 if softmax else 0.5
+    q, k, v, do = oracle.make_inputs(B, H, N, D, seed=N + D, dtype=dtype, std=std, key_norm_sigma=0.3 if softmax else 0.0)
+    ref_o, ref_dq, ref_dk, ref_dv = oracle.torch_forward_backward(q, k, v, do, causal, softmax, dtype=torch.float32)
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+    out, lse = cabi_forward(qd, kd, vd, causal, softmax)
+    dq, dk, dv = cabi_backward(qd, kd, vd, out, lse, dod, causal, softmax)
+    tol = REL_L2[dtype]
+    check("O", out.cpu().float(), ref_o, tol)
+    check("dQ", dq.cpu().float(), ref_dq, tol)
+    check("dK", dk.cpu().float(), ref_dk, tol)
+    check("dV", dv.cpu().float(), ref_dv, tol)
+    if softmax:
+        ref_l = oracle.torch_lse2(q, k, causal)
+        assert (lse.cpu() - ref_l).abs().max().item() <= 2e-4 * max(1.0, ref_l.abs().max().item())
+
+
+def test_golden_fixture_small(golden_dir):
+    """attn_small.npz holds the reference's fp32 results; the kernel sees the same inputs rounded to bf16."""
+    g = np.load(os.path.join(golden_dir, "attn_small.npz"))
+    for causal in (True, False):
+        for softmax in (True, False):
+            scale = 1.0 if softmax else 0.5
+            q, k, v = (torch.tensor(g[n] * scale, device=DEV).bfloat16() for n in ("q", "k", "v"))
+            do = torch.tensor(g["do"], device=DEV).bfloat16()
+            out, lse = cabi_forward(q, k, v, causal, softmax)
+            dq, dk, dv = cabi_backward(q, k, v, out, lse, do, causal, softmax)
+            tag = f"{'c' if causal else 'f'}{'s' if softmax else 'n'}"
+            for got, name in ((out, "o"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+                ref = torch.tensor(g[f"{name}_{tag}"])
+                rep = oracle.error_report(got.cpu().float(), ref)
+                assert rep["rel_l2"] <= 1.5e-2, (tag, name, rep)   # includes the bf16 rounding of the inputs
+
+
+@pytest.mark.parametrize("dtype,atol", [(torch.float16, 1e-2), (torch.float32, 3e-2)])
+def test_reference_parity_script_case(golden_dir, dtype, atol):
+    """test_equivalence.py:36-103 replayed: B2 H4 N128 D64, seed 42, causal, tolerances of that script."""
+    g = np.load(os.path.join(golden_dir, "attn_equiv.npz"))
+    torch.manual_seed(42)
+    q, k, v, do = (torch.randn(2, 4, 128, 64) for _ in range(4))
+    qd, kd, vd = (t.to(DEV, dtype).requires_grad_(True) for t in (q, k, v))
+    out = attention.run_triton_rbf(qd, kd, vd, is_causal=True)
+    out.backward(do.to(DEV, dtype))
+    for got, name in ((out, "o"), (qd.grad, "dq"), (kd.grad, "dk"), (vd.grad, "dv")):
+        assert got.dtype == dtype
+        ref = torch.tensor(g[name])
+        sub = got.detach().cpu().float()[:, :, ::8]
+        if dtype == torch.float32:
+            # fp32 inputs run on 16-bit tensor-core operands here (the reference uses TF32 for them)
+            assert (sub - ref).abs().max().item() <= atol + 1e-3 * ref.abs().max().item(), name
+        else:
+            assert torch.allclose(sub, ref, atol=atol, rtol=1e-3), (name, (sub - ref).abs().max().item())
+
+
+def test_strided_views_as_the_attention_block_produces_them():
+    """q, k dense-but-permuted, v a view into the fused qkv buffer, dout non-contiguous (rbf_attention.py:1659-1662)."""
+    B, S, H, D = 2, 300, 4, 64
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, S, 3 * H * D, generator=g).to(DEV, torch.bfloat16)
+    q, k, v = qkv.view(B, S, 3, H, D).permute(2, 0, 3, 1, 4).unbind(0)
+    assert not v.is_contiguous() and v.stride(3) == 1
+    q = (q + 0.01).detach().requires_grad_(True)        # a fresh permuted-dense tensor like q + pos_emb
+    k = (k + 0.01).detach().requires_grad_(True)
+    v = v.detach().requires_grad_(True)
+    do = torch.randn(B, S, H * D, generator=g).to(DEV, torch.bfloat16).view(B, S, H, D).transpose(1, 2)
+    out = ops.run_triton_rbf(q, k, v, True)
+    out.backward(do)
+    ref = oracle.torch_forward_backward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(), True, True,
+                                        dtype=torch.float32)
+    for name, got, want in zip(("O", "dQ", "dK", "dV"), (out, q.grad, k.grad, v.grad), ref):
+        check(name, got.detach().cpu().float(), want, 6e-3)
+
+
+def test_results_are_bitwise_reproducible():
+    q, k, v, do = (t.to(DEV) for t in oracle.make_inputs(2, 2, 700, 64, seed=1, dtype=torch.bfloat16))
+    o1, l1 = cabi_forward(q, k, v, True, True)
+    g1 = cabi_backward(q, k, v, o1, l1, do, True, True)
+    o2, l2 = cabi_forward(q, k, v, True, True)
+    g2 = cabi_backward(q, k, v, o2, l2, do, True, True)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    for a, b in zip(g1, g2):
+        assert torch.equal(a, b)
+
+
+def _properties(B, H, N, D, causal, key_norm_sigma, oracle_pairs):
+    q, k, v, do = (t.to(DEV) for t in oracle.make_inputs(B, H, N, D, seed=0, dtype=torch.bfloat16,
+                                                        key_norm_sigma=key_norm_sigma))
+    out, lse = cabi_forward(q, k, v, causal, True)
+    dq, dk, dv = cabi_backward(q, k, v, out, lse, do, causal, True)
+    for t in (out, dq, dk, dv):
+        assert torch.isfinite(t).all()
+    # (1) rows of P sum to one: V = 1 gives O = 1
+    ones = torch.ones_like(v)
+    o1, _ = cabi_forward(q, k, ones, causal, True)
+    assert (o1.float() - 1.0).abs().max().item() <= 1e-2
+    # (2) column sums: sum_j dV_j = sum_i dO_i because every row of P sums to one
+    lhs, rhs = dv.float().sum(2), do.float().sum(2)
+    assert (lhs - rhs).norm().item() <= 1e-2 * rhs.norm().item()
+    # (3) translation invariance of |q - k|^2: sum_i dQ_i + sum_j dK_j = 0; this only holds with the
+    #     gradient through the key-norm term included
+    resid = dq.float().sum(2) + dk.float().sum(2)
+    scale = dq.float().abs().sum(2) + dk.float().abs().sum(2)
+    assert (resid.abs() / scale).max().item() <= 2e-2
+    # (4) linearity in V
+    o_half, _ = cabi_forward(q, k, (v.float() * 0.5).bfloat16(), causal, True)
+    assert (o_half.float() * 2 - out.float()).abs().max().item() <= 4e-2
+    # (5) a few (batch, head) pairs against the oracle at full sequence length
+    for (b, h) in oracle_pairs:
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        ref = oracle.torch_forward_backward(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), do[sl].cpu(), causal, True,
+                                            dtype=torch.float32)
+        for name, got, want in zip(("O", "dQ", "dK", "dV"), (out, dq, dk, dv), ref):
+            check(f"{name}[{b},{h}]", got[sl].cpu().float(), want, 6e-3)
+
+
+def test_full_size_config2_properties():
+    """B8 H16 N4096 D64 causal with outlier key norms: size-independent properties + oracle on two pairs."""
+    _properties(8, 16, 4096, 64, True, 0.5, [(0, 0), (7, 15)])
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_full_length_config3_properties(causal):
+    """N = 16384, D = 128 (batch x heads reduced to keep the check short): properties + oracle on one pair."""
+    _properties(1, 4, 16384, 128, causal, 0.0, [(0, 3)] if causal else [])
+
+
+def test_config4_non_softmax_slice_against_oracle():
+    """Non-softmax variant at N = 8192, D = 64, causal, inputs ~ N(0, 0.5^2); one pair against the oracle."""
+    q, k, v, do = (t.to(DEV) for t in oracle.make_inputs(1, 4, 8192, 64, seed=0, dtype=torch.bfloat16, std=0.5))
+    out, _ = cabi_forward(q, k, v, True, False)
+    dq, dk, dv = cabi_backward(q, k, v, out, None, do, True, False)
+    sl = (slice(0, 1), slice(2, 3))
+    ref = oracle.torch_forward_backward(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), do[sl].cpu(), True, False,
+                                        dtype=torch.float32)
+    for name, got, want in zip(("O", "dQ", "dK", "dV"), (out, dq, dk, dv), ref):
+        check(name, got[sl].cpu().float(), want, 6e-3)
+    # translation invariance holds for the non-softmax variant too (both norm terms are differentiated)
+    resid = dq.float().sum(2) + dk.float().sum(2)
+    scale = dq.float().abs().sum(2) + dk.float().abs().sum(2)
+    assert (resid.abs() / scale).max().item() <= 2e-2
+
+
+def test_operator_errors():
+    q = torch.randn(1, 2, 64, 64, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        ops.run_triton_rbf(q, q[:, :1], q)
+    with pytest.raises(ValueError):
+        ops.run_triton_rbf(q, q.half(), q)
+    with pytest.raises(ValueError):
+        ops.run_triton_rbf(q[..., :48], q[..., :48], q[..., :48])
+    with pytest.raises(ValueError):
+        ops.run_triton_rbf(q[0], q[0], q[0])
+
+
+def test_attention_block_matches_its_comparator_branch():
+    """CustomCausalAttention('rbf_triton') in bf16 against 'rbf_slow' in fp32 with the same weights:
+    1024 text tokens + 4 register tokens, SuSiE positions (the end-to-end model's attention shape)."""
+    torch.manual_seed(0)
+    slow = attention.CustomCausalAttention(8, 512, max_seq_len=1024, attention_type="rbf_slow", num_registers=4)
+    fast = attention.CustomCausalAttention(8, 512, max_seq_len=1024, attention_type="rbf_triton", num_registers=4)
+    fast.load_state_dict(slow.state_dict())
+    fast = fast.to(DEV, torch.bfloat16)
+    x = torch.randn(2, 1028, 512)
+    gy = torch.randn(2, 1028, 512)
+    xs = x.clone().requires_grad_(True)
+    ys, _ = slow(xs)
+    ys.backward(gy)
+    xf = x.to(DEV, torch.bfloat16).requires_grad_(True)
+    yf, w = fast(xf)
+    yf.backward(gy.to(DEV, torch.bfloat16))
+    assert w is None
+    assert oracle.error_report(yf.detach().cpu().float(), ys.detach())["rel_l2"] <= 2e-2
+    assert oracle.error_report(xf.grad.cpu().float(), xs.grad)["rel_l2"] <= 3e-2
+    for (name, pf), (_, ps) in zip(fast.named_parameters(), slow.named_parameters()):
+        assert oracle.error_report(pf.grad.cpu().float(), ps.grad)["rel_l2"] <= 5e-2, name
+
+
+def test_non_softmax_block_and_compiled_call():
+    torch.manual_seed(1)
+    blk = attention.CustomCausalAttention(4, 256, max_seq_len=256, attention_type="rbf_non_softmax").to(DEV, torch.bfloat16)
+    ref = attention.CustomCausalAttention(4, 256, max_seq_len=256, attention_type="rbf_non_softmax_slow").to(DEV)
+    ref.load_state_dict({k: v.float() for k, v in blk.state_dict().items()})
+    x = (torch.randn(2, 200, 256, device=DEV) * 0.3)
+    y, _ = blk(x.bfloat16())
+    y_ref, _ = ref(x.bfloat16().float())
+    assert oracle.error_report(y.float().cpu(), y_ref.detach().cpu())["rel_l2"] <= 3e-2
+
+    @torch.compile(fullgraph=True)
+    def f(q, k, v):
+        return attention.run_triton_rbf(q * 1.0, k, v, is_causal=True) + 0.0
+
+    q, k, v, _ = (t.to(DEV) for t in oracle.make_inputs(1, 2, 256, 64, seed=2, dtype=torch.bfloat16))
+    assert torch.equal(f(q, k, v), attention.run_triton_rbf(q, k, v, True))
