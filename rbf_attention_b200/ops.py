@@ -53,9 +53,10 @@ def _compute_dtype(q: torch.Tensor) -> torch.dtype:
     if q.dtype in _DTYPE_CODE:
         return q.dtype
     if q.dtype == torch.float32:
-        # fp32 inputs run with 16-bit tensor-core operands and fp32 accumulation; the reference's
-        # Triton path uses TF32 for them (rbf_attention.py:183). bf16 keeps fp32's exponent range.
-        return torch.bfloat16
+        # fp32 inputs run with fp16 tensor-core operands (11-bit significand, like the TF32 the reference's
+        # Triton path uses for them, rbf_attention.py:183) and fp32 accumulation. fp16's range limit applies:
+        # |x| must stay below 65504, which attention activations do by orders of magnitude.
+        return torch.float16
     raise ValueError(f"unsupported dtype {q.dtype} (bfloat16, float16 or float32)")
 
 

@@ -66,6 +66,8 @@ def cabi_backward(q, k, v, out, lse, do, causal, softmax):
 def check(name, got, ref, rel_l2, max_frac=2e-2):
     rep = oracle.error_report(got, ref)
     assert not torch.isnan(got).any(), f"{name}: NaN"
+    if rep["max_abs"] <= 1e-5:      # e.g. a single-key row, whose dQ and dK are exactly zero in the oracle
+        return rep
     assert rep["rel_l2"] <= rel_l2, f"{name}: {rep}"
     assert rep["max_abs"] <= max_frac * max(1.0, ref.abs().max().item()), f"{name}: {rep}"
     return rep
