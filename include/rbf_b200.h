@@ -79,6 +79,25 @@ int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, c
                  const int64_t* dk_strides, const int64_t* dv_strides, int dtype, int causal, int softmax,
                  float sm_scale, void* stream);
 
+/* The same calls restricted to some of their kernels, for per-kernel timing and profiling. `phases` is a
+ * mask of RBF_B200_PHASE_*: the pre-passes (key / query norms, delta), the main kernel (forward; dK/dV in the
+ * backward) and the backward's second kernel (dQ). Skipped phases leave the workspace contents of an earlier
+ * full call in place. No counterpart in the reference, whose launchers always run every kernel. */
+#define RBF_B200_PHASE_PREPASS 1
+#define RBF_B200_PHASE_MAIN 2
+#define RBF_B200_PHASE_MAIN2 4
+#define RBF_B200_PHASE_ALL 7
+int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
+                        size_t workspace_bytes, int B, int H, int N, int D, const int64_t* q_strides,
+                        const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides, int dtype,
+                        int causal, int softmax, float sm_scale, void* stream, int phases);
+int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void* out, const float* lse,
+                        const void* dout, void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int B,
+                        int H, int N, int D, const int64_t* q_strides, const int64_t* k_strides,
+                        const int64_t* v_strides, const int64_t* o_strides, const int64_t* do_strides,
+                        const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides, int dtype,
+                        int causal, int softmax, float sm_scale, void* stream, int phases);
+
 /* Synchronises `stream` and reads the device status word that the last call using `workspace` left:
  * 0 = ok, otherwise (site << 24 | block) of the bounded wait that ran out. Returns RBF_B200_ERR_DEVICE
  * when the word is non-zero. No counterpart in the reference (its kernels have no device-side waits). */

@@ -105,10 +105,10 @@ size_t rbf_b200_workspace_bytes(int B, int H, int N, int D, int softmax, int bac
   return carve(nullptr, B, H, N, softmax, backward).bytes;
 }
 
-int rbf_b200_fwd(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
-                 size_t workspace_bytes, int B, int H, int N, int D, const int64_t* q_strides,
-                 const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides, int dtype,
-                 int causal, int softmax, float sm_scale, void* stream_v) {
+int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
+                        size_t workspace_bytes, int B, int H, int N, int D, const int64_t* q_strides,
+                        const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides, int dtype,
+                        int causal, int softmax, float sm_scale, void* stream_v, int phases) {
   g_last_error[0] = 0;
   int rc;
   if ((rc = check_common(B, H, N, D, dtype, sm_scale))) return rc;
@@ -137,13 +137,17 @@ int rbf_b200_fwd(const void* q, const void* k, const void* v, void* out, float* 
   r.x = k; r.y = nullptr; r.out = ws.ksq; r.B = B; r.H = H; r.N = N; r.n_pad = n_pad;
   set_strides(r.xs, k_strides); set_strides(r.ys, k_strides);
   r.scale = c; r.pad_value = INFINITY; r.status_to_clear = ws.status;
-  cudaError_t e = rbf::launch_row_reduce(r, bf16, D, stream);
-  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "key-norm pre-pass launch failed: %s", cudaGetErrorString(e));
-  if (!softmax) {
-    r.x = q; r.out = ws.row_bias; set_strides(r.xs, q_strides); r.pad_value = 0.f; r.status_to_clear = nullptr;
+  cudaError_t e = cudaSuccess;
+  if (phases & RBF_B200_PHASE_PREPASS) {
     e = rbf::launch_row_reduce(r, bf16, D, stream);
-    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "query-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "key-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+    if (!softmax) {
+      r.x = q; r.out = ws.row_bias; set_strides(r.xs, q_strides); r.pad_value = 0.f; r.status_to_clear = nullptr;
+      e = rbf::launch_row_reduce(r, bf16, D, stream);
+      if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "query-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+    }
   }
+  if (!(phases & RBF_B200_PHASE_MAIN)) return RBF_B200_OK;
 
   a.ksq = ws.ksq; a.qsq = ws.row_bias; a.lse = lse; a.status = ws.status;
   a.B = B; a.H = H; a.N = N; a.n_pad = n_pad; a.causal = causal ? 1 : 0; a.scale2 = 2.f * c;
@@ -152,12 +156,20 @@ int rbf_b200_fwd(const void* q, const void* k, const void* v, void* out, float* 
   return RBF_B200_OK;
 }
 
-int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, const float* lse, const void* dout,
-                 void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int B, int H, int N, int D,
-                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
-                 const int64_t* o_strides, const int64_t* do_strides, const int64_t* dq_strides,
-                 const int64_t* dk_strides, const int64_t* dv_strides, int dtype, int causal, int softmax,
-                 float sm_scale, void* stream_v) {
+int rbf_b200_fwd(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
+                 size_t workspace_bytes, int B, int H, int N, int D, const int64_t* q_strides,
+                 const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides, int dtype,
+                 int causal, int softmax, float sm_scale, void* stream_v) {
+  return rbf_b200_fwd_phases(q, k, v, out, lse, workspace, workspace_bytes, B, H, N, D, q_strides, k_strides,
+                             v_strides, o_strides, dtype, causal, softmax, sm_scale, stream_v, RBF_B200_PHASE_ALL);
+}
+
+int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void* out, const float* lse,
+                        const void* dout, void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int B,
+                        int H, int N, int D, const int64_t* q_strides, const int64_t* k_strides,
+                        const int64_t* v_strides, const int64_t* o_strides, const int64_t* do_strides,
+                        const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides, int dtype,
+                        int causal, int softmax, float sm_scale, void* stream_v, int phases) {
   g_last_error[0] = 0;
   int rc;
   if ((rc = check_common(B, H, N, D, dtype, sm_scale))) return rc;
@@ -196,7 +208,9 @@ int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, c
   // key norms
   r.x = k; r.y = nullptr; r.out = ws.ksq; set_strides(r.xs, k_strides); set_strides(r.ys, k_strides);
   r.scale = c; r.pad_value = INFINITY; r.status_to_clear = ws.status;
-  cudaError_t e = rbf::launch_row_reduce(r, bf16, D, stream);
+  cudaError_t e = cudaSuccess;
+  if (phases & RBF_B200_PHASE_PREPASS) {
+  e = rbf::launch_row_reduce(r, bf16, D, stream);
   if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "key-norm pre-pass launch failed: %s", cudaGetErrorString(e));
   r.status_to_clear = nullptr;
   if (softmax) {
@@ -213,6 +227,7 @@ int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, c
     e = cudaMemsetAsync(ws.delta, 0, static_cast<size_t>(B) * H * n_pad * sizeof(float), stream);
     if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "delta clear failed: %s", cudaGetErrorString(e));
   }
+  }
 
   a.ksq = ws.ksq;
   a.row_bias = softmax ? lse : ws.row_bias;
@@ -221,11 +236,26 @@ int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, c
   a.status = ws.status;
   a.B = B; a.H = H; a.N = N; a.n_pad = n_pad; a.causal = causal ? 1 : 0;
   a.scale2 = 2.f * c; a.grad_scale = 2.f * sm_scale;
-  e = rbf::launch_bwd_dkdv(a, bf16, D, softmax != 0, stream);
-  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
-  e = rbf::launch_bwd_dq(a, bf16, D, softmax != 0, stream);
-  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
+  if (phases & RBF_B200_PHASE_MAIN) {
+    e = rbf::launch_bwd_dkdv(a, bf16, D, softmax != 0, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "dK/dV launch failed: %s", cudaGetErrorString(e));
+  }
+  if (phases & RBF_B200_PHASE_MAIN2) {
+    e = rbf::launch_bwd_dq(a, bf16, D, softmax != 0, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "dQ launch failed: %s", cudaGetErrorString(e));
+  }
   return RBF_B200_OK;
+}
+
+int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, const float* lse, const void* dout,
+                 void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int B, int H, int N, int D,
+                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const int64_t* o_strides, const int64_t* do_strides, const int64_t* dq_strides,
+                 const int64_t* dk_strides, const int64_t* dv_strides, int dtype, int causal, int softmax,
+                 float sm_scale, void* stream_v) {
+  return rbf_b200_bwd_phases(q, k, v, out, lse, dout, dq, dk, dv, workspace, workspace_bytes, B, H, N, D, q_strides,
+                             k_strides, v_strides, o_strides, do_strides, dq_strides, dk_strides, dv_strides, dtype,
+                             causal, softmax, sm_scale, stream_v, RBF_B200_PHASE_ALL);
 }
 
 int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned int* code) {
