@@ -31,10 +31,14 @@ struct Workspace {
   float* ksq;
   float* row_bias;   // query norms (non-softmax)
   float* delta;      // backward only
+  float* dq_acc;     // single-kernel backward only: fp32 (B, H, N, D)
   size_t bytes;
 };
 
-Workspace carve(void* base, int B, int H, int N, int softmax, int backward) {
+// The softmax backward at head dim 64 runs as one kernel that accumulates dQ in fp32 global memory.
+bool use_fused_backward(int D, int softmax) { return softmax && D == 64; }
+
+Workspace carve(void* base, int B, int H, int N, int D, int softmax, int backward) {
   const size_t rows = static_cast<size_t>(B) * H * rbf::padded_rows(N);
   const size_t vec = align256(rows * sizeof(float));
   char* p = static_cast<char*>(base);
@@ -51,6 +55,10 @@ Workspace carve(void* base, int B, int H, int N, int softmax, int backward) {
   if (backward) {
     w.delta = reinterpret_cast<float*>(p + off);
     off += vec;
+    if (use_fused_backward(D, softmax)) {
+      w.dq_acc = reinterpret_cast<float*>(p + off);
+      off += align256(static_cast<size_t>(B) * H * N * D * sizeof(float));
+    }
   }
   w.bytes = off;
   return w;
@@ -100,9 +108,8 @@ int rbf_b200_abi_version(void) { return RBF_B200_ABI_VERSION; }
 const char* rbf_b200_last_error(void) { return g_last_error; }
 
 size_t rbf_b200_workspace_bytes(int B, int H, int N, int D, int softmax, int backward) {
-  (void)D;
   if (B <= 0 || H <= 0 || N <= 0) return 0;
-  return carve(nullptr, B, H, N, softmax, backward).bytes;
+  return carve(nullptr, B, H, N, D, softmax, backward).bytes;
 }
 
 int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
@@ -119,7 +126,7 @@ int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, 
   if (softmax && lse == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "lse is NULL");
   if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL or not 256-byte aligned");
-  const Workspace ws = carve(workspace, B, H, N, softmax, 0);
+  const Workspace ws = carve(workspace, B, H, N, D, softmax, 0);
   if (workspace_bytes < ws.bytes)
     return fail(RBF_B200_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, ws.bytes);
 
@@ -186,7 +193,7 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
   }
   if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL or not 256-byte aligned");
-  const Workspace ws = carve(workspace, B, H, N, softmax, 1);
+  const Workspace ws = carve(workspace, B, H, N, D, softmax, 1);
   if (workspace_bytes < ws.bytes)
     return fail(RBF_B200_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, ws.bytes);
 
@@ -227,6 +234,21 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     e = cudaMemsetAsync(ws.delta, 0, static_cast<size_t>(B) * H * n_pad * sizeof(float), stream);
     if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "delta clear failed: %s", cudaGetErrorString(e));
   }
+  }
+
+  if (use_fused_backward(D, softmax)) {
+    if (!(phases & (RBF_B200_PHASE_MAIN | RBF_B200_PHASE_MAIN2))) return RBF_B200_OK;
+    rbf::BwdFusedArgs f{};
+    f.tm_q = a.tm_q; f.tm_k = a.tm_k; f.tm_v = a.tm_v; f.tm_do = a.tm_do; f.tm_dk = a.tm_dk; f.tm_dv = a.tm_dv;
+    const int tr = rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, rbf::kTile);
+    if (tr != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the dQ accumulator (code %d)", tr);
+    f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
+    f.ksq = ws.ksq; f.lse = lse; f.delta = ws.delta; f.status = ws.status;
+    f.B = B; f.H = H; f.N = N; f.n_pad = n_pad; f.causal = causal ? 1 : 0;
+    f.scale2 = 2.f * c; f.grad_scale = 2.f * sm_scale;
+    e = rbf::launch_bwd_fused(f, bf16, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "backward launch failed: %s", cudaGetErrorString(e));
+    return RBF_B200_OK;
   }
 
   a.ksq = ws.ksq;

@@ -50,4 +50,21 @@ struct BwdArgs {
 cudaError_t launch_bwd_dkdv(const BwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream);
 cudaError_t launch_bwd_dq(const BwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream);
 
+// Single-kernel softmax backward for head dim 64 (five MMAs per tile pair, dQ through an fp32 accumulator).
+struct BwdFusedArgs {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
+  CUtensorMap tm_dq_acc;  // fp32 (B, H, N, 64) contiguous accumulator, box 32 x 128
+  float* dq_acc;
+  void* dq;               // final dQ in the operand type
+  int64_t dq_strides[3];
+  const float* ksq;       // (B*H, n_pad)
+  const float* lse;       // (B, H, N)
+  const float* delta;     // (B*H, n_pad)
+  DeviceStatus* status;
+  int B, H, N, n_pad;
+  int causal;
+  float scale2, grad_scale;
+};
+cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream);
+
 }  // namespace rbf

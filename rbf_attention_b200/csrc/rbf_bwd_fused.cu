@@ -1,0 +1,515 @@
+// Single-kernel backward of the softmax RBF attention for head dim 64 (sm_100a).
+//
+// A CTA owns 128 keys (K, V resident in shared memory) and streams the query tiles (Q, dO) past them. Per
+// query tile it issues five MMAs - the algorithmic minimum - and evaluates every exponential once:
+//   S^T  = K Q^T                 smem x smem -> TMEM
+//   dP^T = V dO^T                smem x smem -> TMEM
+//   P^T  = exp2(S^T * 2c - ksq[key] - L[query]),   dS^T = P^T * (dP^T - delta[query])     (registers)
+//   dV  += P^T  dO               TMEM x smem   (P^T written back over S^T as 16-bit pairs)
+//   dK  += dS^T Q                TMEM x smem   (dS^T written back over dP^T)
+//   dQ_partial = dS K            smem x smem   (dS^T also stored to shared memory; read as an M-major A operand)
+// dQ_partial leaves the CTA through a TMA reduce-add into an fp32 accumulator in global memory; a small
+// kernel converts it to the output type (times 2g) afterwards. dK gets the norm-gradient term in the
+// epilogue: dK = 2g (acc - rowsum(dS^T)[key] * k).
+//
+// Roles: warps 0-3 / 4-7 compute groups (thread = key row; group g owns query columns [64g, 64g+64) of the tile),
+// warps 8-11 drain dQ_partial (thread = query row), warp 12 TMA producer, warp 13 MMA issuer.
+// TMEM columns: S^T [0,128), dP^T [128,256), dV [256,320), dK [320,384), dQ_partial x2 [384,512).
+#include "common.cuh"
+#include "launch.h"
+
+namespace rbf {
+
+namespace bwdf {
+
+static constexpr int D = 64;
+static constexpr int kThreads = 448;
+static constexpr int kNumCompute = 256;
+static constexpr int kDrainWarp0 = 8;
+static constexpr int kLoadWarp = 12;
+static constexpr int kMmaWarp = 13;
+
+static constexpr int kTileBytes = kTile * D * 2;    // 16 KB: one 128 x 64 16-bit tile
+static constexpr int kQStages = 3;
+static constexpr int kDoStages = 3;
+static constexpr int kDsBytes = kTile * kTile * 2;  // 32 KB: dS^T as [key][query], two 64-query boxes
+static constexpr int kDqStageBytes = kTile * D * 4; // 32 KB: fp32 dQ_partial, two 32-column boxes
+
+struct Smem {
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTileBytes;
+  static constexpr int kQ = kV + kTileBytes;
+  static constexpr int kDo = kQ + kQStages * kTileBytes;
+  static constexpr int kDs = kDo + kDoStages * kTileBytes;
+  static constexpr int kDqStage = kDs + kDsBytes;
+  static constexpr int kVec = kDqStage + kDqStageBytes;   // [2 buffers][L | delta][128] floats
+  static constexpr int kRowsum = kVec + 2 * 2 * kTile * 4; // [128] floats: group 1's partial row sums
+  static constexpr int kBars = kRowsum + kTile * 4;
+  static constexpr int kNumBars = 1 + 2 * kQStages + 2 * kDoStages + 1 + 1 + 1 + 1 + 2 + 2 + 1 + 1 + 1;
+  static constexpr int kMisc = kBars + kNumBars * 8;
+  static constexpr int kTotal = kMisc + 16;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+static constexpr int kColS = 0, kColDP = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
+
+enum Site : uint32_t {
+  kSiteKV = 64, kSiteQFull, kSiteDoFull, kSiteQEmpty, kSiteDoEmpty, kSiteSFull, kSiteDPFull, kSitePFull, kSiteDSFull,
+  kSiteDQFull, kSiteDQDrained, kSiteAccDone, kSiteGroup, kSiteDrainGroup, kSiteDsFree
+};
+
+struct Params {
+  const float* ksq;      // (B*H, n_pad), +inf on padding rows
+  const float* lse;      // (B*H, N)
+  const float* delta;    // (B*H, n_pad), zero padded
+  DeviceStatus* status;
+  int H, N, n_pad, causal;
+  float scale2, grad_scale;
+};
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                     const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                     const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
+                     const __grid_constant__ CUtensorMap tm_dq_acc, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* s_k = smem + Smem::kK;
+  uint8_t* s_v = smem + Smem::kV;
+  uint8_t* s_q = smem + Smem::kQ;
+  uint8_t* s_do = smem + Smem::kDo;
+  uint8_t* s_ds = smem + Smem::kDs;
+  uint8_t* s_dq = smem + Smem::kDqStage;
+  float* s_vec = reinterpret_cast<float*>(smem + Smem::kVec);
+  float* s_rowsum = reinterpret_cast<float*>(smem + Smem::kRowsum);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = kv_full + 1;
+  uint64_t* q_empty = q_full + kQStages;
+  uint64_t* do_full = q_empty + kQStages;
+  uint64_t* do_empty = do_full + kDoStages;
+  uint64_t* s_full = do_empty + kDoStages;
+  uint64_t* dp_full = s_full + 1;
+  uint64_t* p_full = dp_full + 1;
+  uint64_t* ds_full = p_full + 1;
+  uint64_t* dq_full = ds_full + 1;       // [2]  dQ_partial buffer written (also: dS^T shared tile consumed)
+  uint64_t* dq_drained = dq_full + 2;    // [2]  drain group has copied the buffer out of TMEM
+  uint64_t* acc_done = dq_drained + 2;
+  uint64_t* grp_sync = acc_done + 1;     // compute groups (256 threads)
+  uint64_t* drain_sync = grp_sync + 1;   // drain group (128 threads)
+  uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + Smem::kMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 4);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int n_tiles = (p.N + kTile - 1) / kTile;
+  const int kt = blockIdx.x;                       // key tile; tile 0 is the heaviest under the causal mask
+  const int k_row0 = kt * kTile;
+  const int first = p.causal ? kt : 0;             // first query tile that sees these keys
+  const int cnt = n_tiles - first;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < kQStages; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    for (int s = 0; s < kDoStages; ++s) { mbar_init(&do_full[s], 1); mbar_init(&do_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_full, kNumCompute);
+    mbar_init(ds_full, kNumCompute);
+    mbar_init(&dq_full[0], 1);
+    mbar_init(&dq_full[1], 1);
+    mbar_init(&dq_drained[0], kTile);
+    mbar_init(&dq_drained[1], kTile);
+    mbar_init(acc_done, 1);
+    mbar_init(grp_sync, kNumCompute);
+    mbar_init(drain_sync, kTile);
+    fence_mbar_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_base_s;
+
+  if (warp == kLoadWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
+      tma_load_4d(s_k, &tm_k, kv_full, 0, k_row0, h, b);
+      tma_load_4d(s_v, &tm_v, kv_full, 0, k_row0, h, b);
+      for (int n = 0; n < cnt; ++n) {
+        const int row0 = (first + n) * kTile;
+        const int sq = n % kQStages, sd = n % kDoStages;
+        if (n >= kQStages && !mbar_wait(&q_empty[sq], ((n / kQStages) - 1) & 1, abort_flag, p.status, kSiteQEmpty))
+          break;
+        mbar_arrive_expect_tx(&q_full[sq], kTileBytes);
+        tma_load_4d(s_q + sq * kTileBytes, &tm_q, &q_full[sq], 0, row0, h, b);
+        if (n >= kDoStages && !mbar_wait(&do_empty[sd], ((n / kDoStages) - 1) & 1, abort_flag, p.status, kSiteDoEmpty))
+          break;
+        mbar_arrive_expect_tx(&do_full[sd], kTileBytes);
+        tma_load_4d(s_do + sd * kTileBytes, &tm_do, &do_full[sd], 0, row0, h, b);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(kTile, kTile, kBf16, false, false);  // keys x queries, both K-major
+      constexpr uint32_t idesc_acc = make_idesc(kTile, D, kBf16, false, true);     // A from TMEM, B N-major
+      constexpr uint32_t idesc_dq = make_idesc(kTile, D, kBf16, true, true);       // A M-major (dS^T tile), B N-major
+      const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v), q_addr = smem_u32(s_q), do_addr = smem_u32(s_do),
+                     ds_addr = smem_u32(s_ds);
+      auto issue_kmajor = [&](uint32_t dst, uint32_t a_addr, uint32_t b_addr) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss(dst, make_sdesc_sw128(a_addr + kk * 32, 16, 1024), make_sdesc_sw128(b_addr + kk * 32, 16, 1024),
+                  idesc_s, kk > 0);
+      };
+      // A: 16-bit pairs in TMEM; group g's 64 queries live at columns [64g, 64g+32) of the region
+      auto issue_acc = [&](uint32_t dst, uint32_t a_region, uint32_t b_addr, bool accumulate) {
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          const uint32_t a_col = (kk >> 2) * 64 + (kk & 3) * 8;
+          umma_ts(dst, a_region + a_col, make_sdesc_sw128(b_addr + kk * 2048, kTile * 128, 1024), idesc_acc,
+                  (accumulate || kk > 0) ? 1u : 0u);
+        }
+      };
+      auto wait_q = [&](int n) {
+        return mbar_wait(&q_full[n % kQStages], (n / kQStages) & 1, abort_flag, p.status, kSiteQFull);
+      };
+      auto wait_do = [&](int n) {
+        return mbar_wait(&do_full[n % kDoStages], (n / kDoStages) & 1, abort_flag, p.status, kSiteDoFull);
+      };
+
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kSiteKV);
+      if (ok) ok = wait_q(0);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_kmajor(tmem + kColS, k_addr, q_addr);
+        umma_commit(s_full);
+        ok = wait_do(0);
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        issue_kmajor(tmem + kColDP, v_addr, do_addr);
+        umma_commit(dp_full);
+      }
+      for (int n = 0; n < cnt && ok; ++n) {
+        const uint32_t q_n = q_addr + (n % kQStages) * kTileBytes;
+        const uint32_t do_n = do_addr + (n % kDoStages) * kTileBytes;
+        // dV += P^T dO
+        ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_acc(tmem + kColDV, tmem + kColS, do_n, n > 0);
+        // next S^T (S^T columns are free once dV has consumed P^T; the tensor pipe runs in issue order)
+        if (n + 1 < cnt) {
+          ok = wait_q(n + 1);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_kmajor(tmem + kColS, k_addr, q_addr + ((n + 1) % kQStages) * kTileBytes);
+          umma_commit(s_full);
+        }
+        // dK += dS^T Q
+        ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_acc(tmem + kColDK, tmem + kColDP, q_n, n > 0);
+        umma_commit(&q_empty[n % kQStages]);      // Q(n) and dO(n) have no reader left once these complete
+        umma_commit(&do_empty[n % kDoStages]);
+        // next dP^T
+        if (n + 1 < cnt) {
+          ok = wait_do(n + 1);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_kmajor(tmem + kColDP, v_addr, do_addr + ((n + 1) % kDoStages) * kTileBytes);
+          umma_commit(dp_full);
+        }
+        // dQ_partial = dS K : A = dS^T tile read M-major (rows = keys = reduction index), B = K read N-major
+        if (n >= 2) {
+          ok = mbar_wait(&dq_drained[n & 1], ((n - 2) >> 1) & 1, abort_flag, p.status, kSiteDQDrained);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) {
+          umma_ss(tmem + kColDQ + (n & 1) * D, make_sdesc_sw128(ds_addr + kk * 2048, kTile * 128, 1024),
+                  make_sdesc_sw128(k_addr + kk * 2048, kTile * 128, 1024), idesc_dq, kk > 0);
+        }
+        umma_commit(&dq_full[n & 1]);
+      }
+      if (ok) umma_commit(acc_done);
+    }
+  } else if (warp >= kDrainWarp0) {
+    // ------------------------------------------------------------------ dQ_partial drain (thread = query row)
+    const int r = tid - kDrainWarp0 * 32;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint32_t phase = 0;
+    bool ok = true;
+    auto drain_group_sync = [&]() -> bool {
+      mbar_arrive(drain_sync);
+      const bool done = mbar_wait(drain_sync, phase & 1, abort_flag, p.status, kSiteDrainGroup);
+      ++phase;
+      return done;
+    };
+    for (int n = 0; n < cnt; ++n) {
+      ok = mbar_wait(&dq_full[n & 1], (n >> 1) & 1, abort_flag, p.status, kSiteDQFull);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(tmem + kColDQ + (n & 1) * D + lane_sel + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<uint4*>(s_dq + c * (kTile * 128) + sw128_offset(r, g)) =
+              make_uint4(v[g * 4 + 0], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&dq_drained[n & 1]);
+      fence_proxy_async_smem();
+      ok = drain_group_sync();
+      if (!ok) break;
+      if (r == 0) {
+        const int row0 = (first + n) * kTile;
+        asm volatile(
+            "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+            ::"l"(reinterpret_cast<uint64_t>(&tm_dq_acc)), "r"(smem_u32(s_dq)), "r"(0), "r"(row0), "r"(h), "r"(b)
+            : "memory");
+        asm volatile(
+            "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+            ::"l"(reinterpret_cast<uint64_t>(&tm_dq_acc)), "r"(smem_u32(s_dq + kTile * 128)), "r"(32), "r"(row0),
+            "r"(h), "r"(b)
+            : "memory");
+        tma_store_commit();
+        tma_store_wait_read();     // the staging tile may be overwritten once the bulk engine has read it
+      }
+      ok = drain_group_sync();
+      if (!ok) break;
+    }
+    if (r == 0) tma_store_wait_all();
+  } else {
+    // ------------------------------------------------------------------ compute groups (thread = key row)
+    const int g = warp >> 2;                               // column half of the query tile
+    const int r = tid & (kTile - 1);
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int64_t bh64 = bh;
+    const float neg_ksq = -p.ksq[bh64 * p.n_pad + k_row0 + r];
+    float ds_rowsum = 0.f;
+    bool ok = true;
+    uint32_t grp_phase = 0;
+    auto group_sync = [&]() -> bool {
+      mbar_arrive(grp_sync);
+      const bool done = mbar_wait(grp_sync, grp_phase & 1, abort_flag, p.status, kSiteGroup);
+      ++grp_phase;
+      return done;
+    };
+    // per query tile: L (threads 0-127) and delta (threads 128-255), double buffered
+    auto fetch_vec = [&](int n) -> float {
+      const int idx = (first + n) * kTile + r;
+      if (g == 0) return (idx < p.N) ? p.lse[bh64 * p.N + idx] : INFINITY;
+      return p.delta[bh64 * p.n_pad + idx];
+    };
+    s_vec[g * kTile + r] = fetch_vec(0);
+
+    for (int n = 0; n < cnt; ++n) {
+      float vec_next = 0.f;
+      if (n + 1 < cnt) vec_next = fetch_vec(n + 1);
+      ok = group_sync() && mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const float* vbuf = s_vec + (n & 1) * 2 * kTile;
+      const float4* l4 = reinterpret_cast<const float4*>(vbuf + g * 64);
+      const float4* d4 = reinterpret_cast<const float4*>(vbuf + kTile + g * 64);
+
+      float pr[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t raw[32];
+        tmem_ld_x32(tmem + kColS + lane_sel + g * 64 + c * 32, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 lv = l4[c * 8 + i];
+          pr[c * 32 + i * 4 + 0] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 0]), p.scale2, neg_ksq) - lv.x);
+          pr[c * 32 + i * 4 + 1] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 1]), p.scale2, neg_ksq) - lv.y);
+          pr[c * 32 + i * 4 + 2] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 2]), p.scale2, neg_ksq) - lv.z);
+          pr[c * 32 + i * 4 + 3] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 3]), p.scale2, neg_ksq) - lv.w);
+        }
+      }
+      if (p.causal && n == 0) {
+        // diagonal tile: query column (64g + c) sees key row r iff column >= row
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          if (g * 64 + c < r) pr[c] = 0.f;
+      }
+      {
+        uint32_t packed[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) packed[i] = pack2<kBf16>(pr[2 * i], pr[2 * i + 1]);
+        tmem_st_x32(tmem + kColS + lane_sel + g * 64, packed);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
+      }
+
+      ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull);
+      // the dS^T shared tile is free once the previous dQ_partial MMA has completed
+      if (ok && n > 0) ok = mbar_wait(&dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, abort_flag, p.status, kSiteDsFree);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t ds_packed[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t raw[32];
+        tmem_ld_x32(tmem + kColDP + lane_sel + g * 64 + c * 32, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 dl = d4[c * 8 + i];
+          const float d0 = pr[c * 32 + i * 4 + 0] * (__uint_as_float(raw[i * 4 + 0]) - dl.x);
+          const float d1 = pr[c * 32 + i * 4 + 1] * (__uint_as_float(raw[i * 4 + 1]) - dl.y);
+          const float d2 = pr[c * 32 + i * 4 + 2] * (__uint_as_float(raw[i * 4 + 2]) - dl.z);
+          const float d3 = pr[c * 32 + i * 4 + 3] * (__uint_as_float(raw[i * 4 + 3]) - dl.w);
+          ds_rowsum += (d0 + d1) + (d2 + d3);
+          ds_packed[c * 16 + i * 2 + 0] = pack2<kBf16>(d0, d1);
+          ds_packed[c * 16 + i * 2 + 1] = pack2<kBf16>(d2, d3);
+        }
+      }
+      tmem_st_x32(tmem + kColDP + lane_sel + g * 64, ds_packed);
+      // the same values to shared memory as row r of the [key][query] tile, box g (queries 64g .. 64g+63)
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        *reinterpret_cast<uint4*>(s_ds + g * (kTile * 128) + sw128_offset(r, ch)) =
+            make_uint4(ds_packed[ch * 4 + 0], ds_packed[ch * 4 + 1], ds_packed[ch * 4 + 2], ds_packed[ch * 4 + 3]);
+      tmem_st_wait();
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(ds_full);
+      if (n + 1 < cnt) s_vec[((n + 1) & 1) * 2 * kTile + g * kTile + r] = vec_next;
+    }
+
+    if (ok) ok = mbar_wait(acc_done, 0, abort_flag, p.status, kSiteAccDone);
+    if (ok) {
+      tc_fence_after_sync();
+      // group 1 publishes its half of rowsum(dS^T); group 0 finishes dK, group 1 stores dV
+      if (g == 1) s_rowsum[r] = ds_rowsum;
+      ok = group_sync();
+    }
+    if (ok) {
+      uint8_t* stage = s_q + g * kTileBytes;   // the Q ring is dead: every MMA has completed
+      const float w = (g == 0) ? (ds_rowsum + s_rowsum[r]) : 0.f;
+      const float out_scale = (g == 0) ? p.grad_scale : 1.0f;
+      const uint32_t acc_col = (g == 0) ? kColDK : kColDV;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld_x32(tmem + acc_col + lane_sel + c * 32, acc);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t off = sw128_offset(r, c * 4 + q4);
+          const uint4 k_raw = *reinterpret_cast<const uint4*>(s_k + off);
+          const uint32_t kw[4] = {k_raw.x, k_raw.y, k_raw.z, k_raw.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 kv = unpack2<kBf16>(kw[i]);
+            const float x0 = out_scale * fmaf(-w, kv.x, __uint_as_float(acc[q4 * 8 + 2 * i]));
+            const float x1 = out_scale * fmaf(-w, kv.y, __uint_as_float(acc[q4 * 8 + 2 * i + 1]));
+            o[i] = pack2<kBf16>(x0, x1);
+          }
+          *reinterpret_cast<uint4*>(stage + off) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      ok = group_sync();
+      if (ok && r == 0) {
+        tma_store_4d(g == 0 ? &tm_dk : &tm_dv, stage, 0, k_row0, h, b);
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
+}
+
+// dq[b,h,n,:] = scale * acc[b,h,n,:]  (acc fp32 contiguous, dq 16-bit with strides)
+template <bool kBf16>
+__global__ void __launch_bounds__(256) dq_convert_kernel(const float* __restrict__ acc, void* __restrict__ dq, int H,
+                                                         int N, int64_t sb, int64_t sh, int64_t sn, float scale,
+                                                         int64_t total_chunks) {
+  // one thread per 8 consecutive elements of a row (D = 64: 8 chunks per row)
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total_chunks) return;
+  const int64_t row = i >> 3;
+  const int ch = static_cast<int>(i & 7);
+  const int64_t n = row % N;
+  const int64_t bh = row / N;
+  const int64_t b = bh / H, h = bh % H;
+  const float4* src = reinterpret_cast<const float4*>(acc + row * 64 + ch * 8);
+  const float4 a = src[0], c = src[1];
+  uint4 o;
+  o.x = pack2<kBf16>(a.x * scale, a.y * scale);
+  o.y = pack2<kBf16>(a.z * scale, a.w * scale);
+  o.z = pack2<kBf16>(c.x * scale, c.y * scale);
+  o.w = pack2<kBf16>(c.z * scale, c.w * scale);
+  uint16_t* dst = reinterpret_cast<uint16_t*>(dq) + b * sb + h * sh + n * sn + ch * 8;
+  *reinterpret_cast<uint4*>(dst) = o;
+}
+
+template <bool kBf16>
+static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
+  auto kernel = rbf_bwd_fused_kernel<kBf16>;
+  constexpr int smem = Smem::kDynamic;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const size_t acc_bytes = static_cast<size_t>(a.B) * a.H * a.N * D * sizeof(float);
+  cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, stream);
+  if (e != cudaSuccess) return e;
+  Params p{};
+  p.ksq = a.ksq; p.lse = a.lse; p.delta = a.delta; p.status = a.status;
+  p.H = a.H; p.N = a.N; p.n_pad = a.n_pad; p.causal = a.causal;
+  p.scale2 = a.scale2; p.grad_scale = a.grad_scale;
+  dim3 grid((a.N + kTile - 1) / kTile, a.B * a.H);
+  kernel<<<grid, kThreads, smem, stream>>>(a.tm_k, a.tm_v, a.tm_q, a.tm_do, a.tm_dk, a.tm_dv, a.tm_dq_acc, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int64_t chunks = static_cast<int64_t>(a.B) * a.H * a.N * 8;
+  dq_convert_kernel<kBf16><<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(
+      a.dq_acc, a.dq, a.H, a.N, a.dq_strides[0], a.dq_strides[1], a.dq_strides[2], a.grad_scale, chunks);
+  return cudaGetLastError();
+}
+
+}  // namespace bwdf
+
+cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream) {
+  return bf16 ? bwdf::launch_t<true>(a, stream) : bwdf::launch_t<false>(a, stream);
+}
+
+}  // namespace rbf

@@ -35,7 +35,9 @@ def test_abi_version_and_workspace_size(built_library):
     rows = 2 * 3 * 256 * 4  # N = 200 pads to 256 rows
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 0) == 256 + rows
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 0) == 256 + 2 * rows
-    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 1) == 256 + 2 * rows
+    # the single-kernel softmax backward at D = 64 adds an fp32 (B, H, N, D) dQ accumulator
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 1) == 256 + 2 * rows + 2 * 3 * 200 * 64 * 4
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 128, 1, 1) == 256 + 2 * rows
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 1) == 256 + 3 * rows
     assert lib.rbf_b200_workspace_bytes(0, 3, 200, 64, 1, 0) == 0
 
