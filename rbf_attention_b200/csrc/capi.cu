@@ -29,7 +29,7 @@ size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 struct Workspace {
   rbf::DeviceStatus* status;
   float* ksq;
-  float* row_bias;   // query norms (non-softmax)
+  float* row_bias;   // query norms (non-softmax) or the forward's L re-pitched to n_pad (softmax backward)
   float* delta;      // backward only
   float* dq_acc;     // single-kernel backward only: fp32 (B, H, N, D)
   size_t bytes;
@@ -48,7 +48,7 @@ Workspace carve(void* base, int B, int H, int N, int D, int softmax, int backwar
   off += kStatusBytes;
   w.ksq = reinterpret_cast<float*>(p + off);
   off += vec;
-  if (!softmax) {
+  if (!softmax || backward) {
     w.row_bias = reinterpret_cast<float*>(p + off);
     off += vec;
   }
@@ -140,19 +140,16 @@ int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, 
 
   const int n_pad = rbf::padded_rows(N);
   const float c = sm_scale * rbf::kLog2e;
-  rbf::RowReduceArgs r{};
-  r.x = k; r.y = nullptr; r.out = ws.ksq; r.B = B; r.H = H; r.N = N; r.n_pad = n_pad;
-  set_strides(r.xs, k_strides); set_strides(r.ys, k_strides);
-  r.scale = c; r.pad_value = INFINITY; r.status_to_clear = ws.status;
   cudaError_t e = cudaSuccess;
   if (phases & RBF_B200_PHASE_PREPASS) {
-    e = rbf::launch_row_reduce(r, bf16, D, stream);
-    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "key-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+    rbf::RowStatsArgs r{};
+    r.B = B; r.H = H; r.N = N; r.n_pad = n_pad; r.scale = c; r.status_to_clear = ws.status;
+    r.k = k; r.ksq_out = ws.ksq; set_strides(r.ks, k_strides);
     if (!softmax) {
-      r.x = q; r.out = ws.row_bias; set_strides(r.xs, q_strides); r.pad_value = 0.f; r.status_to_clear = nullptr;
-      e = rbf::launch_row_reduce(r, bf16, D, stream);
-      if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "query-norm pre-pass launch failed: %s", cudaGetErrorString(e));
+      r.q = q; r.qsq_out = ws.row_bias; r.qsq_pad = 0.f; set_strides(r.qs, q_strides);
     }
+    e = rbf::launch_row_stats(r, bf16, D, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "pre-pass launch failed: %s", cudaGetErrorString(e));
   }
   if (!(phases & RBF_B200_PHASE_MAIN)) return RBF_B200_OK;
 
@@ -210,30 +207,20 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
 
   const int n_pad = rbf::padded_rows(N);
   const float c = sm_scale * rbf::kLog2e;
-  rbf::RowReduceArgs r{};
-  r.B = B; r.H = H; r.N = N; r.n_pad = n_pad;
-  // key norms
-  r.x = k; r.y = nullptr; r.out = ws.ksq; set_strides(r.xs, k_strides); set_strides(r.ys, k_strides);
-  r.scale = c; r.pad_value = INFINITY; r.status_to_clear = ws.status;
   cudaError_t e = cudaSuccess;
   if (phases & RBF_B200_PHASE_PREPASS) {
-  e = rbf::launch_row_reduce(r, bf16, D, stream);
-  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "key-norm pre-pass launch failed: %s", cudaGetErrorString(e));
-  r.status_to_clear = nullptr;
-  if (softmax) {
-    // delta = rowsum(O * dO)
-    r.x = out; r.y = dout; r.out = ws.delta; set_strides(r.xs, o_strides); set_strides(r.ys, do_strides);
-    r.pad_value = 0.f;
-    e = rbf::launch_row_reduce(r, bf16, D, stream);
-    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "delta pre-pass launch failed: %s", cudaGetErrorString(e));
-  } else {
-    // query norms play the role of the row statistic; delta is identically zero
-    r.x = q; r.y = nullptr; r.out = ws.row_bias; set_strides(r.xs, q_strides); r.pad_value = INFINITY;
-    e = rbf::launch_row_reduce(r, bf16, D, stream);
-    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "query-norm pre-pass launch failed: %s", cudaGetErrorString(e));
-    e = cudaMemsetAsync(ws.delta, 0, static_cast<size_t>(B) * H * n_pad * sizeof(float), stream);
-    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "delta clear failed: %s", cudaGetErrorString(e));
-  }
+    rbf::RowStatsArgs r{};
+    r.B = B; r.H = H; r.N = N; r.n_pad = n_pad; r.scale = c; r.status_to_clear = ws.status;
+    r.k = k; r.ksq_out = ws.ksq; set_strides(r.ks, k_strides);
+    r.delta_out = ws.delta;                     // written as zeros when there is no O (non-softmax variant)
+    if (softmax) {
+      r.o = out; r.dout = dout; set_strides(r.os, o_strides); set_strides(r.dos, do_strides);
+      r.lse = lse; r.lse_pad_out = ws.row_bias;
+    } else {
+      r.q = q; r.qsq_out = ws.row_bias; r.qsq_pad = INFINITY; set_strides(r.qs, q_strides);
+    }
+    e = rbf::launch_row_stats(r, bf16, D, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "pre-pass launch failed: %s", cudaGetErrorString(e));
   }
 
   if (use_fused_backward(D, softmax)) {
@@ -243,7 +230,7 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     const int tr = rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, rbf::kTile);
     if (tr != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the dQ accumulator (code %d)", tr);
     f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
-    f.ksq = ws.ksq; f.lse = lse; f.delta = ws.delta; f.status = ws.status;
+    f.ksq = ws.ksq; f.lse_pad = ws.row_bias; f.delta = ws.delta; f.status = ws.status;
     f.B = B; f.H = H; f.N = N; f.n_pad = n_pad; f.causal = causal ? 1 : 0;
     f.scale2 = 2.f * c; f.grad_scale = 2.f * sm_scale;
     e = rbf::launch_bwd_fused(f, bf16, stream);
@@ -252,8 +239,8 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
   }
 
   a.ksq = ws.ksq;
-  a.row_bias = softmax ? lse : ws.row_bias;
-  a.row_bias_pitch = softmax ? N : n_pad;
+  a.row_bias = ws.row_bias;
+  a.row_bias_pitch = n_pad;
   a.delta = ws.delta;
   a.status = ws.status;
   a.B = B; a.H = H; a.N = N; a.n_pad = n_pad; a.causal = causal ? 1 : 0;

@@ -9,17 +9,25 @@
 
 namespace rbf {
 
-struct RowReduceArgs {
-  const void* x;
-  const void* y;          // nullptr: scaled squared norm of x rows; else dot(x, y) per row
-  float* out;             // (B*H, n_pad)
+// One pre-pass launch: any subset of the four row statistics (null input pointer = skip).
+struct RowStatsArgs {
+  const void* k;          // -> ksq_out = scale * |k|^2, +inf on padding rows
+  const void* q;          // -> qsq_out = scale * |q|^2, qsq_pad on padding rows
+  const void* o;          // with dout -> delta_out = rowsum(o * dout), 0 on padding rows
+  const void* dout;
+  const float* lse;       // (B, H, N) -> lse_pad_out re-pitched to n_pad, +inf on padding rows
+  float* ksq_out;
+  float* qsq_out;
+  float* delta_out;
+  float* lse_pad_out;
+  int64_t ks[3], qs[3], os[3], dos[3];   // element strides of dims b, h, n
   int B, H, N, n_pad;
-  int64_t xs[3], ys[3];   // element strides of dims b, h, n
   float scale;
-  float pad_value;
+  float qsq_pad;
+  int iters;              // set by the launcher
   DeviceStatus* status_to_clear;  // optional: zeroed by the first thread of the grid
 };
-cudaError_t launch_row_reduce(const RowReduceArgs& a, bool bf16, int D, cudaStream_t stream);
+cudaError_t launch_row_stats(const RowStatsArgs& a, bool bf16, int D, cudaStream_t stream);
 
 // Forward pass. Tensor maps use a 64-element x 128-row box with the 128-byte swizzle.
 struct FwdArgs {
@@ -38,8 +46,8 @@ cudaError_t launch_fwd(const FwdArgs& a, bool bf16, int D, bool softmax, cudaStr
 struct BwdArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dq, tm_dk, tm_dv;
   const float* ksq;       // (B*H, n_pad)
-  const float* row_bias;  // (B*H, n_pad): softmax: L (base-2 LSE, +inf on padding); non-softmax: c*|q|^2
-  int row_bias_pitch;     // row pitch of row_bias: N for L, n_pad for the query norms
+  const float* row_bias;  // (B*H, n_pad): softmax: L (base-2 LSE); non-softmax: c*|q|^2; +inf on padding rows
+  int row_bias_pitch;     // row pitch of row_bias (n_pad)
   const float* delta;     // (B*H, n_pad): rowsum(O*dO); all zero for the non-softmax variant
   DeviceStatus* status;
   int B, H, N, n_pad;
@@ -58,7 +66,7 @@ struct BwdFusedArgs {
   void* dq;               // final dQ in the operand type
   int64_t dq_strides[3];
   const float* ksq;       // (B*H, n_pad)
-  const float* lse;       // (B, H, N)
+  const float* lse_pad;   // (B*H, n_pad): base-2 LSE, +inf on padding rows
   const float* delta;     // (B*H, n_pad)
   DeviceStatus* status;
   int B, H, N, n_pad;

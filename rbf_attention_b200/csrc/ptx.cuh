@@ -46,6 +46,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival per warp: arrivals are atomic updates of one shared-memory word and serialise, so per-thread
+// arrivals of a few hundred threads cost thousands of cycles per phase. __syncwarp orders every lane's earlier
+// writes before the elected lane's release-arrive; initialise such barriers with the number of WARPS.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -95,6 +102,21 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* t
       "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// 1-D bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// fp32 reduce-add of a shared-memory tile into global memory through a tensor map.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* tmap, const void* smem_src, int c0, int c1,
+                                                  int c2, int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)),
+      "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* tmap, const void* smem_src, int c0, int c1,
                                              int c2, int c3) {
   asm volatile(
@@ -123,6 +145,15 @@ __device__ __forceinline__ void tmem_relinquish() {
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Warpgroup-wide register re-allocation (all four warps of an aligned warpgroup execute it).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 __device__ __forceinline__ void tc_fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -158,6 +189,22 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
   d |= 1ull << 46;  // descriptor version for sm_100
   d |= 2ull << 61;  // SWIZZLE_128B
   return d;
+}
+
+// The same descriptor split into its two 32-bit words: the high word (SBO, version, swizzle) is loop invariant and
+// the start address lives in the low 14 bits of the low word, so stepping through a tile is one 32-bit add
+// per MMA on the issuing thread instead of rebuilding the descriptor.
+struct SmemDesc {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ SmemDesc make_sdesc_parts(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  SmemDesc d;
+  d.lo = ((smem_addr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+  d.hi = ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
+  return d;
+}
+__device__ __forceinline__ uint64_t sdesc_at(const SmemDesc& d, uint32_t byte_offset) {
+  return (static_cast<uint64_t>(d.hi) << 32) | static_cast<uint64_t>(d.lo + (byte_offset >> 4));
 }
 
 // D[tmem] (+)= A[smem] * B[smem]

@@ -130,19 +130,23 @@ rbf_bwd_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_constant_
   }
   const int diag = p.causal ? at : -1;   // streamed tile index that straddles the diagonal
 
+  // A wait that ran out in an earlier CTA of this launch ends the whole launch quickly: later CTAs leave at once.
+  if (tid == 0) *abort_flag = (*reinterpret_cast<volatile unsigned int*>(&p.status->code) != 0u) ? 1 : 0;
+  __syncthreads();
+  if (*abort_flag) return;
+
   if (tid == 0) {
-    *abort_flag = 0;
     mbar_init(a_full, 1);
     for (int s = 0; s < C::kB1Stages; ++s) { mbar_init(&b1_full[s], 1); mbar_init(&b1_empty[s], 1); }
     for (int s = 0; s < C::kB2Stages; ++s) { mbar_init(&b2_full[s], 1); mbar_init(&b2_empty[s], 1); }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
     mbar_init(dp_full, 1);
-    mbar_init(&p_full[0], kTile);
-    mbar_init(&p_full[1], kTile);
-    mbar_init(ds_full, kTile);
+    mbar_init(&p_full[0], 4);                 // one arrival per compute warp
+    mbar_init(&p_full[1], 4);
+    mbar_init(ds_full, 4);
     mbar_init(acc_done, 1);
-    mbar_init(grp_sync, kTile);
+    mbar_init(grp_sync, 4);
     fence_mbar_init();
   }
   if (warp == kMmaWarp) {
@@ -290,7 +294,7 @@ rbf_bwd_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_constant_
     bool ok = true;
     uint32_t grp_phase = 0;
     auto group_sync = [&]() -> bool {
-      mbar_arrive(grp_sync);
+      mbar_arrive_warp(grp_sync);
       const bool done = mbar_wait(grp_sync, grp_phase & 1, abort_flag, p.status, kSiteGroup);
       ++grp_phase;
       return done;
@@ -353,7 +357,7 @@ rbf_bwd_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_constant_
         }
         tmem_st_wait();
         tc_fence_before_sync();
-        mbar_arrive(&p_full[sb]);
+        mbar_arrive_warp(&p_full[sb]);
       }
 
       ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull);
@@ -388,7 +392,7 @@ rbf_bwd_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_constant_
       }
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(ds_full);
+      mbar_arrive_warp(ds_full);
       if (n + 1 < cnt) {
         float* nbuf = s_vec + ((n + 1) & 1) * 2 * kTile;
         nbuf[r] = cs_next;

@@ -12,8 +12,10 @@
 // kernel converts it to the output type (times 2g) afterwards. dK gets the norm-gradient term in the
 // epilogue: dK = 2g (acc - rowsum(dS^T)[key] * k).
 //
-// Roles: warps 0-3 / 4-7 compute groups (thread = key row; group g owns query columns [64g, 64g+64) of the tile),
-// warps 8-11 drain dQ_partial (thread = query row), warp 12 TMA producer, warp 13 MMA issuer.
+// Roles: warp 0 MMA issuer, warp 1 TMA producer (the lowest warp ids: the warp scheduler favours older warps, and a
+// starved issuer idles the tensor pipe), warps 4-19 compute (thread = key row; group g owns query columns
+// [32g, 32g+32) of the tile), warps 20-23 drain dQ_partial (thread = query row). The compute warpgroups take
+// registers from the others (setmaxnreg) so that four warps per scheduler hide the MUFU and TMEM latencies.
 // TMEM columns: S^T [0,128), dP^T [128,256), dV [256,320), dK [320,384), dQ_partial x2 [384,512).
 #include "common.cuh"
 #include "launch.h"
@@ -22,12 +24,32 @@ namespace rbf {
 
 namespace bwdf {
 
+#ifdef RBF_TRACE
+// Bring-up aid (not compiled into the product): clock64 stamps of one CTA's roles per step.
+__device__ long long g_trace[4 * 64 * 16];
+#define RBF_TRACE_EVENT(role, step, ev)                                                              \
+  do {                                                                                               \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (step) < 64) g_trace[((role)*64 + (step)) * 16 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define RBF_TRACE_EVENT(role, step, ev) \
+  do {                                  \
+  } while (0)
+#endif
+
 static constexpr int D = 64;
-static constexpr int kThreads = 448;
-static constexpr int kNumCompute = 256;
-static constexpr int kDrainWarp0 = 8;
-static constexpr int kLoadWarp = 12;
-static constexpr int kMmaWarp = 13;
+static constexpr int kThreads = 768;
+static constexpr int kNumComputeWarps = 16;
+static constexpr int kMmaWarp = 0;
+static constexpr int kLoadWarp = 1;
+static constexpr int kComputeWarp0 = 4;
+static constexpr int kDrainWarp0 = 20;
+// Register budget: the launch allocates 80 per thread (768 threads); setmaxnreg may only redistribute that
+// total: 512 * 96 + 256 * 40 = 59392 <= 768 * 80 = 61440. (An increase beyond what the decreases released blocks
+// forever, with no timeout.)
+static constexpr int kComputeRegs = 96;
+static constexpr int kOtherRegs = 40;
+static_assert(512 * kComputeRegs + 256 * kOtherRegs <= 768 * 80, "setmaxnreg budget");
 
 static constexpr int kTileBytes = kTile * D * 2;    // 16 KB: one 128 x 64 16-bit tile
 static constexpr int kQStages = 3;
@@ -42,10 +64,10 @@ struct Smem {
   static constexpr int kDo = kQ + kQStages * kTileBytes;
   static constexpr int kDs = kDo + kDoStages * kTileBytes;
   static constexpr int kDqStage = kDs + kDsBytes;
-  static constexpr int kVec = kDqStage + kDqStageBytes;   // [2 buffers][L | delta][128] floats
-  static constexpr int kRowsum = kVec + 2 * 2 * kTile * 4; // [128] floats: group 1's partial row sums
-  static constexpr int kBars = kRowsum + kTile * 4;
-  static constexpr int kNumBars = 1 + 2 * kQStages + 2 * kDoStages + 1 + 1 + 1 + 1 + 2 + 2 + 1 + 1 + 1;
+  static constexpr int kVec = kDqStage + kDqStageBytes;        // [kQStages][L | delta][128] floats
+  static constexpr int kRowsum = kVec + kQStages * 2 * kTile * 4;  // [4 groups][128] floats: partial row sums
+  static constexpr int kBars = kRowsum + 4 * kTile * 4;
+  static constexpr int kNumBars = 1 + 2 * kQStages + 2 * kDoStages + 1 + 1 + 1 + 1 + 2 + 2 + 1 + 1 + 1 + 1;
   static constexpr int kMisc = kBars + kNumBars * 8;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;
@@ -60,7 +82,7 @@ enum Site : uint32_t {
 
 struct Params {
   const float* ksq;      // (B*H, n_pad), +inf on padding rows
-  const float* lse;      // (B*H, N)
+  const float* lse_pad;  // (B*H, n_pad), +inf on padding rows
   const float* delta;    // (B*H, n_pad), zero padded
   DeviceStatus* status;
   int H, N, n_pad, causal;
@@ -98,6 +120,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   uint64_t* acc_done = dq_drained + 2;
   uint64_t* grp_sync = acc_done + 1;     // compute groups (256 threads)
   uint64_t* drain_sync = grp_sync + 1;   // drain group (128 threads)
+  uint64_t* dbg_bar = drain_sync + 1;    // bring-up only
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + Smem::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 4);
 
@@ -112,22 +135,27 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   const int first = p.causal ? kt : 0;             // first query tile that sees these keys
   const int cnt = n_tiles - first;
 
+  // A wait that ran out in an earlier CTA of this launch ends the whole launch quickly: later CTAs leave at once.
+  if (tid == 0) *abort_flag = (*reinterpret_cast<volatile unsigned int*>(&p.status->code) != 0u) ? 1 : 0;
+  __syncthreads();
+  if (*abort_flag) return;
+
   if (tid == 0) {
-    *abort_flag = 0;
     mbar_init(kv_full, 1);
     for (int s = 0; s < kQStages; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     for (int s = 0; s < kDoStages; ++s) { mbar_init(&do_full[s], 1); mbar_init(&do_empty[s], 1); }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_full, kNumCompute);
-    mbar_init(ds_full, kNumCompute);
+    mbar_init(p_full, kNumComputeWarps);      // one arrival per warp
+    mbar_init(ds_full, kNumComputeWarps);
     mbar_init(&dq_full[0], 1);
     mbar_init(&dq_full[1], 1);
-    mbar_init(&dq_drained[0], kTile);
-    mbar_init(&dq_drained[1], kTile);
+    mbar_init(&dq_drained[0], 4);
+    mbar_init(&dq_drained[1], 4);
     mbar_init(acc_done, 1);
-    mbar_init(grp_sync, kNumCompute);
-    mbar_init(drain_sync, kTile);
+    mbar_init(grp_sync, kNumComputeWarps);
+    mbar_init(drain_sync, 4);
+    mbar_init(dbg_bar, 1);
     fence_mbar_init();
   }
   if (warp == kMmaWarp) {
@@ -138,8 +166,14 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_base_s;
-
-  if (warp == kLoadWarp) {
+  // Register re-allocation is issued at the top of each role's branch (whole warpgroups take the same branch
+  // class: warps 0-3 issuer / producer / idle, 4-19 compute, 20-23 drain).
+  if (warp < kComputeWarp0) {
+    setmaxnreg_dec<kOtherRegs>();
+  }
+  if (warp > kLoadWarp && warp < kComputeWarp0) {
+    // idle warps of the first warpgroup
+  } else if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
@@ -154,10 +188,17 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         const int sq = n % kQStages, sd = n % kDoStages;
         if (n >= kQStages && !mbar_wait(&q_empty[sq], ((n / kQStages) - 1) & 1, abort_flag, p.status, kSiteQEmpty))
           break;
-        mbar_arrive_expect_tx(&q_full[sq], kTileBytes);
+        RBF_TRACE_EVENT(1, n, 4);
+        mbar_arrive_expect_tx(&q_full[sq], kTileBytes + 2 * kTile * 4);
         tma_load_4d(s_q + sq * kTileBytes, &tm_q, &q_full[sq], 0, row0, h, b);
+        // this query tile's L and delta ride on the same barrier (row pitch n_pad keeps them 16-byte aligned)
+        bulk_load_1d(s_vec + sq * 2 * kTile, p.lse_pad + static_cast<int64_t>(bh) * p.n_pad + row0, kTile * 4,
+                     &q_full[sq]);
+        bulk_load_1d(s_vec + sq * 2 * kTile + kTile, p.delta + static_cast<int64_t>(bh) * p.n_pad + row0, kTile * 4,
+                     &q_full[sq]);
         if (n >= kDoStages && !mbar_wait(&do_empty[sd], ((n / kDoStages) - 1) & 1, abort_flag, p.status, kSiteDoEmpty))
           break;
+        RBF_TRACE_EVENT(1, n, 5);
         mbar_arrive_expect_tx(&do_full[sd], kTileBytes);
         tma_load_4d(s_do + sd * kTileBytes, &tm_do, &do_full[sd], 0, row0, h, b);
       }
@@ -168,21 +209,30 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       constexpr uint32_t idesc_s = make_idesc(kTile, kTile, kBf16, false, false);  // keys x queries, both K-major
       constexpr uint32_t idesc_acc = make_idesc(kTile, D, kBf16, false, true);     // A from TMEM, B N-major
       constexpr uint32_t idesc_dq = make_idesc(kTile, D, kBf16, true, true);       // A M-major (dS^T tile), B N-major
-      const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v), q_addr = smem_u32(s_q), do_addr = smem_u32(s_do),
-                     ds_addr = smem_u32(s_ds);
-      auto issue_kmajor = [&](uint32_t dst, uint32_t a_addr, uint32_t b_addr) {
+      // descriptors: K-major view (rows = M/N index) and N-/M-major view (rows = reduction index) of each tile
+      const SmemDesc k_kmaj = make_sdesc_parts(smem_u32(s_k), 16, 1024);
+      const SmemDesc v_kmaj = make_sdesc_parts(smem_u32(s_v), 16, 1024);
+      const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
+      const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);
+      const SmemDesc q_kmaj0 = make_sdesc_parts(smem_u32(s_q), 16, 1024);
+      const SmemDesc do_kmaj0 = make_sdesc_parts(smem_u32(s_do), 16, 1024);
+      const SmemDesc q_nmaj0 = make_sdesc_parts(smem_u32(s_q), kTile * 128, 1024);
+      const SmemDesc do_nmaj0 = make_sdesc_parts(smem_u32(s_do), kTile * 128, 1024);
+      auto stage_of = [](SmemDesc d, int stage) {
+        d.lo += static_cast<uint32_t>(stage) * (kTileBytes >> 4);
+        return d;
+      };
+      auto issue_kmajor = [&](uint32_t dst, const SmemDesc& a_desc, const SmemDesc& b_desc) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss(dst, make_sdesc_sw128(a_addr + kk * 32, 16, 1024), make_sdesc_sw128(b_addr + kk * 32, 16, 1024),
-                  idesc_s, kk > 0);
+          umma_ss(dst, sdesc_at(a_desc, kk * 32), sdesc_at(b_desc, kk * 32), idesc_s, kk > 0);
       };
-      // A: 16-bit pairs in TMEM; group g's 64 queries live at columns [64g, 64g+32) of the region
-      auto issue_acc = [&](uint32_t dst, uint32_t a_region, uint32_t b_addr, bool accumulate) {
+      // A: 16-bit pairs in TMEM; group g's 32 queries live at columns [32g, 32g+16) of the region
+      auto issue_acc = [&](uint32_t dst, uint32_t a_region, const SmemDesc& b_desc, uint32_t accumulate) {
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
-          const uint32_t a_col = (kk >> 2) * 64 + (kk & 3) * 8;
-          umma_ts(dst, a_region + a_col, make_sdesc_sw128(b_addr + kk * 2048, kTile * 128, 1024), idesc_acc,
-                  (accumulate || kk > 0) ? 1u : 0u);
+          const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
+          umma_ts(dst, a_region + a_col, sdesc_at(b_desc, kk * 2048), idesc_acc, kk > 0 ? 1u : accumulate);
         }
       };
       auto wait_q = [&](int n) {
@@ -192,80 +242,117 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         return mbar_wait(&do_full[n % kDoStages], (n / kDoStages) & 1, abort_flag, p.status, kSiteDoFull);
       };
 
+#ifdef RBF_SERIALIZE_MMA
+      uint32_t dbg_phase = 0;
+#define RBF_DBG_DRAIN()                                                        \
+  do {                                                                         \
+    umma_commit(dbg_bar);                                                      \
+    mbar_wait(dbg_bar, dbg_phase & 1, abort_flag, p.status, 99);               \
+    ++dbg_phase;                                                               \
+  } while (0)
+#else
+#define RBF_DBG_DRAIN() \
+  do {                  \
+  } while (0)
+#endif
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kSiteKV);
       if (ok) ok = wait_q(0);
       if (ok) {
         tc_fence_after_sync();
-        issue_kmajor(tmem + kColS, k_addr, q_addr);
+        issue_kmajor(tmem + kColS, k_kmaj, q_kmaj0);
         umma_commit(s_full);
         ok = wait_do(0);
       }
       if (ok) {
         tc_fence_after_sync();
-        issue_kmajor(tmem + kColDP, v_addr, do_addr);
+        issue_kmajor(tmem + kColDP, v_kmaj, do_kmaj0);
         umma_commit(dp_full);
       }
       for (int n = 0; n < cnt && ok; ++n) {
-        const uint32_t q_n = q_addr + (n % kQStages) * kTileBytes;
-        const uint32_t do_n = do_addr + (n % kDoStages) * kTileBytes;
+        const SmemDesc q_n = stage_of(q_nmaj0, n % kQStages);
+        const SmemDesc do_n = stage_of(do_nmaj0, n % kDoStages);
+        const uint32_t acc_flag = n > 0 ? 1u : 0u;
         // dV += P^T dO
+        RBF_TRACE_EVENT(0, n, 0);
         ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
         if (!ok) break;
+        RBF_TRACE_EVENT(0, n, 1);
         tc_fence_after_sync();
-        issue_acc(tmem + kColDV, tmem + kColS, do_n, n > 0);
+        issue_acc(tmem + kColDV, tmem + kColS, do_n, acc_flag);
+        RBF_DBG_DRAIN();
+        RBF_TRACE_EVENT(0, n, 5);
         // next S^T (S^T columns are free once dV has consumed P^T; the tensor pipe runs in issue order)
         if (n + 1 < cnt) {
+          RBF_TRACE_EVENT(0, n, 9);
           ok = wait_q(n + 1);
           if (!ok) break;
+          RBF_TRACE_EVENT(0, n, 10);
           tc_fence_after_sync();
-          issue_kmajor(tmem + kColS, k_addr, q_addr + ((n + 1) % kQStages) * kTileBytes);
+          issue_kmajor(tmem + kColS, k_kmaj, stage_of(q_kmaj0, (n + 1) % kQStages));
           umma_commit(s_full);
         }
+        RBF_DBG_DRAIN();
+        RBF_TRACE_EVENT(0, n, 6);
         // dK += dS^T Q
+        RBF_TRACE_EVENT(0, n, 2);
         ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
         if (!ok) break;
+        RBF_TRACE_EVENT(0, n, 3);
         tc_fence_after_sync();
-        issue_acc(tmem + kColDK, tmem + kColDP, q_n, n > 0);
+        issue_acc(tmem + kColDK, tmem + kColDP, q_n, acc_flag);
         umma_commit(&q_empty[n % kQStages]);      // Q(n) and dO(n) have no reader left once these complete
         umma_commit(&do_empty[n % kDoStages]);
+        RBF_DBG_DRAIN();
+        RBF_TRACE_EVENT(0, n, 7);
         // next dP^T
         if (n + 1 < cnt) {
+          RBF_TRACE_EVENT(0, n, 11);
           ok = wait_do(n + 1);
           if (!ok) break;
+          RBF_TRACE_EVENT(0, n, 12);
           tc_fence_after_sync();
-          issue_kmajor(tmem + kColDP, v_addr, do_addr + ((n + 1) % kDoStages) * kTileBytes);
+          issue_kmajor(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, (n + 1) % kDoStages));
           umma_commit(dp_full);
         }
+        RBF_DBG_DRAIN();
+        RBF_TRACE_EVENT(0, n, 8);
         // dQ_partial = dS K : A = dS^T tile read M-major (rows = keys = reduction index), B = K read N-major
+        RBF_TRACE_EVENT(0, n, 13);
         if (n >= 2) {
           ok = mbar_wait(&dq_drained[n & 1], ((n - 2) >> 1) & 1, abort_flag, p.status, kSiteDQDrained);
           if (!ok) break;
           tc_fence_after_sync();
         }
+        RBF_TRACE_EVENT(0, n, 14);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
-          umma_ss(tmem + kColDQ + (n & 1) * D, make_sdesc_sw128(ds_addr + kk * 2048, kTile * 128, 1024),
-                  make_sdesc_sw128(k_addr + kk * 2048, kTile * 128, 1024), idesc_dq, kk > 0);
+          umma_ss(tmem + kColDQ + (n & 1) * D, sdesc_at(ds_mmaj, kk * 2048), sdesc_at(k_nmaj, kk * 2048), idesc_dq,
+                  kk > 0);
         }
         umma_commit(&dq_full[n & 1]);
+        RBF_DBG_DRAIN();
+        RBF_TRACE_EVENT(0, n, 4);
       }
       if (ok) umma_commit(acc_done);
     }
   } else if (warp >= kDrainWarp0) {
     // ------------------------------------------------------------------ dQ_partial drain (thread = query row)
+    setmaxnreg_dec<kOtherRegs>();
     const int r = tid - kDrainWarp0 * 32;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t phase = 0;
     bool ok = true;
     auto drain_group_sync = [&]() -> bool {
-      mbar_arrive(drain_sync);
+      mbar_arrive_warp(drain_sync);
       const bool done = mbar_wait(drain_sync, phase & 1, abort_flag, p.status, kSiteDrainGroup);
       ++phase;
       return done;
     };
     for (int n = 0; n < cnt; ++n) {
+      if (r == 0) RBF_TRACE_EVENT(1, n, 0);
       ok = mbar_wait(&dq_full[n & 1], (n >> 1) & 1, abort_flag, p.status, kSiteDQFull);
       if (!ok) break;
+      if (r == 0) RBF_TRACE_EVENT(1, n, 1);
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -278,166 +365,170 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
               make_uint4(v[g * 4 + 0], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
       }
       tc_fence_before_sync();
-      mbar_arrive(&dq_drained[n & 1]);
+      mbar_arrive_warp(&dq_drained[n & 1]);
       fence_proxy_async_smem();
       ok = drain_group_sync();
       if (!ok) break;
       if (r == 0) {
         const int row0 = (first + n) * kTile;
-        asm volatile(
-            "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-            ::"l"(reinterpret_cast<uint64_t>(&tm_dq_acc)), "r"(smem_u32(s_dq)), "r"(0), "r"(row0), "r"(h), "r"(b)
-            : "memory");
-        asm volatile(
-            "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-            ::"l"(reinterpret_cast<uint64_t>(&tm_dq_acc)), "r"(smem_u32(s_dq + kTile * 128)), "r"(32), "r"(row0),
-            "r"(h), "r"(b)
-            : "memory");
+#ifndef RBF_SKIP_DQ_REDUCE
+        tma_reduce_add_4d(&tm_dq_acc, s_dq, 0, row0, h, b);
+        tma_reduce_add_4d(&tm_dq_acc, s_dq + kTile * 128, 32, row0, h, b);
+#endif
         tma_store_commit();
         tma_store_wait_read();     // the staging tile may be overwritten once the bulk engine has read it
       }
       ok = drain_group_sync();
       if (!ok) break;
+      if (r == 0) RBF_TRACE_EVENT(1, n, 2);
     }
     if (r == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ compute groups (thread = key row)
-    const int g = warp >> 2;                               // column half of the query tile
+    setmaxnreg_inc<kComputeRegs>();
+    const int g = (warp - kComputeWarp0) >> 2;             // 32-column slice of the query tile
     const int r = tid & (kTile - 1);
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int64_t bh64 = bh;
-    const float neg_ksq = -p.ksq[bh64 * p.n_pad + k_row0 + r];
+    const float neg_ksq = -p.ksq[static_cast<int64_t>(bh) * p.n_pad + k_row0 + r];
     float ds_rowsum = 0.f;
     bool ok = true;
-    uint32_t grp_phase = 0;
-    auto group_sync = [&]() -> bool {
-      mbar_arrive(grp_sync);
-      const bool done = mbar_wait(grp_sync, grp_phase & 1, abort_flag, p.status, kSiteGroup);
-      ++grp_phase;
-      return done;
-    };
-    // per query tile: L (threads 0-127) and delta (threads 128-255), double buffered
-    auto fetch_vec = [&](int n) -> float {
-      const int idx = (first + n) * kTile + r;
-      if (g == 0) return (idx < p.N) ? p.lse[bh64 * p.N + idx] : INFINITY;
-      return p.delta[bh64 * p.n_pad + idx];
-    };
-    s_vec[g * kTile + r] = fetch_vec(0);
 
     for (int n = 0; n < cnt; ++n) {
-      float vec_next = 0.f;
-      if (n + 1 < cnt) vec_next = fetch_vec(n + 1);
-      ok = group_sync() && mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
+      const int sq = n % kQStages;
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 0);
+      ok = mbar_wait(&q_full[sq], (n / kQStages) & 1, abort_flag, p.status, kSiteQFull) &&
+           mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
       if (!ok) break;
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 2);
       tc_fence_after_sync();
-      const float* vbuf = s_vec + (n & 1) * 2 * kTile;
-      const float4* l4 = reinterpret_cast<const float4*>(vbuf + g * 64);
-      const float4* d4 = reinterpret_cast<const float4*>(vbuf + kTile + g * 64);
+      const float4* l4 = reinterpret_cast<const float4*>(s_vec + sq * 2 * kTile + g * 32);
+      const float4* d4 = reinterpret_cast<const float4*>(s_vec + sq * 2 * kTile + kTile + g * 32);
 
-      float pr[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      float pr[32];
+      {
         uint32_t raw[32];
-        tmem_ld_x32(tmem + kColS + lane_sel + g * 64 + c * 32, raw);
+        tmem_ld_x32(tmem + kColS + lane_sel + g * 32, raw);
         tmem_ld_wait();
+        if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 6);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float4 lv = l4[c * 8 + i];
-          pr[c * 32 + i * 4 + 0] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 0]), p.scale2, neg_ksq) - lv.x);
-          pr[c * 32 + i * 4 + 1] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 1]), p.scale2, neg_ksq) - lv.y);
-          pr[c * 32 + i * 4 + 2] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 2]), p.scale2, neg_ksq) - lv.z);
-          pr[c * 32 + i * 4 + 3] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 3]), p.scale2, neg_ksq) - lv.w);
+#ifdef RBF_NO_VEC_LDS
+          const float4 lv = make_float4(neg_ksq, neg_ksq, neg_ksq, neg_ksq);
+#else
+          const float4 lv = l4[i];
+#endif
+          pr[i * 4 + 0] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 0]), p.scale2, neg_ksq) - lv.x);
+          pr[i * 4 + 1] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 1]), p.scale2, neg_ksq) - lv.y);
+          pr[i * 4 + 2] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 2]), p.scale2, neg_ksq) - lv.z);
+          pr[i * 4 + 3] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 3]), p.scale2, neg_ksq) - lv.w);
         }
       }
       if (p.causal && n == 0) {
-        // diagonal tile: query column (64g + c) sees key row r iff column >= row
+        // diagonal tile: query column (32g + c) sees key row r iff column >= row
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
-          if (g * 64 + c < r) pr[c] = 0.f;
+        for (int c = 0; c < 32; ++c)
+          if (g * 32 + c < r) pr[c] = 0.f;
       }
       {
-        uint32_t packed[32];
+        uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) packed[i] = pack2<kBf16>(pr[2 * i], pr[2 * i + 1]);
-        tmem_st_x32(tmem + kColS + lane_sel + g * 64, packed);
+        for (int i = 0; i < 16; ++i) packed[i] = pack2<kBf16>(pr[2 * i], pr[2 * i + 1]);
+        if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 7);
+        tmem_st_x16(tmem + kColS + lane_sel + g * 32, packed);
         tmem_st_wait();
+        if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 8);
         tc_fence_before_sync();
-        mbar_arrive(p_full);
+        mbar_arrive_warp(p_full);
       }
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 3);
 
       ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull);
       // the dS^T shared tile is free once the previous dQ_partial MMA has completed
       if (ok && n > 0) ok = mbar_wait(&dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, abort_flag, p.status, kSiteDsFree);
       if (!ok) break;
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 4);
       tc_fence_after_sync();
-      uint32_t ds_packed[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      uint32_t ds_packed[16];
+      {
         uint32_t raw[32];
-        tmem_ld_x32(tmem + kColDP + lane_sel + g * 64 + c * 32, raw);
+        tmem_ld_x32(tmem + kColDP + lane_sel + g * 32, raw);
         tmem_ld_wait();
+        if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 9);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float4 dl = d4[c * 8 + i];
-          const float d0 = pr[c * 32 + i * 4 + 0] * (__uint_as_float(raw[i * 4 + 0]) - dl.x);
-          const float d1 = pr[c * 32 + i * 4 + 1] * (__uint_as_float(raw[i * 4 + 1]) - dl.y);
-          const float d2 = pr[c * 32 + i * 4 + 2] * (__uint_as_float(raw[i * 4 + 2]) - dl.z);
-          const float d3 = pr[c * 32 + i * 4 + 3] * (__uint_as_float(raw[i * 4 + 3]) - dl.w);
+#ifdef RBF_NO_VEC_LDS
+          const float4 dl = make_float4(neg_ksq, neg_ksq, neg_ksq, neg_ksq);
+#else
+          const float4 dl = d4[i];
+#endif
+          const float d0 = pr[i * 4 + 0] * (__uint_as_float(raw[i * 4 + 0]) - dl.x);
+          const float d1 = pr[i * 4 + 1] * (__uint_as_float(raw[i * 4 + 1]) - dl.y);
+          const float d2 = pr[i * 4 + 2] * (__uint_as_float(raw[i * 4 + 2]) - dl.z);
+          const float d3 = pr[i * 4 + 3] * (__uint_as_float(raw[i * 4 + 3]) - dl.w);
           ds_rowsum += (d0 + d1) + (d2 + d3);
-          ds_packed[c * 16 + i * 2 + 0] = pack2<kBf16>(d0, d1);
-          ds_packed[c * 16 + i * 2 + 1] = pack2<kBf16>(d2, d3);
+          ds_packed[i * 2 + 0] = pack2<kBf16>(d0, d1);
+          ds_packed[i * 2 + 1] = pack2<kBf16>(d2, d3);
         }
       }
-      tmem_st_x32(tmem + kColDP + lane_sel + g * 64, ds_packed);
-      // the same values to shared memory as row r of the [key][query] tile, box g (queries 64g .. 64g+63)
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 10);
+      tmem_st_x16(tmem + kColDP + lane_sel + g * 32, ds_packed);
+      // the same values to shared memory: row r of the [key][query] tile, box g/2, 16-byte chunks 4(g%2) .. +3
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch)
-        *reinterpret_cast<uint4*>(s_ds + g * (kTile * 128) + sw128_offset(r, ch)) =
+      for (int ch = 0; ch < 4; ++ch)
+        *reinterpret_cast<uint4*>(s_ds + (g >> 1) * (kTile * 128) + sw128_offset(r, (g & 1) * 4 + ch)) =
             make_uint4(ds_packed[ch * 4 + 0], ds_packed[ch * 4 + 1], ds_packed[ch * 4 + 2], ds_packed[ch * 4 + 3]);
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 11);
       tmem_st_wait();
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 12);
       fence_proxy_async_smem();
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 13);
       tc_fence_before_sync();
-      mbar_arrive(ds_full);
-      if (n + 1 < cnt) s_vec[((n + 1) & 1) * 2 * kTile + g * kTile + r] = vec_next;
+      mbar_arrive_warp(ds_full);
+      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 5);
     }
 
+    uint32_t grp_phase = 0;
+    auto group_sync = [&]() -> bool {
+      mbar_arrive_warp(grp_sync);
+      const bool done = mbar_wait(grp_sync, grp_phase & 1, abort_flag, p.status, kSiteGroup);
+      ++grp_phase;
+      return done;
+    };
     if (ok) ok = mbar_wait(acc_done, 0, abort_flag, p.status, kSiteAccDone);
     if (ok) {
       tc_fence_after_sync();
-      // group 1 publishes its half of rowsum(dS^T); group 0 finishes dK, group 1 stores dV
-      if (g == 1) s_rowsum[r] = ds_rowsum;
+      s_rowsum[g * kTile + r] = ds_rowsum;      // every group holds a quarter of rowsum(dS^T)
       ok = group_sync();
     }
     if (ok) {
-      uint8_t* stage = s_q + g * kTileBytes;   // the Q ring is dead: every MMA has completed
-      const float w = (g == 0) ? (ds_rowsum + s_rowsum[r]) : 0.f;
-      const float out_scale = (g == 0) ? p.grad_scale : 1.0f;
-      const uint32_t acc_col = (g == 0) ? kColDK : kColDV;
+      // groups 0, 1 finish dK (columns [32(g%2), +32)), groups 2, 3 store dV; the Q ring is dead by now
+      const bool is_dk = g < 2;
+      uint8_t* stage = s_q + (is_dk ? 0 : kTileBytes);
+      const float w = is_dk ? (s_rowsum[r] + s_rowsum[kTile + r]) + (s_rowsum[2 * kTile + r] + s_rowsum[3 * kTile + r])
+                            : 0.f;
+      const float out_scale = is_dk ? p.grad_scale : 1.0f;
+      uint32_t acc[32];
+      tmem_ld_x32(tmem + (is_dk ? kColDK : kColDV) + lane_sel + (g & 1) * 32, acc);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld_x32(tmem + acc_col + lane_sel + c * 32, acc);
-        tmem_ld_wait();
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint32_t off = sw128_offset(r, (g & 1) * 4 + q4);
+        const uint4 k_raw = *reinterpret_cast<const uint4*>(s_k + off);
+        const uint32_t kw[4] = {k_raw.x, k_raw.y, k_raw.z, k_raw.w};
+        uint32_t o[4];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t off = sw128_offset(r, c * 4 + q4);
-          const uint4 k_raw = *reinterpret_cast<const uint4*>(s_k + off);
-          const uint32_t kw[4] = {k_raw.x, k_raw.y, k_raw.z, k_raw.w};
-          uint32_t o[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 kv = unpack2<kBf16>(kw[i]);
-            const float x0 = out_scale * fmaf(-w, kv.x, __uint_as_float(acc[q4 * 8 + 2 * i]));
-            const float x1 = out_scale * fmaf(-w, kv.y, __uint_as_float(acc[q4 * 8 + 2 * i + 1]));
-            o[i] = pack2<kBf16>(x0, x1);
-          }
-          *reinterpret_cast<uint4*>(stage + off) = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int i = 0; i < 4; ++i) {
+          const float2 kv = unpack2<kBf16>(kw[i]);
+          const float x0 = out_scale * fmaf(-w, kv.x, __uint_as_float(acc[q4 * 8 + 2 * i]));
+          const float x1 = out_scale * fmaf(-w, kv.y, __uint_as_float(acc[q4 * 8 + 2 * i + 1]));
+          o[i] = pack2<kBf16>(x0, x1);
         }
+        *reinterpret_cast<uint4*>(stage + off) = make_uint4(o[0], o[1], o[2], o[3]);
       }
       fence_proxy_async_smem();
       ok = group_sync();
-      if (ok && r == 0) {
-        tma_store_4d(g == 0 ? &tm_dk : &tm_dv, stage, 0, k_row0, h, b);
+      if (ok && r == 0 && (g & 1) == 0) {
+        tma_store_4d(is_dk ? &tm_dk : &tm_dv, stage, 0, k_row0, h, b);
         tma_store_commit();
         tma_store_wait_all();
       }
@@ -493,7 +584,7 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
   cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, stream);
   if (e != cudaSuccess) return e;
   Params p{};
-  p.ksq = a.ksq; p.lse = a.lse; p.delta = a.delta; p.status = a.status;
+  p.ksq = a.ksq; p.lse_pad = a.lse_pad; p.delta = a.delta; p.status = a.status;
   p.H = a.H; p.N = a.N; p.n_pad = a.n_pad; p.causal = a.causal;
   p.scale2 = a.scale2; p.grad_scale = a.grad_scale;
   dim3 grid((a.N + kTile - 1) / kTile, a.B * a.H);
@@ -507,6 +598,12 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace bwdf
+
+#ifdef RBF_TRACE
+extern "C" int rbf_b200_debug_read_trace(long long* host, int count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, bwdf::g_trace, sizeof(long long) * count));
+}
+#endif
 
 cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream) {
   return bf16 ? bwdf::launch_t<true>(a, stream) : bwdf::launch_t<false>(a, stream);

@@ -94,8 +94,12 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
   const int nkt_max = max(nkt[0], nkt[1]);
 
+  // A wait that ran out in an earlier CTA of this launch ends the whole launch quickly: later CTAs leave at once.
+  if (tid == 0) *abort_flag = (*reinterpret_cast<volatile unsigned int*>(&status->code) != 0u) ? 1 : 0;
+  __syncthreads();
+  if (*abort_flag) return;
+
   if (tid == 0) {
-    *abort_flag = 0;
     mbar_init(&q_full[0], 1);
     mbar_init(&q_full[1], 1);
     for (int s = 0; s < kStages; ++s) {
@@ -106,9 +110,9 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], kTile);
+      mbar_init(&p_full[t], 4);              // one arrival per softmax warp
       mbar_init(&o_done[t], 1);
-      mbar_init(&grp_sync[t], kTile);
+      mbar_init(&grp_sync[t], 4);
     }
     fence_mbar_init();
   }
@@ -226,7 +230,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint32_t grp_phase = 0;
     // Bounded rendezvous of the group's 128 threads (a named barrier could not be abandoned on abort).
     auto group_sync = [&]() -> bool {
-      mbar_arrive(&grp_sync[t]);
+      mbar_arrive_warp(&grp_sync[t]);
       const bool done = mbar_wait(&grp_sync[t], grp_phase & 1, abort_flag, status, kSiteKsqSync);
       ++grp_phase;
       return done;
@@ -313,7 +317,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       l_sum += psum;
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(&p_full[t]);
+      mbar_arrive_warp(&p_full[t]);
       if (j + 1 < my_nkt) ksq_buf[((j + 1) & 1) * kTile + r] = ksq_next;
     }
 

@@ -1,74 +1,96 @@
-// Row-wise pre-passes over (B, H, N, D) tensors: scaled squared row norms (the RBF key / query bias)
-// and the backward's delta = rowsum(O * dO). One warp per row; pure HBM streaming.
+// Row-wise pre-pass over (B, H, N, D) tensors, one launch per forward / backward call:
+//   ksq[row]     = c * |k_row|^2            (+inf on padding rows: a padded key then gets weight exp2(-inf) = 0)
+//   qsq[row]     = c * |q_row|^2            (non-softmax variant)
+//   delta[row]   = sum_d O[row,d] dO[row,d] (softmax backward; 0 on padding rows)
+//   lse_pad[row] = lse[row]                 (softmax backward: the forward's L re-pitched to n_pad, +inf padding)
+// Pure HBM streaming: D/8 lanes per row with 16-byte loads, 32/(D/8) rows per warp per iteration.
 #include "common.cuh"
 #include "launch.h"
 
 namespace rbf {
 
-template <bool kBf16, int D>
-__device__ __forceinline__ void load_row_chunk(const void* base, int64_t row_off, int lane, float (&x)[D / 32]) {
-  constexpr int kPer = D / 32;  // 2 (D=64) or 4 (D=128) consecutive elements per lane
-  const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + row_off + lane * kPer;
-  if constexpr (kPer == 2) {
-    uint32_t w = *reinterpret_cast<const uint32_t*>(p);
-    float2 f = unpack2<kBf16>(w);
-    x[0] = f.x; x[1] = f.y;
-  } else {
-    uint2 w = *reinterpret_cast<const uint2*>(p);
-    float2 f0 = unpack2<kBf16>(w.x), f1 = unpack2<kBf16>(w.y);
-    x[0] = f0.x; x[1] = f0.y; x[2] = f1.x; x[3] = f1.y;
+template <bool kBf16>
+__device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = unpack2<kBf16>(aw[i]), y = unpack2<kBf16>(bw[i]);
+    acc = fmaf(x.x, y.x, acc);
+    acc = fmaf(x.y, y.y, acc);
   }
+  return acc;
 }
 
-// out[bh * n_pad + i] = scale * sum_d x[b,h,i,d]^2 for i < N, `pad_value` for N <= i < n_pad.
-// With y != nullptr: out = sum_d x*y (scale ignored).
+__device__ __forceinline__ uint4 load_chunk(const void* base, const int64_t* s, int b, int h, int row, int part) {
+  return *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + b * s[0] + h * s[1] +
+                                         static_cast<int64_t>(row) * s[2] + part * 8);
+}
+
 template <bool kBf16, int D>
-__global__ void __launch_bounds__(256) row_reduce_kernel(const void* __restrict__ x, const void* __restrict__ y,
-                                                         float* __restrict__ out, int H, int N, int n_pad,
-                                                         int64_t xsb, int64_t xsh, int64_t xsn, int64_t ysb,
-                                                         int64_t ysh, int64_t ysn, float scale, float pad_value,
-                                                         DeviceStatus* status_to_clear) {
-  if (status_to_clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) status_to_clear->code = 0;
+__global__ void __launch_bounds__(256) row_stats_kernel(const RowStatsArgs a) {
+  constexpr int kLanesPerRow = D / 8;                 // 8 (D=64) or 16 (D=128)
+  constexpr int kRowsPerWarp = 32 / kLanesPerRow;     // 4 or 2
+  if (a.status_to_clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+    a.status_to_clear->code = 0;
   const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int warp = threadIdx.x >> 5;
+  const int sub = lane / kLanesPerRow;                // row within the warp's group
+  const int part = lane % kLanesPerRow;               // 16-byte chunk of the row
   const int bh = blockIdx.y;
-  if (row >= n_pad) return;
-  float acc;
-  if (row < N) {
-    const int b = bh / H, h = bh % H;
-    float xv[D / 32];
-    load_row_chunk<kBf16, D>(x, b * xsb + h * xsh + row * xsn, lane, xv);
-    acc = 0.f;
-    if (y != nullptr) {
-      float yv[D / 32];
-      load_row_chunk<kBf16, D>(y, b * ysb + h * ysh + row * ysn, lane, yv);
-#pragma unroll
-      for (int i = 0; i < D / 32; ++i) acc = fmaf(xv[i], yv[i], acc);
-    } else {
-#pragma unroll
-      for (int i = 0; i < D / 32; ++i) acc = fmaf(xv[i], xv[i], acc);
+  const int b = bh / a.H, h = bh % a.H;
+  const int rows_per_block = 8 * kRowsPerWarp * a.iters;
+  const int row_begin = blockIdx.x * rows_per_block;
+  const int64_t out_base = static_cast<int64_t>(bh) * a.n_pad;
+
+  for (int it = 0; it < a.iters; ++it) {
+    const int row = row_begin + (it * 8 + warp) * kRowsPerWarp + sub;
+    const bool valid = row < a.N;
+    float ksq = 0.f, qsq = 0.f, delta = 0.f;
+    if (valid) {
+      if (a.k != nullptr) {
+        const uint4 v = load_chunk(a.k, a.ks, b, h, row, part);
+        ksq = dot8<kBf16>(v, v);
+      }
+      if (a.q != nullptr) {
+        const uint4 v = load_chunk(a.q, a.qs, b, h, row, part);
+        qsq = dot8<kBf16>(v, v);
+      }
+      if (a.o != nullptr) {
+        const uint4 x = load_chunk(a.o, a.os, b, h, row, part);
+        const uint4 y = load_chunk(a.dout, a.dos, b, h, row, part);
+        delta = dot8<kBf16>(x, y);
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (y == nullptr) acc *= scale;
-  } else {
-    acc = pad_value;
+    for (int o = kLanesPerRow / 2; o > 0; o >>= 1) {
+      ksq += __shfl_xor_sync(0xffffffffu, ksq, o);
+      qsq += __shfl_xor_sync(0xffffffffu, qsq, o);
+      delta += __shfl_xor_sync(0xffffffffu, delta, o);
+    }
+    if (part == 0 && row < a.n_pad) {
+      if (a.ksq_out != nullptr) a.ksq_out[out_base + row] = valid ? ksq * a.scale : INFINITY;
+      if (a.qsq_out != nullptr) a.qsq_out[out_base + row] = valid ? qsq * a.scale : a.qsq_pad;
+      if (a.delta_out != nullptr) a.delta_out[out_base + row] = delta;
+      if (a.lse_pad_out != nullptr)
+        a.lse_pad_out[out_base + row] = valid ? a.lse[static_cast<int64_t>(bh) * a.N + row] : INFINITY;
+    }
   }
-  if (lane == 0) out[static_cast<int64_t>(bh) * n_pad + row] = acc;
 }
 
 template <bool kBf16, int D>
-static cudaError_t launch_row_reduce_t(const RowReduceArgs& a, cudaStream_t stream) {
-  dim3 grid((a.n_pad + 7) / 8, a.B * a.H);
-  row_reduce_kernel<kBf16, D><<<grid, 256, 0, stream>>>(a.x, a.y, a.out, a.H, a.N, a.n_pad, a.xs[0], a.xs[1],
-                                                         a.xs[2], a.ys[0], a.ys[1], a.ys[2], a.scale, a.pad_value,
-                                                         a.status_to_clear);
+static cudaError_t launch_row_stats_t(RowStatsArgs a, cudaStream_t stream) {
+  constexpr int kRowsPerWarp = 32 / (D / 8);
+  a.iters = 4;
+  const int rows_per_block = 8 * kRowsPerWarp * a.iters;
+  dim3 grid((a.n_pad + rows_per_block - 1) / rows_per_block, a.B * a.H);
+  row_stats_kernel<kBf16, D><<<grid, 256, 0, stream>>>(a);
   return cudaGetLastError();
 }
 
-cudaError_t launch_row_reduce(const RowReduceArgs& a, bool bf16, int D, cudaStream_t stream) {
-  if (D == 64) return bf16 ? launch_row_reduce_t<true, 64>(a, stream) : launch_row_reduce_t<false, 64>(a, stream);
-  return bf16 ? launch_row_reduce_t<true, 128>(a, stream) : launch_row_reduce_t<false, 128>(a, stream);
+cudaError_t launch_row_stats(const RowStatsArgs& a, bool bf16, int D, cudaStream_t stream) {
+  if (D == 64) return bf16 ? launch_row_stats_t<true, 64>(a, stream) : launch_row_stats_t<false, 64>(a, stream);
+  return bf16 ? launch_row_stats_t<true, 128>(a, stream) : launch_row_stats_t<false, 128>(a, stream);
 }
 
 }  // namespace rbf
