@@ -28,34 +28,52 @@ size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 struct Workspace {
   rbf::DeviceStatus* status;
-  float* ksq;
+  void* kslab;       // forward: key-norm bias slabs, 32 bytes per row
+  float* ksq;        // backward: c|k|^2 per row
   float* row_bias;   // query norms (non-softmax) or the forward's L re-pitched to n_pad (softmax backward)
   float* delta;      // backward only
-  float* dq_acc;     // single-kernel backward only: fp32 (B, H, N, D)
+  void* lslab;       // single-kernel backward only: L and delta bias slabs, fp32 (B, H, N, D) dQ accumulator
+  void* dslab;
+  float* dq_acc;
   size_t bytes;
 };
 
 // The softmax backward at head dim 64 runs as one kernel that accumulates dQ in fp32 global memory.
 bool use_fused_backward(int D, int softmax) { return softmax && D == 64; }
 
+// Constant held by the operand-side slab of a bias-slab MMA step, and the "minus infinity" the slabs use on padding
+// rows. fp16 needs the range extension: a bias up to 65504 * 256 stays representable.
+float slab_w(bool bf16) { return bf16 ? 1.0f : 256.0f; }
+float slab_big(bool bf16) { return bf16 ? 1e30f : 60000.0f; }
+
 Workspace carve(void* base, int B, int H, int N, int D, int softmax, int backward) {
   const size_t rows = static_cast<size_t>(B) * H * rbf::padded_rows(N);
   const size_t vec = align256(rows * sizeof(float));
+  const size_t slab = align256(rows * 32);
   char* p = static_cast<char*>(base);
   Workspace w{};
   size_t off = 0;
   w.status = reinterpret_cast<rbf::DeviceStatus*>(p + off);
   off += kStatusBytes;
-  w.ksq = reinterpret_cast<float*>(p + off);
-  off += vec;
-  if (!softmax || backward) {
+  if (!backward) {
+    w.kslab = p + off;
+    off += slab;
+    if (!softmax) {
+      w.row_bias = reinterpret_cast<float*>(p + off);
+      off += vec;
+    }
+  } else {
+    w.ksq = reinterpret_cast<float*>(p + off);
+    off += vec;
     w.row_bias = reinterpret_cast<float*>(p + off);
     off += vec;
-  }
-  if (backward) {
     w.delta = reinterpret_cast<float*>(p + off);
     off += vec;
     if (use_fused_backward(D, softmax)) {
+      w.lslab = p + off;
+      off += slab;
+      w.dslab = p + off;
+      off += slab;
       w.dq_acc = reinterpret_cast<float*>(p + off);
       off += align256(static_cast<size_t>(B) * H * N * D * sizeof(float));
     }
@@ -144,7 +162,8 @@ int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, 
   if (phases & RBF_B200_PHASE_PREPASS) {
     rbf::RowStatsArgs r{};
     r.B = B; r.H = H; r.N = N; r.n_pad = n_pad; r.scale = c; r.status_to_clear = ws.status;
-    r.k = k; r.ksq_out = ws.ksq; set_strides(r.ks, k_strides);
+    r.scale2 = 2.f * c; r.slab_w = slab_w(bf16); r.slab_big = slab_big(bf16);
+    r.k = k; r.kslab_out = ws.kslab; set_strides(r.ks, k_strides);
     if (!softmax) {
       r.q = q; r.qsq_out = ws.row_bias; r.qsq_pad = 0.f; set_strides(r.qs, q_strides);
     }
@@ -153,7 +172,10 @@ int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, 
   }
   if (!(phases & RBF_B200_PHASE_MAIN)) return RBF_B200_OK;
 
-  a.ksq = ws.ksq; a.qsq = ws.row_bias; a.lse = lse; a.status = ws.status;
+  const int sr = rbf::make_tmap_slab16(&a.tm_kslab, ws.kslab, bf16, B * H, n_pad, rbf::kTile);
+  if (sr != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the key-norm slabs (code %d)", sr);
+  a.slab_w = slab_w(bf16);
+  a.qsq = ws.row_bias; a.lse = lse; a.status = ws.status;
   a.B = B; a.H = H; a.N = N; a.n_pad = n_pad; a.causal = causal ? 1 : 0; a.scale2 = 2.f * c;
   e = rbf::launch_fwd(a, bf16, D, softmax != 0, stream);
   if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "forward launch failed: %s", cudaGetErrorString(e));
@@ -211,6 +233,8 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
   if (phases & RBF_B200_PHASE_PREPASS) {
     rbf::RowStatsArgs r{};
     r.B = B; r.H = H; r.N = N; r.n_pad = n_pad; r.scale = c; r.status_to_clear = ws.status;
+    r.scale2 = 2.f * c; r.slab_w = slab_w(bf16); r.slab_big = slab_big(bf16);
+    r.lslab_out = ws.lslab; r.dslab_out = ws.dslab;   // null unless the single-kernel backward runs
     r.k = k; r.ksq_out = ws.ksq; set_strides(r.ks, k_strides);
     r.delta_out = ws.delta;                     // written as zeros when there is no O (non-softmax variant)
     if (softmax) {

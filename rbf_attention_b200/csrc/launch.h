@@ -20,6 +20,12 @@ struct RowStatsArgs {
   float* qsq_out;
   float* delta_out;
   float* lse_pad_out;
+  // "bias slabs": 16 x 16-bit per row (hi, mid, lo parts of an fp32 value, then zeros), consumed as one extra
+  // K = 16 step of an MMA against a slab of constants `slab_w`, so that the product adds the fp32 value back.
+  void* kslab_out;        // -ksq / (scale2 * slab_w); -slab_big on padding rows
+  void* lslab_out;        // -lse / (scale2 * slab_w); -slab_big on padding rows
+  void* dslab_out;        // -delta / slab_w; 0 on padding rows
+  float scale2, slab_w, slab_big;
   int64_t ks[3], qs[3], os[3], dos[3];   // element strides of dims b, h, n
   int B, H, N, n_pad;
   float scale;
@@ -32,8 +38,9 @@ cudaError_t launch_row_stats(const RowStatsArgs& a, bool bf16, int D, cudaStream
 // Forward pass. Tensor maps use a 64-element x 128-row box with the 128-byte swizzle.
 struct FwdArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
-  const float* ksq;       // (B*H, n_pad): gamma*log2(e)*|k|^2, +inf on padding rows
-  const float* qsq;       // (B*H, n_pad): same for q; non-softmax variant only
+  CUtensorMap tm_kslab;   // (B*H, n_pad, 16) key-norm bias slabs, box 16 x 128, 32-byte swizzle
+  float slab_w;           // constant the other operand's slab holds
+  const float* qsq;       // (B*H, n_pad): gamma*log2(e)*|q|^2; non-softmax variant only
   float* lse;             // (B, H, N) base-2 log-sum-exp; softmax variant only
   DeviceStatus* status;
   int B, H, N, n_pad;

@@ -102,6 +102,14 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* t
       "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 // 1-D bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -201,6 +209,13 @@ __device__ __forceinline__ SmemDesc make_sdesc_parts(uint32_t smem_addr, uint32_
   SmemDesc d;
   d.lo = ((smem_addr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
   d.hi = ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (2u << 29);
+  return d;
+}
+// K-major descriptor of a 16-element-wide "bias slab" (rows of 32 bytes, 32-byte swizzle, 8-row groups 256 bytes apart).
+__device__ __forceinline__ SmemDesc make_sdesc_slab32(uint32_t smem_addr) {
+  SmemDesc d;
+  d.lo = ((smem_addr & 0x3ffffu) >> 4) | (1u << 16);
+  d.hi = (256u >> 4) | (1u << 14) | (6u << 29);   // SBO = 256, version 1, SWIZZLE_32B
   return d;
 }
 __device__ __forceinline__ uint64_t sdesc_at(const SmemDesc& d, uint32_t byte_offset) {

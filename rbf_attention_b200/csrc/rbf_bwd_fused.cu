@@ -12,8 +12,8 @@
 // kernel converts it to the output type (times 2g) afterwards. dK gets the norm-gradient term in the
 // epilogue: dK = 2g (acc - rowsum(dS^T)[key] * k).
 //
-// Roles: warp 0 MMA issuer, warp 1 TMA producer (the lowest warp ids: the warp scheduler favours older warps, and a
-// starved issuer idles the tensor pipe), warps 4-19 compute (thread = key row; group g owns query columns
+// Roles: warps 0 and 1 MMA issuers (two, because one thread cannot issue the N = 64 products as fast as the tensor
+// pipe retires them), warp 2 TMA producer, warps 4-19 compute (thread = key row; group g owns query columns
 // [32g, 32g+32) of the tile), warps 20-23 drain dQ_partial (thread = query row). The compute warpgroups take
 // registers from the others (setmaxnreg) so that four warps per scheduler hide the MUFU and TMEM latencies.
 // TMEM columns: S^T [0,128), dP^T [128,256), dV [256,320), dK [320,384), dQ_partial x2 [384,512).
@@ -40,8 +40,9 @@ __device__ long long g_trace[4 * 64 * 16];
 static constexpr int D = 64;
 static constexpr int kThreads = 768;
 static constexpr int kNumComputeWarps = 16;
-static constexpr int kMmaWarp = 0;
-static constexpr int kLoadWarp = 1;
+static constexpr int kMmaWarpA = 0;
+static constexpr int kMmaWarpB = 1;
+static constexpr int kLoadWarp = 2;
 static constexpr int kComputeWarp0 = 4;
 static constexpr int kDrainWarp0 = 20;
 // Register budget: the launch allocates 80 per thread (768 threads); setmaxnreg may only redistribute that
@@ -152,13 +153,13 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     mbar_init(&dq_full[1], 1);
     mbar_init(&dq_drained[0], 4);
     mbar_init(&dq_drained[1], 4);
-    mbar_init(acc_done, 1);
+    mbar_init(acc_done, 2);                   // one commit from each MMA issuer
     mbar_init(grp_sync, kNumComputeWarps);
     mbar_init(drain_sync, 4);
     mbar_init(dbg_bar, 1);
     fence_mbar_init();
   }
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarpA) {
     tmem_alloc(tmem_base_s, 512);
     tmem_relinquish();
   }
@@ -203,21 +204,17 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         tma_load_4d(s_do + sd * kTileBytes, &tm_do, &do_full[sd], 0, row0, h, b);
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kMmaWarpA || warp == kMmaWarpB) {
+    // ------------------------------------------------------------------ MMA issuers
+    // One thread sustains about one tcgen05.mma per 58 cycles, which is slower than the tensor pipe retires the
+    // N = 64 products (32 cycles each), so the five MMAs of a step are split over two issuing threads such that
+    // every ordering the TMEM aliasing needs stays inside one thread's in-order stream:
+    //   issuer A: dV(n) (reads P^T from the S^T columns), then S^T(n+1) (overwrites them)
+    //   issuer B: dK(n) (reads dS^T from the dP^T columns), then dP^T(n+1) (overwrites them), then dQ_partial(n)
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(kTile, kTile, kBf16, false, false);  // keys x queries, both K-major
       constexpr uint32_t idesc_acc = make_idesc(kTile, D, kBf16, false, true);     // A from TMEM, B N-major
       constexpr uint32_t idesc_dq = make_idesc(kTile, D, kBf16, true, true);       // A M-major (dS^T tile), B N-major
-      // descriptors: K-major view (rows = M/N index) and N-/M-major view (rows = reduction index) of each tile
-      const SmemDesc k_kmaj = make_sdesc_parts(smem_u32(s_k), 16, 1024);
-      const SmemDesc v_kmaj = make_sdesc_parts(smem_u32(s_v), 16, 1024);
-      const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
-      const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);
-      const SmemDesc q_kmaj0 = make_sdesc_parts(smem_u32(s_q), 16, 1024);
-      const SmemDesc do_kmaj0 = make_sdesc_parts(smem_u32(s_do), 16, 1024);
-      const SmemDesc q_nmaj0 = make_sdesc_parts(smem_u32(s_q), kTile * 128, 1024);
-      const SmemDesc do_nmaj0 = make_sdesc_parts(smem_u32(s_do), kTile * 128, 1024);
       auto stage_of = [](SmemDesc d, int stage) {
         d.lo += static_cast<uint32_t>(stage) * (kTileBytes >> 4);
         return d;
@@ -241,99 +238,84 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       auto wait_do = [&](int n) {
         return mbar_wait(&do_full[n % kDoStages], (n / kDoStages) & 1, abort_flag, p.status, kSiteDoFull);
       };
-
-#ifdef RBF_SERIALIZE_MMA
-      uint32_t dbg_phase = 0;
-#define RBF_DBG_DRAIN()                                                        \
-  do {                                                                         \
-    umma_commit(dbg_bar);                                                      \
-    mbar_wait(dbg_bar, dbg_phase & 1, abort_flag, p.status, 99);               \
-    ++dbg_phase;                                                               \
-  } while (0)
-#else
-#define RBF_DBG_DRAIN() \
-  do {                  \
-  } while (0)
-#endif
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kSiteKV);
-      if (ok) ok = wait_q(0);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_kmajor(tmem + kColS, k_kmaj, q_kmaj0);
-        umma_commit(s_full);
-        ok = wait_do(0);
-      }
-      if (ok) {
-        tc_fence_after_sync();
-        issue_kmajor(tmem + kColDP, v_kmaj, do_kmaj0);
-        umma_commit(dp_full);
-      }
-      for (int n = 0; n < cnt && ok; ++n) {
-        const SmemDesc q_n = stage_of(q_nmaj0, n % kQStages);
-        const SmemDesc do_n = stage_of(do_nmaj0, n % kDoStages);
-        const uint32_t acc_flag = n > 0 ? 1u : 0u;
-        // dV += P^T dO
-        RBF_TRACE_EVENT(0, n, 0);
-        ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
-        if (!ok) break;
-        RBF_TRACE_EVENT(0, n, 1);
-        tc_fence_after_sync();
-        issue_acc(tmem + kColDV, tmem + kColS, do_n, acc_flag);
-        RBF_DBG_DRAIN();
-        RBF_TRACE_EVENT(0, n, 5);
-        // next S^T (S^T columns are free once dV has consumed P^T; the tensor pipe runs in issue order)
-        if (n + 1 < cnt) {
-          RBF_TRACE_EVENT(0, n, 9);
-          ok = wait_q(n + 1);
-          if (!ok) break;
-          RBF_TRACE_EVENT(0, n, 10);
+
+      if (warp == kMmaWarpA) {
+        const SmemDesc k_kmaj = make_sdesc_parts(smem_u32(s_k), 16, 1024);
+        const SmemDesc q_kmaj0 = make_sdesc_parts(smem_u32(s_q), 16, 1024);
+        const SmemDesc do_nmaj0 = make_sdesc_parts(smem_u32(s_do), kTile * 128, 1024);
+        if (ok) ok = wait_q(0);
+        if (ok) {
           tc_fence_after_sync();
-          issue_kmajor(tmem + kColS, k_kmaj, stage_of(q_kmaj0, (n + 1) % kQStages));
+          issue_kmajor(tmem + kColS, k_kmaj, q_kmaj0);
           umma_commit(s_full);
         }
-        RBF_DBG_DRAIN();
-        RBF_TRACE_EVENT(0, n, 6);
-        // dK += dS^T Q
-        RBF_TRACE_EVENT(0, n, 2);
-        ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
-        if (!ok) break;
-        RBF_TRACE_EVENT(0, n, 3);
-        tc_fence_after_sync();
-        issue_acc(tmem + kColDK, tmem + kColDP, q_n, acc_flag);
-        umma_commit(&q_empty[n % kQStages]);      // Q(n) and dO(n) have no reader left once these complete
-        umma_commit(&do_empty[n % kDoStages]);
-        RBF_DBG_DRAIN();
-        RBF_TRACE_EVENT(0, n, 7);
-        // next dP^T
-        if (n + 1 < cnt) {
-          RBF_TRACE_EVENT(0, n, 11);
-          ok = wait_do(n + 1);
+        for (int n = 0; n < cnt && ok; ++n) {
+          // dV += P^T dO
+          RBF_TRACE_EVENT(0, n, 0);
+          ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
           if (!ok) break;
-          RBF_TRACE_EVENT(0, n, 12);
+          RBF_TRACE_EVENT(0, n, 1);
           tc_fence_after_sync();
-          issue_kmajor(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, (n + 1) % kDoStages));
+          issue_acc(tmem + kColDV, tmem + kColS, stage_of(do_nmaj0, n % kDoStages), n > 0 ? 1u : 0u);
+          umma_commit(&do_empty[n % kDoStages]);   // dO(n)'s other reader, dP^T(n), completed before P^T(n) existed
+          RBF_TRACE_EVENT(0, n, 5);
+          if (n + 1 < cnt) {
+            ok = wait_q(n + 1);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_kmajor(tmem + kColS, k_kmaj, stage_of(q_kmaj0, (n + 1) % kQStages));
+            umma_commit(s_full);
+          }
+          RBF_TRACE_EVENT(0, n, 6);
+        }
+      } else {
+        const SmemDesc v_kmaj = make_sdesc_parts(smem_u32(s_v), 16, 1024);
+        const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
+        const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);
+        const SmemDesc do_kmaj0 = make_sdesc_parts(smem_u32(s_do), 16, 1024);
+        const SmemDesc q_nmaj0 = make_sdesc_parts(smem_u32(s_q), kTile * 128, 1024);
+        if (ok) ok = wait_do(0);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_kmajor(tmem + kColDP, v_kmaj, do_kmaj0);
           umma_commit(dp_full);
         }
-        RBF_DBG_DRAIN();
-        RBF_TRACE_EVENT(0, n, 8);
-        // dQ_partial = dS K : A = dS^T tile read M-major (rows = keys = reduction index), B = K read N-major
-        RBF_TRACE_EVENT(0, n, 13);
-        if (n >= 2) {
-          ok = mbar_wait(&dq_drained[n & 1], ((n - 2) >> 1) & 1, abort_flag, p.status, kSiteDQDrained);
+        for (int n = 0; n < cnt && ok; ++n) {
+          // dK += dS^T Q
+          RBF_TRACE_EVENT(1, n, 8);
+          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
           if (!ok) break;
+          RBF_TRACE_EVENT(1, n, 9);
           tc_fence_after_sync();
-        }
-        RBF_TRACE_EVENT(0, n, 14);
+          issue_acc(tmem + kColDK, tmem + kColDP, stage_of(q_nmaj0, n % kQStages), n > 0 ? 1u : 0u);
+          umma_commit(&q_empty[n % kQStages]);     // Q(n)'s other reader, S^T(n), completed before dS^T(n) existed
+          RBF_TRACE_EVENT(1, n, 10);
+          if (n + 1 < cnt) {
+            ok = wait_do(n + 1);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_kmajor(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, (n + 1) % kDoStages));
+            umma_commit(dp_full);
+          }
+          RBF_TRACE_EVENT(1, n, 11);
+          // dQ_partial = dS K : A = dS^T tile read M-major (rows = keys = reduction index), B = K read N-major
+          if (n >= 2) {
+            ok = mbar_wait(&dq_drained[n & 1], ((n - 2) >> 1) & 1, abort_flag, p.status, kSiteDQDrained);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          RBF_TRACE_EVENT(1, n, 12);
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          umma_ss(tmem + kColDQ + (n & 1) * D, sdesc_at(ds_mmaj, kk * 2048), sdesc_at(k_nmaj, kk * 2048), idesc_dq,
-                  kk > 0);
+          for (int kk = 0; kk < kTile / 16; ++kk) {
+            umma_ss(tmem + kColDQ + (n & 1) * D, sdesc_at(ds_mmaj, kk * 2048), sdesc_at(k_nmaj, kk * 2048), idesc_dq,
+                    kk > 0);
+          }
+          umma_commit(&dq_full[n & 1]);
+          RBF_TRACE_EVENT(1, n, 13);
         }
-        umma_commit(&dq_full[n & 1]);
-        RBF_DBG_DRAIN();
-        RBF_TRACE_EVENT(0, n, 4);
       }
-      if (ok) umma_commit(acc_done);
+      if (ok) umma_commit(acc_done);   // both issuers arrive: the barrier counts two
     }
   } else if (warp >= kDrainWarp0) {
     // ------------------------------------------------------------------ dQ_partial drain (thread = query row)
@@ -543,7 +525,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
+  if (warp == kMmaWarpA) tmem_dealloc(tmem, 512);
 }
 
 // dq[b,h,n,:] = scale * acc[b,h,n,:]  (acc fp32 contiguous, dq 16-bit with strides)

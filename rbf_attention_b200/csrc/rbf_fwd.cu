@@ -6,11 +6,18 @@
 // One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row tiles and walks the
 // key tiles (128 keys) once for both. Roles:
 //   warps 0-3 / 4-7  softmax group for query tile 0 / 1 (one thread per query row)
-//   warp 8           TMA producer: Q tiles once, then a ring of K and V tiles
-//   warp 9           tcgen05.mma issuer: S_t = Q_t K_j^T (smem x smem) and O_t += P_t V_j (TMEM x smem)
+//   warp 8           TMA producer: Q tiles once, then a ring of K (+ its key-norm bias slab) and V tiles
+//   warps 9, 10      tcgen05.mma issuers, one per query tile: S_t = Q_t K_j^T (smem x smem), O_t += P_t V_j
+//                    (TMEM x smem). One thread sustains one MMA per ~58 cycles, slower than the tensor pipe retires
+//                    the N = 64 products, hence two issuing threads.
 // TMEM columns: [0,128) S_0, [128,256) S_1, then O_0 and O_1 (D columns each). P_t (16-bit) is written
 // back over the first 64 columns of S_t and consumed from there as the A operand of the second MMA.
-// The key-norm bias is applied in registers on the fp32 accumulator: s = acc * (2 g log2e) - ksq_j.
+//
+// The key-norm bias never passes through registers or shared-memory loads: the pre-pass stores
+// -|k_j|^2 / 2 as three 16-bit parts per key ("bias slab"), and S_t gets one extra K = 16 MMA step against a
+// slab of constants, so the fp32 accumulator already holds q.k - |k|^2/2 and the logit is acc * 2 g log2e.
+// (Reading the bias per column from shared memory costs four wavefronts per warp instruction and made the
+// shared-memory pipe, which also feeds the MMA operands, the bottleneck.)
 // The running maximum is only raised (and O rescaled in TMEM) when it grew by more than 2^8, so the
 // rescale is rare; L and the final 1/l normalisation use the maximum actually applied.
 #include "common.cuh"
@@ -20,10 +27,16 @@ namespace rbf {
 
 namespace fwd {
 
-static constexpr int kThreads = 320;
+static constexpr int kThreads = 384;
 static constexpr int kLoadWarp = 8;
-static constexpr int kMmaWarp = 9;
+static constexpr int kMmaWarp0 = 9;          // issuer of query tile t is warp kMmaWarp0 + t
 static constexpr float kRescaleThreshold = 8.0f;
+static constexpr int kSlabBytes = kTile * 32;   // 128 rows x 16 x 16-bit
+// Register budget (setmaxnreg only redistributes the launch allocation of 168 per thread):
+// 256 softmax threads * 216 + 128 other threads * 72 = 64512 = 384 * 168.
+static constexpr int kSoftmaxRegs = 216;
+static constexpr int kOtherRegs = 72;
+static_assert(256 * kSoftmaxRegs + 128 * kOtherRegs <= 384 * 168, "setmaxnreg budget");
 
 template <int D>
 struct Smem {
@@ -32,8 +45,9 @@ struct Smem {
   static constexpr int kQ = 0;                              // 2 tiles
   static constexpr int kK = kQ + 2 * kTileBytes;            // kStages tiles
   static constexpr int kV = kK + kStages * kTileBytes;      // kStages tiles
-  static constexpr int kKsq = kV + kStages * kTileBytes;    // [2 groups][2 buffers][128] floats
-  static constexpr int kBars = kKsq + 2 * 2 * kTile * 4;
+  static constexpr int kKSlab = kV + kStages * kTileBytes;  // kStages bias slabs
+  static constexpr int kOnes = kKSlab + kStages * kSlabBytes;
+  static constexpr int kBars = kOnes + kSlabBytes;
   static constexpr int kNumBars = 2 + 4 * kStages + 8;
   static constexpr int kMisc = kBars + kNumBars * 8;        // tmem base, abort flag
   static constexpr int kTotal = kMisc + 16;
@@ -42,15 +56,16 @@ struct Smem {
 
 enum Site : uint32_t {
   kSiteQFull = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSFull, kSitePFull, kSiteODone,
-  kSiteODoneFinal, kSiteKsqSync
+  kSiteODoneFinal, kSiteGroup
 };
 
 template <int D, bool kSoftmax, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-               const float* __restrict__ ksq, const float* __restrict__ qsq, float* __restrict__ lse,
-               DeviceStatus* status, int H, int N, int n_pad, int causal, float scale2) {
+               const __grid_constant__ CUtensorMap tm_kslab, const float* __restrict__ qsq,
+               float* __restrict__ lse, DeviceStatus* status, int H, int N, int n_pad, int causal, float scale2,
+               float slab_w) {
   using L = Smem<D>;
   constexpr int kStages = L::kStages;
   constexpr int kBoxes = D / 64;                 // 64-column TMA boxes per tile row
@@ -62,17 +77,18 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint8_t* s_q = smem + L::kQ;
   uint8_t* s_k = smem + L::kK;
   uint8_t* s_v = smem + L::kV;
-  float* s_ksq = reinterpret_cast<float*>(smem + L::kKsq);
+  uint8_t* s_kslab = smem + L::kKSlab;
+  uint8_t* s_ones = smem + L::kOnes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
   uint64_t* q_full = bars;                       // [2]
   uint64_t* k_full = bars + 2;                   // [kStages]
-  uint64_t* k_empty = k_full + kStages;
+  uint64_t* k_empty = k_full + kStages;          // two arrivals: one per issuer
   uint64_t* v_full = k_empty + kStages;
-  uint64_t* v_empty = v_full + kStages;
+  uint64_t* v_empty = v_full + kStages;          // two arrivals
   uint64_t* s_full = v_empty + kStages;          // [2]
   uint64_t* p_full = s_full + 2;                 // [2]
   uint64_t* o_done = p_full + 2;                 // [2]
-  uint64_t* grp_sync = o_done + 2;               // [2] rendezvous of the 128 threads of a softmax group
+  uint64_t* grp_sync = o_done + 2;               // [2] rendezvous of the 4 warps of a softmax group
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
 
@@ -104,9 +120,9 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(&q_full[1], 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
+      mbar_init(&k_empty[s], 2);
       mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
+      mbar_init(&v_empty[s], 2);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
@@ -116,9 +132,17 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     fence_mbar_init();
   }
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp0) {
     tmem_alloc(tmem_base_s, 512);
     tmem_relinquish();
+  }
+  if (tid < kTile) {
+    // slab of constants: every row [w, w, w, 0 x5 | w, w, w, 0 x5]; both 16-byte halves are equal, so the
+    // 32-byte swizzle leaves it unchanged
+    const uint4 v = make_uint4(pack2<kBf16>(slab_w, slab_w), pack2<kBf16>(slab_w, 0.f), 0u, 0u);
+    *reinterpret_cast<uint4*>(s_ones + tid * 32) = v;
+    *reinterpret_cast<uint4*>(s_ones + tid * 32 + 16) = v;
+    fence_proxy_async_smem();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -129,10 +153,12 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA producer
+    setmaxnreg_dec<kOtherRegs>();
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_kslab);
       for (int t = 0; t < 2; ++t) {
         if (nkt[t] == 0) continue;
         mbar_arrive_expect_tx(&q_full[t], kTileBytes);
@@ -143,137 +169,162 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int st = j % kStages;
         const uint32_t par = ((j / kStages) - 1) & 1;
         if (j >= kStages && !mbar_wait(&k_empty[st], par, abort_flag, status, kSiteKEmpty)) break;
-        mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+        mbar_arrive_expect_tx(&k_full[st], kTileBytes + kSlabBytes);
         for (int x = 0; x < kBoxes; ++x)
           tma_load_4d(s_k + st * kTileBytes + x * kBoxBytes, &tm_k, &k_full[st], x * 64, j * kTile, h, b);
+        tma_load_3d(s_kslab + st * kSlabBytes, &tm_kslab, &k_full[st], 0, j * kTile, bh);
         if (j >= kStages && !mbar_wait(&v_empty[st], par, abort_flag, status, kSiteVEmpty)) break;
         mbar_arrive_expect_tx(&v_full[st], kTileBytes);
         for (int x = 0; x < kBoxes; ++x)
           tma_load_4d(s_v + st * kTileBytes + x * kBoxBytes, &tm_v, &v_full[st], x * 64, j * kTile, h, b);
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+    // ------------------------------------------------------------------ MMA issuer of query tile t
+    setmaxnreg_dec<kOtherRegs>();
     if (lane == 0) {
+      const int t = warp - kMmaWarp0;
+      const int my_nkt = nkt[t];
       constexpr uint32_t idesc_s = make_idesc(kTile, kTile, kBf16, false, false);   // S = Q K^T
       constexpr uint32_t idesc_o = make_idesc(kTile, D, kBf16, false, true);        // O += P V (V is N-major)
-      const uint32_t q_addr = smem_u32(s_q), k_addr = smem_u32(s_k), v_addr = smem_u32(s_v);
-      auto issue_s = [&](int t, int st) {
+      const SmemDesc q_desc = make_sdesc_parts(smem_u32(s_q) + t * kTileBytes, 16, 1024);
+      const SmemDesc k_desc0 = make_sdesc_parts(smem_u32(s_k), 16, 1024);
+      const SmemDesc v_desc0 = make_sdesc_parts(smem_u32(s_v), kBoxBytes, 1024);
+      const SmemDesc ones_desc = make_sdesc_slab32(smem_u32(s_ones));
+      const SmemDesc kslab_desc0 = make_sdesc_slab32(smem_u32(s_kslab));
+      auto issue_s = [&](int st) {
+        SmemDesc k_desc = k_desc0;
+        k_desc.lo += static_cast<uint32_t>(st) * (kTileBytes >> 4);
+        SmemDesc slab = kslab_desc0;
+        slab.lo += static_cast<uint32_t>(st) * (kSlabBytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          umma_ss(tmem_s[t], make_sdesc_sw128(q_addr + t * kTileBytes + off, 16, 1024),
-                  make_sdesc_sw128(k_addr + st * kTileBytes + off, 16, 1024), idesc_s, kk > 0);
+          umma_ss(tmem_s[t], sdesc_at(q_desc, off), sdesc_at(k_desc, off), idesc_s, kk > 0);
         }
+        umma_ss(tmem_s[t], sdesc_at(ones_desc, 0), sdesc_at(slab, 0), idesc_s, 1u);   // + key-norm bias
         umma_commit(&s_full[t]);
       };
-      auto issue_o = [&](int t, int st, bool accumulate) {
+      auto issue_o = [&](int st, uint32_t accumulate) {
+        SmemDesc v_desc = v_desc0;
+        v_desc.lo += static_cast<uint32_t>(st) * (kTileBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          umma_ts(tmem_o[t], tmem_s[t] + kk * 8, make_sdesc_sw128(v_addr + st * kTileBytes + kk * 2048, kBoxBytes, 1024),
-                  idesc_o, (accumulate || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts(tmem_o[t], tmem_s[t] + kk * 8, sdesc_at(v_desc, kk * 2048), idesc_o, kk > 0 ? 1u : accumulate);
         umma_commit(&o_done[t]);
       };
       bool ok = true;
-      for (int t = 0; t < 2 && ok; ++t)
-        if (nkt[t] > 0) ok = mbar_wait(&q_full[t], 0, abort_flag, status, kSiteQFull);
-      if (ok && nkt_max > 0) ok = mbar_wait(&k_full[0], 0, abort_flag, status, kSiteKFull);
-      if (ok) {
-        tc_fence_after_sync();
-        for (int t = 0; t < 2; ++t)
-          if (nkt[t] > 0) issue_s(t, 0);
-        umma_commit(&k_empty[0]);
+      if (my_nkt > 0) {
+        ok = mbar_wait(&q_full[t], 0, abort_flag, status, kSiteQFull) &&
+             mbar_wait(&k_full[0], 0, abort_flag, status, kSiteKFull);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_s(0);
+        }
+      }
+      // Every stage is released by both issuers: by a commit after this tile's last MMA that reads it, or - when this
+      // tile has nothing (left) to do with it - by a plain arrival made only after the stage has been filled, so that
+      // an idle issuer can never arrive twice within one phase.
+      auto wait_k = [&](int jj) {
+        return mbar_wait(&k_full[jj % kStages], (jj / kStages) & 1, abort_flag, status, kSiteKFull);
+      };
+      auto wait_v = [&](int jj) {
+        return mbar_wait(&v_full[jj % kStages], (jj / kStages) & 1, abort_flag, status, kSiteVFull);
+      };
+      if (ok && nkt_max > 0) {
+        if (my_nkt > 0) {
+          umma_commit(&k_empty[0]);
+        } else {
+          ok = wait_k(0);
+          if (ok) mbar_arrive(&k_empty[0]);
+        }
       }
       for (int j = 0; j < nkt_max && ok; ++j) {
         const int st = j % kStages;
         const int st_next = (j + 1) % kStages;
-        ok = mbar_wait(&v_full[st], (j / kStages) & 1, abort_flag, status, kSiteVFull);
-        if (!ok) break;
-        bool next_k_ready = false;
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= nkt[t]) continue;
-          ok = mbar_wait(&p_full[t], j & 1, abort_flag, status, kSitePFull);
+        bool used_k_next = false;
+        if (j < my_nkt) {
+          ok = wait_v(j) && mbar_wait(&p_full[t], j & 1, abort_flag, status, kSitePFull);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_o(t, st, j > 0);
-          if (j + 1 < nkt[t]) {
-            if (!next_k_ready) {
-              ok = mbar_wait(&k_full[st_next], ((j + 1) / kStages) & 1, abort_flag, status, kSiteKFull);
-              if (!ok) break;
-              tc_fence_after_sync();
-              next_k_ready = true;
-            }
-            issue_s(t, st_next);
+          issue_o(st, j > 0 ? 1u : 0u);
+          if (j + 1 < my_nkt) {
+            ok = wait_k(j + 1);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_s(st_next);
+            used_k_next = true;
+          }
+          umma_commit(&v_empty[st]);
+        } else {
+          ok = wait_v(j);
+          if (!ok) break;
+          mbar_arrive(&v_empty[st]);
+        }
+        if (j + 1 < nkt_max) {
+          if (used_k_next) {
+            umma_commit(&k_empty[st_next]);
+          } else {
+            ok = wait_k(j + 1);
+            if (!ok) break;
+            mbar_arrive(&k_empty[st_next]);
           }
         }
-        if (!ok) break;
-        umma_commit(&v_empty[st]);
-        if (j + 1 < nkt_max) umma_commit(&k_empty[st_next]);
       }
     }
-  } else {
+  } else if (warp < kLoadWarp) {
     // ------------------------------------------------------------------ softmax groups
+    setmaxnreg_inc<kSoftmaxRegs>();
     const int t = warp >> 2;                         // query tile of this group
     const int r = tid & (kTile - 1);                 // row within the tile == TMEM lane
     const int r0 = m0 + t * kTile;
     const int row = r0 + r;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int my_nkt = nkt[t];
-    float* ksq_buf = s_ksq + t * 2 * kTile;
-    const float* ksq_row = ksq + static_cast<int64_t>(bh) * n_pad;
-    float m_used = -INFINITY;
+    float m_used = -INFINITY;                        // maximum applied so far, in accumulator units times scale2
     float l_sum = 0.f;
     float row_bias = 0.f;
     if (!kSoftmax && my_nkt > 0) row_bias = qsq[static_cast<int64_t>(bh) * n_pad + row];
     bool ok = true;
-    uint32_t grp_phase = 0;
-    // Bounded rendezvous of the group's 128 threads (a named barrier could not be abandoned on abort).
-    auto group_sync = [&]() -> bool {
-      mbar_arrive_warp(&grp_sync[t]);
-      const bool done = mbar_wait(&grp_sync[t], grp_phase & 1, abort_flag, status, kSiteKsqSync);
-      ++grp_phase;
-      return done;
-    };
-    if (my_nkt > 0) ksq_buf[r] = ksq_row[r];
 
     for (int j = 0; j < my_nkt; ++j) {
-      float ksq_next = 0.f;
-      if (j + 1 < my_nkt) ksq_next = ksq_row[(j + 1) * kTile + r];
-      // all 128 threads of the group: publishes buffer j&1, retires buffer (j+1)&1
-      ok = group_sync() && mbar_wait(&s_full[t], j & 1, abort_flag, status, kSiteSFull);
+      ok = mbar_wait(&s_full[t], j & 1, abort_flag, status, kSiteSFull);
       if (!ok) break;
       tc_fence_after_sync();
 
-      float s[kTile];
-      const float4* kb = reinterpret_cast<const float4*>(ksq_buf + (j & 1) * kTile);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t raw[32];
-        tmem_ld_x32(tmem_s[t] + lane_sel + c * 32, raw);
+      // acc = q.k - |k|^2 / 2 for 128 keys; the logit in base-2 units is acc * scale2
+      uint32_t raw[kTile];
+      {
+        uint32_t(&c0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[0]);
+        uint32_t(&c1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[32]);
+        uint32_t(&c2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[64]);
+        uint32_t(&c3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[96]);
+        tmem_ld_x32(tmem_s[t] + lane_sel + 0, c0);
+        tmem_ld_x32(tmem_s[t] + lane_sel + 32, c1);
+        tmem_ld_x32(tmem_s[t] + lane_sel + 64, c2);
+        tmem_ld_x32(tmem_s[t] + lane_sel + 96, c3);
         tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 kq = kb[c * 8 + i];
-          s[c * 32 + i * 4 + 0] = fmaf(__uint_as_float(raw[i * 4 + 0]), scale2, -kq.x);
-          s[c * 32 + i * 4 + 1] = fmaf(__uint_as_float(raw[i * 4 + 1]), scale2, -kq.y);
-          s[c * 32 + i * 4 + 2] = fmaf(__uint_as_float(raw[i * 4 + 2]), scale2, -kq.z);
-          s[c * 32 + i * 4 + 3] = fmaf(__uint_as_float(raw[i * 4 + 3]), scale2, -kq.w);
-        }
       }
       if (causal && j * kTile == r0) {
         // diagonal tile: key (r0 + c) is visible to query (r0 + r) iff c <= r
 #pragma unroll
         for (int c = 0; c < kTile; ++c)
-          if (c > r) s[c] = -INFINITY;
+          if (c > r) raw[c] = 0xff800000u;   // -inf
       }
 
-      float sub;
+      float sub;   // p = exp2(acc * scale2 - sub)
       if constexpr (kSoftmax) {
-        float mx = s[0];
+        // four independent maxima keep the dependency chains short
+        float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]), mx2 = __uint_as_float(raw[2]),
+              mx3 = __uint_as_float(raw[3]);
 #pragma unroll
-        for (int c = 1; c < kTile; ++c) mx = fmaxf(mx, s[c]);
-        const float m_new = fmaxf(m_used, mx);
+        for (int c = 4; c < kTile; c += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(raw[c + 0]));
+          mx1 = fmaxf(mx1, __uint_as_float(raw[c + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(raw[c + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(raw[c + 3]));
+        }
+        const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale2);
         const bool need = (m_new - m_used) > kRescaleThreshold;
         float alpha = 1.f;
         if (need) {
@@ -301,24 +352,27 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         sub = row_bias;
       }
 
-      float psum = 0.f;
+      const float neg_sub = -sub;
+      float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t packed[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = ex2_approx(s[c * 64 + 2 * i] - sub);
-          const float p1 = ex2_approx(s[c * 64 + 2 * i + 1] - sub);
-          psum += p0 + p1;
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(raw[c * 64 + 2 * i + 0]), scale2, neg_sub));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(raw[c * 64 + 2 * i + 1]), scale2, neg_sub));
+          const float p2 = ex2_approx(fmaf(__uint_as_float(raw[c * 64 + 2 * i + 2]), scale2, neg_sub));
+          const float p3 = ex2_approx(fmaf(__uint_as_float(raw[c * 64 + 2 * i + 3]), scale2, neg_sub));
+          ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
           packed[i] = pack2<kBf16>(p0, p1);
+          packed[i + 1] = pack2<kBf16>(p2, p3);
         }
         tmem_st_x32(tmem_s[t] + lane_sel + c * 32, packed);
       }
-      l_sum += psum;
+      l_sum += (ps0 + ps1) + (ps2 + ps3);
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive_warp(&p_full[t]);
-      if (j + 1 < my_nkt) ksq_buf[((j + 1) & 1) * kTile + r] = ksq_next;
     }
 
     if (ok && my_nkt > 0) {
@@ -344,7 +398,8 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
         fence_proxy_async_smem();
-        ok = group_sync();
+        mbar_arrive_warp(&grp_sync[t]);
+        ok = mbar_wait(&grp_sync[t], 0, abort_flag, status, kSiteGroup);
         if (ok && r == 0) {
           for (int x = 0; x < kBoxes; ++x) tma_store_4d(&tm_o, stage + x * kBoxBytes, x * 64, r0, h, b);
           tma_store_commit();
@@ -353,6 +408,8 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (kSoftmax && row < N) lse[static_cast<int64_t>(bh) * N + row] = m_used + log2f(l_sum);
       }
     }
+  } else {
+    setmaxnreg_dec<kOtherRegs>();   // idle warp of the producer / issuer warpgroup
   }
 
   // ------------------------------------------------------------------ teardown
@@ -364,7 +421,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kMmaWarp) tmem_dealloc(tmem, 512);
+  if (warp == kMmaWarp0) tmem_dealloc(tmem, 512);
 }
 
 }  // namespace fwd
@@ -380,8 +437,8 @@ static cudaError_t launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid((a.N + 2 * kTile - 1) / (2 * kTile), a.B * a.H);
-  kernel<<<grid, fwd::kThreads, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.tm_o, a.ksq, a.qsq, a.lse, a.status, a.H,
-                                                a.N, a.n_pad, a.causal, a.scale2);
+  kernel<<<grid, fwd::kThreads, smem, stream>>>(a.tm_q, a.tm_k, a.tm_v, a.tm_o, a.tm_kslab, a.qsq, a.lse, a.status,
+                                                a.H, a.N, a.n_pad, a.causal, a.scale2, a.slab_w);
   return cudaGetLastError();
 }
 

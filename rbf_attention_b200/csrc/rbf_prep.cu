@@ -22,6 +22,24 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
   return acc;
 }
 
+// fp32 value -> three 16-bit floats whose sum reproduces it to ~24 bits, as one 32-byte slab row (13 zeros follow).
+template <bool kBf16>
+__device__ __forceinline__ void store_slab_row(void* slab, int64_t row, float x) {
+  float hi, mid, lo;
+  if constexpr (kBf16) {
+    hi = __bfloat162float(__float2bfloat16_rn(x));
+    mid = __bfloat162float(__float2bfloat16_rn(x - hi));
+    lo = __bfloat162float(__float2bfloat16_rn(x - hi - mid));
+  } else {
+    hi = __half2float(__float2half_rn(x));
+    mid = __half2float(__float2half_rn(x - hi));
+    lo = __half2float(__float2half_rn(x - hi - mid));
+  }
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(slab) + row * 32);
+  dst[0] = make_uint4(pack2<kBf16>(hi, mid), pack2<kBf16>(lo, 0.f), 0u, 0u);
+  dst[1] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 __device__ __forceinline__ uint4 load_chunk(const void* base, const int64_t* s, int b, int h, int row, int part) {
   return *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + b * s[0] + h * s[1] +
                                          static_cast<int64_t>(row) * s[2] + part * 8);
@@ -72,8 +90,13 @@ __global__ void __launch_bounds__(256) row_stats_kernel(const RowStatsArgs a) {
       if (a.ksq_out != nullptr) a.ksq_out[out_base + row] = valid ? ksq * a.scale : INFINITY;
       if (a.qsq_out != nullptr) a.qsq_out[out_base + row] = valid ? qsq * a.scale : a.qsq_pad;
       if (a.delta_out != nullptr) a.delta_out[out_base + row] = delta;
-      if (a.lse_pad_out != nullptr)
-        a.lse_pad_out[out_base + row] = valid ? a.lse[static_cast<int64_t>(bh) * a.N + row] : INFINITY;
+      float lse = INFINITY;
+      if (a.lse != nullptr && valid) lse = a.lse[static_cast<int64_t>(bh) * a.N + row];
+      if (a.lse_pad_out != nullptr) a.lse_pad_out[out_base + row] = lse;
+      const float inv = 1.0f / (a.scale2 * a.slab_w);
+      if (a.kslab_out != nullptr) store_slab_row<kBf16>(a.kslab_out, out_base + row, valid ? -ksq * a.scale * inv : -a.slab_big);
+      if (a.lslab_out != nullptr) store_slab_row<kBf16>(a.lslab_out, out_base + row, valid ? -lse * inv : -a.slab_big);
+      if (a.dslab_out != nullptr) store_slab_row<kBf16>(a.dslab_out, out_base + row, -delta / a.slab_w);
     }
   }
 }

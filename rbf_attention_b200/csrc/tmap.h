@@ -50,6 +50,21 @@ inline int make_tmap_bhnd(CUtensorMap* out, const void* base, bool bf16, int B, 
   return static_cast<int>(r);
 }
 
+// Tensor map over a contiguous 16-bit (rows_total / n_pad, n_pad, 16) array of "bias slabs": 16 elements (32 bytes)
+// per row, loaded as a 16 x `box_rows` box with the 32-byte swizzle (an extra K = 16 step of an MMA).
+inline int make_tmap_slab16(CUtensorMap* out, const void* base, bool bf16, int BH, int n_pad, int box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return -1;
+  cuuint64_t gdim[3] = {16, static_cast<cuuint64_t>(n_pad), static_cast<cuuint64_t>(BH)};
+  cuuint64_t gstr[2] = {32, static_cast<cuuint64_t>(n_pad) * 32};
+  cuuint32_t box[3] = {16, static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                   const_cast<void*>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return static_cast<int>(r);
+}
+
 // Tensor map over a contiguous fp32 (B, H, N, D) accumulator; box = 32 floats (128 bytes) x `box_rows`.
 inline int make_tmap_f32_bhnd(CUtensorMap* out, const void* base, int B, int H, int N, int D, int box_rows) {
   EncodeTiledFn enc = get_encode_tiled();
