@@ -251,12 +251,14 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     if (!(phases & (RBF_B200_PHASE_MAIN | RBF_B200_PHASE_MAIN2))) return RBF_B200_OK;
     rbf::BwdFusedArgs f{};
     f.tm_q = a.tm_q; f.tm_k = a.tm_k; f.tm_v = a.tm_v; f.tm_do = a.tm_do; f.tm_dk = a.tm_dk; f.tm_dv = a.tm_dv;
-    const int tr = rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, rbf::kTile);
-    if (tr != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the dQ accumulator (code %d)", tr);
+    const int t1 = rbf::make_tmap_slab16(&f.tm_lslab, ws.lslab, bf16, B * H, n_pad, rbf::kTile);
+    const int t2 = rbf::make_tmap_slab16(&f.tm_dslab, ws.dslab, bf16, B * H, n_pad, rbf::kTile);
+    if (t1 != 0 || t2 != 0)
+      return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the bias slabs (codes %d, %d)", t1, t2);
     f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
-    f.ksq = ws.ksq; f.lse_pad = ws.row_bias; f.delta = ws.delta; f.status = ws.status;
+    f.ksq = ws.ksq; f.status = ws.status;
     f.B = B; f.H = H; f.N = N; f.n_pad = n_pad; f.causal = causal ? 1 : 0;
-    f.scale2 = 2.f * c; f.grad_scale = 2.f * sm_scale;
+    f.scale2 = 2.f * c; f.grad_scale = 2.f * sm_scale; f.slab_w = slab_w(bf16);
     e = rbf::launch_bwd_fused(f, bf16, stream);
     if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "backward launch failed: %s", cudaGetErrorString(e));
     return RBF_B200_OK;

@@ -68,17 +68,15 @@ cudaError_t launch_bwd_dq(const BwdArgs& a, bool bf16, int D, bool softmax, cuda
 // Single-kernel softmax backward for head dim 64 (five MMAs per tile pair, dQ through an fp32 accumulator).
 struct BwdFusedArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
-  CUtensorMap tm_dq_acc;  // fp32 (B, H, N, 64) contiguous accumulator, box 32 x 128
-  float* dq_acc;
+  CUtensorMap tm_lslab, tm_dslab;  // (B*H, n_pad, 16) bias slabs of -L / scale2 and -delta, box 16 x 128
+  float* dq_acc;          // fp32 (B, H, N, 64) contiguous accumulator
   void* dq;               // final dQ in the operand type
   int64_t dq_strides[3];
   const float* ksq;       // (B*H, n_pad)
-  const float* lse_pad;   // (B*H, n_pad): base-2 LSE, +inf on padding rows
-  const float* delta;     // (B*H, n_pad)
   DeviceStatus* status;
   int B, H, N, n_pad;
   int causal;
-  float scale2, grad_scale;
+  float scale2, grad_scale, slab_w;
 };
 cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream);
 

@@ -2,40 +2,31 @@
 //
 // A CTA owns 128 keys (K, V resident in shared memory) and streams the query tiles (Q, dO) past them. Per
 // query tile it issues five MMAs - the algorithmic minimum - and evaluates every exponential once:
-//   S^T  = K Q^T                 smem x smem -> TMEM
-//   dP^T = V dO^T                smem x smem -> TMEM
-//   P^T  = exp2(S^T * 2c - ksq[key] - L[query]),   dS^T = P^T * (dP^T - delta[query])     (registers)
-//   dV  += P^T  dO               TMEM x smem   (P^T written back over S^T as 16-bit pairs)
-//   dK  += dS^T Q                TMEM x smem   (dS^T written back over dP^T)
-//   dQ_partial = dS K            smem x smem   (dS^T also stored to shared memory; read as an M-major A operand)
-// dQ_partial leaves the CTA through a TMA reduce-add into an fp32 accumulator in global memory; a small
-// kernel converts it to the output type (times 2g) afterwards. dK gets the norm-gradient term in the
-// epilogue: dK = 2g (acc - rowsum(dS^T)[key] * k).
+//   S^T  = K Q^T  (+ bias slab: -L[query] / scale)        smem x smem -> TMEM
+//   dP^T = V dO^T (+ bias slab: -delta[query])            smem x smem -> TMEM
+//   P^T  = exp2(S^T * 2c - ksq[key]),   dS^T = P^T * dP^T                        (registers)
+//   dV  += P^T  dO               TMEM x smem   (P^T written to TMEM as 16-bit pairs)
+//   dK  += dS^T Q                smem x smem   (dS^T stored to shared memory as a [key][query] tile)
+//   dQ_partial = dS K            smem x smem   (the same tile read as an M-major A operand)
+// The per-query statistics L and delta never pass through registers: the pre-pass stores them as three 16-bit
+// parts per query ("bias slabs") and S^T / dP^T get one extra K = 16 MMA step against a slab of constants.
+// dQ_partial leaves the CTA as fp32 reduce-adds into an accumulator in global memory; a small kernel converts it
+// to the output type (times 2g) afterwards. dK gets the norm-gradient term in the epilogue:
+// dK = 2g (acc - rowsum(dS^T)[key] * k).
 //
-// Roles: warps 0 and 1 MMA issuers (two, because one thread cannot issue the N = 64 products as fast as the tensor
-// pipe retires them), warp 2 TMA producer, warps 4-19 compute (thread = key row; group g owns query columns
-// [32g, 32g+32) of the tile), warps 20-23 drain dQ_partial (thread = query row). The compute warpgroups take
-// registers from the others (setmaxnreg) so that four warps per scheduler hide the MUFU and TMEM latencies.
-// TMEM columns: S^T [0,128), dP^T [128,256), dV [256,320), dK [320,384), dQ_partial x2 [384,512).
+// Roles: warps 0, 1 MMA issuers (one thread cannot issue the N = 64 products as fast as the tensor pipe retires
+// them), warp 2 TMA producer, warps 4-19 compute (thread = key row; group g owns query columns [32g, 32g+32) of the
+// tile), warps 20-23 drain dQ_partial (thread = query row). Compute warpgroups take registers from the others.
+//   issuer A: S^T(n+1) as soon as the compute warps have read S^T(n); dV(n) when P^T(n) is in TMEM
+//   issuer B: dP^T(n+1) as soon as dP^T(n) has been read; dK(n) and dQ_partial(n) when dS^T(n) is in shared memory
+// so the compute warps never wait for an MMA that was not issued a full step ahead.
+// TMEM columns: S^T [0,128), dP^T [128,256), P^T [256,320), dV [320,384), dK [384,448), dQ_partial [448,512).
 #include "common.cuh"
 #include "launch.h"
 
 namespace rbf {
 
 namespace bwdf {
-
-#ifdef RBF_TRACE
-// Bring-up aid (not compiled into the product): clock64 stamps of one CTA's roles per step.
-__device__ long long g_trace[4 * 64 * 16];
-#define RBF_TRACE_EVENT(role, step, ev)                                                              \
-  do {                                                                                               \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (step) < 64) g_trace[((role)*64 + (step)) * 16 + (ev)] = clock64(); \
-  } while (0)
-#else
-#define RBF_TRACE_EVENT(role, step, ev) \
-  do {                                  \
-  } while (0)
-#endif
 
 static constexpr int D = 64;
 static constexpr int kThreads = 768;
@@ -53,41 +44,40 @@ static constexpr int kOtherRegs = 40;
 static_assert(512 * kComputeRegs + 256 * kOtherRegs <= 768 * 80, "setmaxnreg budget");
 
 static constexpr int kTileBytes = kTile * D * 2;    // 16 KB: one 128 x 64 16-bit tile
-static constexpr int kQStages = 3;
-static constexpr int kDoStages = 3;
+static constexpr int kSlabBytes = kTile * 32;       // 4 KB: 128 rows x 16 x 16-bit
+static constexpr int kStages = 3;                   // Q (+ L slab) and dO (+ delta slab) rings
 static constexpr int kDsBytes = kTile * kTile * 2;  // 32 KB: dS^T as [key][query], two 64-query boxes
-static constexpr int kDqStageBytes = kTile * D * 4; // 32 KB: fp32 dQ_partial, two 32-column boxes
 
 struct Smem {
   static constexpr int kK = 0;
   static constexpr int kV = kK + kTileBytes;
   static constexpr int kQ = kV + kTileBytes;
-  static constexpr int kDo = kQ + kQStages * kTileBytes;
-  static constexpr int kDs = kDo + kDoStages * kTileBytes;
-  static constexpr int kDqStage = kDs + kDsBytes;
-  static constexpr int kVec = kDqStage + kDqStageBytes;        // [kQStages][L | delta][128] floats
-  static constexpr int kRowsum = kVec + kQStages * 2 * kTile * 4;  // [4 groups][128] floats: partial row sums
+  static constexpr int kDo = kQ + kStages * kTileBytes;
+  static constexpr int kDs = kDo + kStages * kTileBytes;
+  static constexpr int kLSlab = kDs + kDsBytes;
+  static constexpr int kDSlab = kLSlab + kStages * kSlabBytes;
+  static constexpr int kOnes = kDSlab + kStages * kSlabBytes;
+  static constexpr int kRowsum = kOnes + kSlabBytes;           // [4 groups][128] floats: partial row sums
   static constexpr int kBars = kRowsum + 4 * kTile * 4;
-  static constexpr int kNumBars = 1 + 2 * kQStages + 2 * kDoStages + 1 + 1 + 1 + 1 + 2 + 2 + 1 + 1 + 1 + 1;
+  static constexpr int kNumBars = 1 + 4 * kStages + 11;
   static constexpr int kMisc = kBars + kNumBars * 8;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-static constexpr int kColS = 0, kColDP = 128, kColDV = 256, kColDK = 320, kColDQ = 384;
+static constexpr int kColS = 0, kColDP = 128, kColPT = 256, kColDV = 320, kColDK = 384, kColDQ = 448;
 
 enum Site : uint32_t {
   kSiteKV = 64, kSiteQFull, kSiteDoFull, kSiteQEmpty, kSiteDoEmpty, kSiteSFull, kSiteDPFull, kSitePFull, kSiteDSFull,
-  kSiteDQFull, kSiteDQDrained, kSiteAccDone, kSiteGroup, kSiteDrainGroup, kSiteDsFree
+  kSiteDQFull, kSiteDQDrained, kSiteAccDone, kSiteGroup, kSiteSConsumed, kSiteDPConsumed, kSiteDVDone, kSiteDsFree
 };
 
 struct Params {
   const float* ksq;      // (B*H, n_pad), +inf on padding rows
-  const float* lse_pad;  // (B*H, n_pad), +inf on padding rows
-  const float* delta;    // (B*H, n_pad), zero padded
+  float* dq_acc;         // fp32 (B, H, N, 64), zero-initialised
   DeviceStatus* status;
   int H, N, n_pad, causal;
-  float scale2, grad_scale;
+  float scale2, grad_scale, slab_w;
 };
 
 template <bool kBf16>
@@ -95,7 +85,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                      const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
-                     const __grid_constant__ CUtensorMap tm_dq_acc, const Params p) {
+                     const __grid_constant__ CUtensorMap tm_lslab, const __grid_constant__ CUtensorMap tm_dslab,
+                     const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_k = smem + Smem::kK;
@@ -103,25 +94,27 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   uint8_t* s_q = smem + Smem::kQ;
   uint8_t* s_do = smem + Smem::kDo;
   uint8_t* s_ds = smem + Smem::kDs;
-  uint8_t* s_dq = smem + Smem::kDqStage;
-  float* s_vec = reinterpret_cast<float*>(smem + Smem::kVec);
+  uint8_t* s_lslab = smem + Smem::kLSlab;
+  uint8_t* s_dslab = smem + Smem::kDSlab;
+  uint8_t* s_ones = smem + Smem::kOnes;
   float* s_rowsum = reinterpret_cast<float*>(smem + Smem::kRowsum);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
   uint64_t* kv_full = bars;
-  uint64_t* q_full = kv_full + 1;
-  uint64_t* q_empty = q_full + kQStages;
-  uint64_t* do_full = q_empty + kQStages;
-  uint64_t* do_empty = do_full + kDoStages;
-  uint64_t* s_full = do_empty + kDoStages;
-  uint64_t* dp_full = s_full + 1;
-  uint64_t* p_full = dp_full + 1;
-  uint64_t* ds_full = p_full + 1;
-  uint64_t* dq_full = ds_full + 1;       // [2]  dQ_partial buffer written (also: dS^T shared tile consumed)
-  uint64_t* dq_drained = dq_full + 2;    // [2]  drain group has copied the buffer out of TMEM
-  uint64_t* acc_done = dq_drained + 2;
-  uint64_t* grp_sync = acc_done + 1;     // compute groups (256 threads)
-  uint64_t* drain_sync = grp_sync + 1;   // drain group (128 threads)
-  uint64_t* dbg_bar = drain_sync + 1;    // bring-up only
+  uint64_t* q_full = kv_full + 1;            // [kStages] Q tile + L slab landed
+  uint64_t* q_empty = q_full + kStages;      // two arrivals: S^T (issuer A) and dK (issuer B) have completed
+  uint64_t* do_full = q_empty + kStages;     // dO tile + delta slab landed
+  uint64_t* do_empty = do_full + kStages;    // two arrivals: dV (issuer A) and dP^T (issuer B)
+  uint64_t* s_full = do_empty + kStages;     // S^T(n) complete
+  uint64_t* s_consumed = s_full + 1;         // compute warps hold S^T(n) in registers
+  uint64_t* dp_full = s_consumed + 1;
+  uint64_t* dp_consumed = dp_full + 1;
+  uint64_t* p_full = dp_consumed + 1;        // P^T(n) stored to TMEM
+  uint64_t* dv_done = p_full + 1;            // dV(n) complete: the P^T columns may be overwritten
+  uint64_t* ds_full = dv_done + 1;           // dS^T(n) stored to shared memory
+  uint64_t* dq_full = ds_full + 1;           // dK(n) and dQ_partial(n) complete: dS^T tile free, dQ_partial readable
+  uint64_t* dq_drained = dq_full + 1;        // drain warps have read dQ_partial(n) out of TMEM
+  uint64_t* acc_done = dq_drained + 1;       // two arrivals: all MMAs of both issuers complete
+  uint64_t* grp_sync = acc_done + 1;         // compute warps (16 arrivals)
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + Smem::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 4);
 
@@ -143,37 +136,46 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
 
   if (tid == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < kQStages; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
-    for (int s = 0; s < kDoStages; ++s) { mbar_init(&do_full[s], 1); mbar_init(&do_empty[s], 1); }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 2);
+      mbar_init(&do_full[s], 1);
+      mbar_init(&do_empty[s], 2);
+    }
     mbar_init(s_full, 1);
+    mbar_init(s_consumed, kNumComputeWarps);   // one arrival per warp
     mbar_init(dp_full, 1);
-    mbar_init(p_full, kNumComputeWarps);      // one arrival per warp
+    mbar_init(dp_consumed, kNumComputeWarps);
+    mbar_init(p_full, kNumComputeWarps);
+    mbar_init(dv_done, 1);
     mbar_init(ds_full, kNumComputeWarps);
-    mbar_init(&dq_full[0], 1);
-    mbar_init(&dq_full[1], 1);
-    mbar_init(&dq_drained[0], 4);
-    mbar_init(&dq_drained[1], 4);
-    mbar_init(acc_done, 2);                   // one commit from each MMA issuer
+    mbar_init(dq_full, 1);
+    mbar_init(dq_drained, 4);
+    mbar_init(acc_done, 2);
     mbar_init(grp_sync, kNumComputeWarps);
-    mbar_init(drain_sync, 4);
-    mbar_init(dbg_bar, 1);
     fence_mbar_init();
   }
   if (warp == kMmaWarpA) {
     tmem_alloc(tmem_base_s, 512);
     tmem_relinquish();
   }
+  if (tid < kTile) {
+    // slab of constants (A operand of the bias-slab MMA steps): rows [w, w, w, 0 x5 | w, w, w, 0 x5]
+    const uint4 v = make_uint4(pack2<kBf16>(p.slab_w, p.slab_w), pack2<kBf16>(p.slab_w, 0.f), 0u, 0u);
+    *reinterpret_cast<uint4*>(s_ones + tid * 32) = v;
+    *reinterpret_cast<uint4*>(s_ones + tid * 32 + 16) = v;
+    fence_proxy_async_smem();
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_base_s;
-  // Register re-allocation is issued at the top of each role's branch (whole warpgroups take the same branch
-  // class: warps 0-3 issuer / producer / idle, 4-19 compute, 20-23 drain).
+
   if (warp < kComputeWarp0) {
     setmaxnreg_dec<kOtherRegs>();
   }
-  if (warp > kLoadWarp && warp < kComputeWarp0) {
-    // idle warps of the first warpgroup
+  if (warp == 3) {
+    // idle warp of the first warpgroup
   } else if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -181,138 +183,131 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_lslab);
+      tma_prefetch_desc(&tm_dslab);
       mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
       tma_load_4d(s_k, &tm_k, kv_full, 0, k_row0, h, b);
       tma_load_4d(s_v, &tm_v, kv_full, 0, k_row0, h, b);
       for (int n = 0; n < cnt; ++n) {
         const int row0 = (first + n) * kTile;
-        const int sq = n % kQStages, sd = n % kDoStages;
-        if (n >= kQStages && !mbar_wait(&q_empty[sq], ((n / kQStages) - 1) & 1, abort_flag, p.status, kSiteQEmpty))
-          break;
-        RBF_TRACE_EVENT(1, n, 4);
-        mbar_arrive_expect_tx(&q_full[sq], kTileBytes + 2 * kTile * 4);
-        tma_load_4d(s_q + sq * kTileBytes, &tm_q, &q_full[sq], 0, row0, h, b);
-        // this query tile's L and delta ride on the same barrier (row pitch n_pad keeps them 16-byte aligned)
-        bulk_load_1d(s_vec + sq * 2 * kTile, p.lse_pad + static_cast<int64_t>(bh) * p.n_pad + row0, kTile * 4,
-                     &q_full[sq]);
-        bulk_load_1d(s_vec + sq * 2 * kTile + kTile, p.delta + static_cast<int64_t>(bh) * p.n_pad + row0, kTile * 4,
-                     &q_full[sq]);
-        if (n >= kDoStages && !mbar_wait(&do_empty[sd], ((n / kDoStages) - 1) & 1, abort_flag, p.status, kSiteDoEmpty))
-          break;
-        RBF_TRACE_EVENT(1, n, 5);
-        mbar_arrive_expect_tx(&do_full[sd], kTileBytes);
-        tma_load_4d(s_do + sd * kTileBytes, &tm_do, &do_full[sd], 0, row0, h, b);
+        const int st = n % kStages;
+        const uint32_t par = ((n / kStages) - 1) & 1;
+        if (n >= kStages && !mbar_wait(&q_empty[st], par, abort_flag, p.status, kSiteQEmpty)) break;
+        mbar_arrive_expect_tx(&q_full[st], kTileBytes + kSlabBytes);
+        tma_load_4d(s_q + st * kTileBytes, &tm_q, &q_full[st], 0, row0, h, b);
+        tma_load_3d(s_lslab + st * kSlabBytes, &tm_lslab, &q_full[st], 0, row0, bh);
+        if (n >= kStages && !mbar_wait(&do_empty[st], par, abort_flag, p.status, kSiteDoEmpty)) break;
+        mbar_arrive_expect_tx(&do_full[st], kTileBytes + kSlabBytes);
+        tma_load_4d(s_do + st * kTileBytes, &tm_do, &do_full[st], 0, row0, h, b);
+        tma_load_3d(s_dslab + st * kSlabBytes, &tm_dslab, &do_full[st], 0, row0, bh);
       }
     }
   } else if (warp == kMmaWarpA || warp == kMmaWarpB) {
     // ------------------------------------------------------------------ MMA issuers
-    // One thread sustains about one tcgen05.mma per 58 cycles, which is slower than the tensor pipe retires the
-    // N = 64 products (32 cycles each), so the five MMAs of a step are split over two issuing threads such that
-    // every ordering the TMEM aliasing needs stays inside one thread's in-order stream:
-    //   issuer A: dV(n) (reads P^T from the S^T columns), then S^T(n+1) (overwrites them)
-    //   issuer B: dK(n) (reads dS^T from the dP^T columns), then dP^T(n+1) (overwrites them), then dQ_partial(n)
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(kTile, kTile, kBf16, false, false);  // keys x queries, both K-major
-      constexpr uint32_t idesc_acc = make_idesc(kTile, D, kBf16, false, true);     // A from TMEM, B N-major
+      constexpr uint32_t idesc_acc = make_idesc(kTile, D, kBf16, false, true);     // A K-major (or TMEM), B N-major
       constexpr uint32_t idesc_dq = make_idesc(kTile, D, kBf16, true, true);       // A M-major (dS^T tile), B N-major
-      auto stage_of = [](SmemDesc d, int stage) {
-        d.lo += static_cast<uint32_t>(stage) * (kTileBytes >> 4);
+      const SmemDesc ones_desc = make_sdesc_slab32(smem_u32(s_ones));
+      auto stage_of = [](SmemDesc d, int stage, uint32_t stage_bytes) {
+        d.lo += static_cast<uint32_t>(stage) * (stage_bytes >> 4);
         return d;
       };
-      auto issue_kmajor = [&](uint32_t dst, const SmemDesc& a_desc, const SmemDesc& b_desc) {
+      // dst = A B^T over D (both K-major) plus the bias-slab step: dst[m][n] += w * (slab[n] hi + mid + lo)
+      auto issue_scores = [&](uint32_t dst, const SmemDesc& a_desc, const SmemDesc& b_desc, const SmemDesc& slab) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           umma_ss(dst, sdesc_at(a_desc, kk * 32), sdesc_at(b_desc, kk * 32), idesc_s, kk > 0);
-      };
-      // A: 16-bit pairs in TMEM; group g's 32 queries live at columns [32g, 32g+16) of the region
-      auto issue_acc = [&](uint32_t dst, uint32_t a_region, const SmemDesc& b_desc, uint32_t accumulate) {
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
-          umma_ts(dst, a_region + a_col, sdesc_at(b_desc, kk * 2048), idesc_acc, kk > 0 ? 1u : accumulate);
-        }
+        umma_ss(dst, sdesc_at(ones_desc, 0), sdesc_at(slab, 0), idesc_s, 1u);
       };
       auto wait_q = [&](int n) {
-        return mbar_wait(&q_full[n % kQStages], (n / kQStages) & 1, abort_flag, p.status, kSiteQFull);
+        return mbar_wait(&q_full[n % kStages], (n / kStages) & 1, abort_flag, p.status, kSiteQFull);
       };
       auto wait_do = [&](int n) {
-        return mbar_wait(&do_full[n % kDoStages], (n / kDoStages) & 1, abort_flag, p.status, kSiteDoFull);
+        return mbar_wait(&do_full[n % kStages], (n / kStages) & 1, abort_flag, p.status, kSiteDoFull);
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kSiteKV);
 
       if (warp == kMmaWarpA) {
         const SmemDesc k_kmaj = make_sdesc_parts(smem_u32(s_k), 16, 1024);
         const SmemDesc q_kmaj0 = make_sdesc_parts(smem_u32(s_q), 16, 1024);
+        const SmemDesc lslab0 = make_sdesc_slab32(smem_u32(s_lslab));
         const SmemDesc do_nmaj0 = make_sdesc_parts(smem_u32(s_do), kTile * 128, 1024);
         if (ok) ok = wait_q(0);
         if (ok) {
           tc_fence_after_sync();
-          issue_kmajor(tmem + kColS, k_kmaj, q_kmaj0);
+          issue_scores(tmem + kColS, k_kmaj, q_kmaj0, lslab0);
           umma_commit(s_full);
+          umma_commit(&q_empty[0]);
         }
         for (int n = 0; n < cnt && ok; ++n) {
-          // dV += P^T dO
-          RBF_TRACE_EVENT(0, n, 0);
-          ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
-          if (!ok) break;
-          RBF_TRACE_EVENT(0, n, 1);
-          tc_fence_after_sync();
-          issue_acc(tmem + kColDV, tmem + kColS, stage_of(do_nmaj0, n % kDoStages), n > 0 ? 1u : 0u);
-          umma_commit(&do_empty[n % kDoStages]);   // dO(n)'s other reader, dP^T(n), completed before P^T(n) existed
-          RBF_TRACE_EVENT(0, n, 5);
           if (n + 1 < cnt) {
-            ok = wait_q(n + 1);
+            // S^T(n+1) may overwrite S^T(n) as soon as every compute warp holds it in registers
+            const int st = (n + 1) % kStages;
+            ok = wait_q(n + 1) && mbar_wait(s_consumed, n & 1, abort_flag, p.status, kSiteSConsumed);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_kmajor(tmem + kColS, k_kmaj, stage_of(q_kmaj0, (n + 1) % kQStages));
+            issue_scores(tmem + kColS, k_kmaj, stage_of(q_kmaj0, st, kTileBytes), stage_of(lslab0, st, kSlabBytes));
             umma_commit(s_full);
+            umma_commit(&q_empty[st]);
           }
-          RBF_TRACE_EVENT(0, n, 6);
+          // dV += P^T dO
+          ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const SmemDesc do_n = stage_of(do_nmaj0, n % kStages, kTileBytes);
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ts(tmem + kColDV, tmem + kColPT + kk * 8, sdesc_at(do_n, kk * 2048), idesc_acc,
+                    (n > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(dv_done);
+          umma_commit(&do_empty[n % kStages]);
         }
       } else {
         const SmemDesc v_kmaj = make_sdesc_parts(smem_u32(s_v), 16, 1024);
-        const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
-        const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);
         const SmemDesc do_kmaj0 = make_sdesc_parts(smem_u32(s_do), 16, 1024);
+        const SmemDesc dslab0 = make_sdesc_slab32(smem_u32(s_dslab));
+        const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
         const SmemDesc q_nmaj0 = make_sdesc_parts(smem_u32(s_q), kTile * 128, 1024);
+        const SmemDesc ds_kmaj = make_sdesc_parts(smem_u32(s_ds), 16, 1024);            // rows = keys, K = queries
+        const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);   // rows = reduction (keys)
         if (ok) ok = wait_do(0);
         if (ok) {
           tc_fence_after_sync();
-          issue_kmajor(tmem + kColDP, v_kmaj, do_kmaj0);
+          issue_scores(tmem + kColDP, v_kmaj, do_kmaj0, dslab0);
           umma_commit(dp_full);
+          umma_commit(&do_empty[0]);
         }
         for (int n = 0; n < cnt && ok; ++n) {
-          // dK += dS^T Q
-          RBF_TRACE_EVENT(1, n, 8);
+          if (n + 1 < cnt) {
+            const int st = (n + 1) % kStages;
+            ok = wait_do(n + 1) && mbar_wait(dp_consumed, n & 1, abort_flag, p.status, kSiteDPConsumed);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_scores(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, st, kTileBytes), stage_of(dslab0, st, kSlabBytes));
+            umma_commit(dp_full);
+            umma_commit(&do_empty[st]);
+          }
+          // dK += dS^T Q : A = dS^T tile (K-major: 64-query boxes of 128-byte rows), B = Q read N-major
           ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
           if (!ok) break;
-          RBF_TRACE_EVENT(1, n, 9);
           tc_fence_after_sync();
-          issue_acc(tmem + kColDK, tmem + kColDP, stage_of(q_nmaj0, n % kQStages), n > 0 ? 1u : 0u);
-          umma_commit(&q_empty[n % kQStages]);     // Q(n)'s other reader, S^T(n), completed before dS^T(n) existed
-          RBF_TRACE_EVENT(1, n, 10);
-          if (n + 1 < cnt) {
-            ok = wait_do(n + 1);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_kmajor(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, (n + 1) % kDoStages));
-            umma_commit(dp_full);
-          }
-          RBF_TRACE_EVENT(1, n, 11);
-          // dQ_partial = dS K : A = dS^T tile read M-major (rows = keys = reduction index), B = K read N-major
-          if (n >= 2) {
-            ok = mbar_wait(&dq_drained[n & 1], ((n - 2) >> 1) & 1, abort_flag, p.status, kSiteDQDrained);
-            if (!ok) break;
-            tc_fence_after_sync();
-          }
-          RBF_TRACE_EVENT(1, n, 12);
+          const SmemDesc q_n = stage_of(q_nmaj0, n % kStages, kTileBytes);
 #pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk) {
-            umma_ss(tmem + kColDQ + (n & 1) * D, sdesc_at(ds_mmaj, kk * 2048), sdesc_at(k_nmaj, kk * 2048), idesc_dq,
-                    kk > 0);
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ss(tmem + kColDK, sdesc_at(ds_kmaj, (kk >> 2) * (kTile * 128) + (kk & 3) * 32), sdesc_at(q_n, kk * 2048),
+                    idesc_acc, (n > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&q_empty[n % kStages]);
+          // dQ_partial = dS K : A = the same tile read M-major (rows = keys = reduction index), B = K read N-major
+          if (n > 0) {
+            ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained);
+            if (!ok) break;
+            tc_fence_after_sync();
           }
-          umma_commit(&dq_full[n & 1]);
-          RBF_TRACE_EVENT(1, n, 13);
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ss(tmem + kColDQ, sdesc_at(ds_mmaj, kk * 2048), sdesc_at(k_nmaj, kk * 2048), idesc_dq, kk > 0);
+          umma_commit(dq_full);
         }
       }
       if (ok) umma_commit(acc_done);   // both issuers arrive: the barrier counts two
@@ -322,49 +317,37 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     setmaxnreg_dec<kOtherRegs>();
     const int r = tid - kDrainWarp0 * 32;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint32_t phase = 0;
     bool ok = true;
-    auto drain_group_sync = [&]() -> bool {
-      mbar_arrive_warp(drain_sync);
-      const bool done = mbar_wait(drain_sync, phase & 1, abort_flag, p.status, kSiteDrainGroup);
-      ++phase;
-      return done;
-    };
     for (int n = 0; n < cnt; ++n) {
-      if (r == 0) RBF_TRACE_EVENT(1, n, 0);
-      ok = mbar_wait(&dq_full[n & 1], (n >> 1) & 1, abort_flag, p.status, kSiteDQFull);
+      ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull);
       if (!ok) break;
-      if (r == 0) RBF_TRACE_EVENT(1, n, 1);
       tc_fence_after_sync();
+      const int q_row = (first + n) * kTile + r;
+      float* dst = p.dq_acc + (static_cast<int64_t>(bh) * p.N + q_row) * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(tmem + kColDQ + (n & 1) * D + lane_sel + c * 32, v);
+      for (int c = 0; c < D / 16; ++c) {
+        uint32_t v[16];
+        tmem_ld_x16(tmem + kColDQ + lane_sel + c * 16, v);
         tmem_ld_wait();
+        if (c == D / 16 - 1) {
+          // the whole row is in registers (or already on its way): the next dQ_partial MMA may overwrite TMEM
+          tc_fence_before_sync();
+          mbar_arrive_warp(dq_drained);
+        }
+#ifndef RBF_SKIP_DQ_RED
+        if (q_row < p.N) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<uint4*>(s_dq + c * (kTile * 128) + sw128_offset(r, g)) =
-              make_uint4(v[g * 4 + 0], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-      }
-      tc_fence_before_sync();
-      mbar_arrive_warp(&dq_drained[n & 1]);
-      fence_proxy_async_smem();
-      ok = drain_group_sync();
-      if (!ok) break;
-      if (r == 0) {
-        const int row0 = (first + n) * kTile;
-#ifndef RBF_SKIP_DQ_REDUCE
-        tma_reduce_add_4d(&tm_dq_acc, s_dq, 0, row0, h, b);
-        tma_reduce_add_4d(&tm_dq_acc, s_dq + kTile * 128, 32, row0, h, b);
+          for (int g = 0; g < 4; ++g)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 16 + g * 4),
+                         "f"(__uint_as_float(v[g * 4 + 0])), "f"(__uint_as_float(v[g * 4 + 1])),
+                         "f"(__uint_as_float(v[g * 4 + 2])), "f"(__uint_as_float(v[g * 4 + 3]))
+                         : "memory");
+        }
+#else
+        if (q_row < 0) dst[c] = __uint_as_float(v[0]);
 #endif
-        tma_store_commit();
-        tma_store_wait_read();     // the staging tile may be overwritten once the bulk engine has read it
       }
-      ok = drain_group_sync();
-      if (!ok) break;
-      if (r == 0) RBF_TRACE_EVENT(1, n, 2);
     }
-    if (r == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ compute groups (thread = key row)
     setmaxnreg_inc<kComputeRegs>();
@@ -376,34 +359,19 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     bool ok = true;
 
     for (int n = 0; n < cnt; ++n) {
-      const int sq = n % kQStages;
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 0);
-      ok = mbar_wait(&q_full[sq], (n / kQStages) & 1, abort_flag, p.status, kSiteQFull) &&
-           mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
+      ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
       if (!ok) break;
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 2);
       tc_fence_after_sync();
-      const float4* l4 = reinterpret_cast<const float4*>(s_vec + sq * 2 * kTile + g * 32);
-      const float4* d4 = reinterpret_cast<const float4*>(s_vec + sq * 2 * kTile + kTile + g * 32);
-
       float pr[32];
       {
         uint32_t raw[32];
         tmem_ld_x32(tmem + kColS + lane_sel + g * 32, raw);
         tmem_ld_wait();
-        if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 6);
+        tc_fence_before_sync();
+        mbar_arrive_warp(s_consumed);
+        // acc = k.q - L / scale2 ; P = exp2(acc * scale2 - ksq)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-#ifdef RBF_NO_VEC_LDS
-          const float4 lv = make_float4(neg_ksq, neg_ksq, neg_ksq, neg_ksq);
-#else
-          const float4 lv = l4[i];
-#endif
-          pr[i * 4 + 0] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 0]), p.scale2, neg_ksq) - lv.x);
-          pr[i * 4 + 1] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 1]), p.scale2, neg_ksq) - lv.y);
-          pr[i * 4 + 2] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 2]), p.scale2, neg_ksq) - lv.z);
-          pr[i * 4 + 3] = ex2_approx(fmaf(__uint_as_float(raw[i * 4 + 3]), p.scale2, neg_ksq) - lv.w);
-        }
+        for (int i = 0; i < 32; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(raw[i]), p.scale2, neg_ksq));
       }
       if (p.causal && n == 0) {
         // diagonal tile: query column (32g + c) sees key row r iff column >= row
@@ -415,58 +383,52 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) packed[i] = pack2<kBf16>(pr[2 * i], pr[2 * i + 1]);
-        if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 7);
-        tmem_st_x16(tmem + kColS + lane_sel + g * 32, packed);
+        // the P^T columns are free once dV of the previous step has completed
+        if (n > 0) {
+          ok = mbar_wait(dv_done, (n - 1) & 1, abort_flag, p.status, kSiteDVDone);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+        tmem_st_x16(tmem + kColPT + lane_sel + g * 16, packed);
         tmem_st_wait();
-        if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 8);
         tc_fence_before_sync();
         mbar_arrive_warp(p_full);
       }
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 3);
 
       ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull);
-      // the dS^T shared tile is free once the previous dQ_partial MMA has completed
-      if (ok && n > 0) ok = mbar_wait(&dq_full[(n - 1) & 1], ((n - 1) >> 1) & 1, abort_flag, p.status, kSiteDsFree);
       if (!ok) break;
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 4);
       tc_fence_after_sync();
       uint32_t ds_packed[16];
       {
         uint32_t raw[32];
         tmem_ld_x32(tmem + kColDP + lane_sel + g * 32, raw);
         tmem_ld_wait();
-        if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 9);
+        tc_fence_before_sync();
+        mbar_arrive_warp(dp_consumed);
+        // acc = v.dO - delta ; dS = P * acc
+        float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-#ifdef RBF_NO_VEC_LDS
-          const float4 dl = make_float4(neg_ksq, neg_ksq, neg_ksq, neg_ksq);
-#else
-          const float4 dl = d4[i];
-#endif
-          const float d0 = pr[i * 4 + 0] * (__uint_as_float(raw[i * 4 + 0]) - dl.x);
-          const float d1 = pr[i * 4 + 1] * (__uint_as_float(raw[i * 4 + 1]) - dl.y);
-          const float d2 = pr[i * 4 + 2] * (__uint_as_float(raw[i * 4 + 2]) - dl.z);
-          const float d3 = pr[i * 4 + 3] * (__uint_as_float(raw[i * 4 + 3]) - dl.w);
-          ds_rowsum += (d0 + d1) + (d2 + d3);
-          ds_packed[i * 2 + 0] = pack2<kBf16>(d0, d1);
-          ds_packed[i * 2 + 1] = pack2<kBf16>(d2, d3);
+        for (int i = 0; i < 16; ++i) {
+          const float d0 = pr[2 * i] * __uint_as_float(raw[2 * i]);
+          const float d1 = pr[2 * i + 1] * __uint_as_float(raw[2 * i + 1]);
+          rs0 += d0;
+          rs1 += d1;
+          ds_packed[i] = pack2<kBf16>(d0, d1);
         }
+        ds_rowsum += rs0 + rs1;
       }
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 10);
-      tmem_st_x16(tmem + kColDP + lane_sel + g * 32, ds_packed);
-      // the same values to shared memory: row r of the [key][query] tile, box g/2, 16-byte chunks 4(g%2) .. +3
+      // the dS^T tile is free once dK and dQ_partial of the previous step have completed
+      if (n > 0) {
+        ok = mbar_wait(dq_full, (n - 1) & 1, abort_flag, p.status, kSiteDsFree);
+        if (!ok) break;
+      }
+      // row r of the [key][query] tile, box g/2, 16-byte chunks 4(g%2) .. +3
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch)
         *reinterpret_cast<uint4*>(s_ds + (g >> 1) * (kTile * 128) + sw128_offset(r, (g & 1) * 4 + ch)) =
             make_uint4(ds_packed[ch * 4 + 0], ds_packed[ch * 4 + 1], ds_packed[ch * 4 + 2], ds_packed[ch * 4 + 3]);
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 11);
-      tmem_st_wait();
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 12);
       fence_proxy_async_smem();
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 13);
-      tc_fence_before_sync();
       mbar_arrive_warp(ds_full);
-      if (r == 0) RBF_TRACE_EVENT(2 + (g & 1), n, 5);
     }
 
     uint32_t grp_phase = 0;
@@ -566,11 +528,11 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
   cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, stream);
   if (e != cudaSuccess) return e;
   Params p{};
-  p.ksq = a.ksq; p.lse_pad = a.lse_pad; p.delta = a.delta; p.status = a.status;
+  p.ksq = a.ksq; p.dq_acc = a.dq_acc; p.status = a.status;
   p.H = a.H; p.N = a.N; p.n_pad = a.n_pad; p.causal = a.causal;
-  p.scale2 = a.scale2; p.grad_scale = a.grad_scale;
+  p.scale2 = a.scale2; p.grad_scale = a.grad_scale; p.slab_w = a.slab_w;
   dim3 grid((a.N + kTile - 1) / kTile, a.B * a.H);
-  kernel<<<grid, kThreads, smem, stream>>>(a.tm_k, a.tm_v, a.tm_q, a.tm_do, a.tm_dk, a.tm_dv, a.tm_dq_acc, p);
+  kernel<<<grid, kThreads, smem, stream>>>(a.tm_k, a.tm_v, a.tm_q, a.tm_do, a.tm_dk, a.tm_dv, a.tm_lslab, a.tm_dslab, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int64_t chunks = static_cast<int64_t>(a.B) * a.H * a.N * 8;
@@ -580,12 +542,6 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace bwdf
-
-#ifdef RBF_TRACE
-extern "C" int rbf_b200_debug_read_trace(long long* host, int count) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, bwdf::g_trace, sizeof(long long) * count));
-}
-#endif
 
 cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream) {
   return bf16 ? bwdf::launch_t<true>(a, stream) : bwdf::launch_t<false>(a, stream);
