@@ -98,6 +98,28 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
                         const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides, int dtype,
                         int causal, int softmax, float sm_scale, void* stream, int phases);
 
+/* Forward for callers that cannot hand over device memory of their own. It has no counterpart in the reference,
+ * whose launchers allocate freely through torch. Some hosts of this library cannot do that: a plug-in running
+ * inside an engine that owns all device memory and forbids allocation after start-up, a real-time or serving loop
+ * where cudaMalloc's implicit device synchronisation is not acceptable, or a thin foreign-function caller that has
+ * no allocator at hand for the few megabytes of scratch. For them the scratch of the forward (status word, key-norm
+ * bias slabs, and the query norms of the non-softmax variant) lives in a fixed array of
+ * RBF_B200_STATIC_SCRATCH_BYTES inside the library's device image; every GPU that loads the library keeps it
+ * reserved until the process exits. The call makes no cudaMalloc / cudaFree and calls nothing that allocates.
+ *   - Problems whose scratch (rbf_b200_workspace_bytes(..., backward = 0)) exceeds the array are refused with
+ *     RBF_B200_ERR_WORKSPACE; configuration 2 of the benchmark (B8 H16 N4096) just fits.
+ *   - The first call on each device looks up the array's device address (with that device current); make that
+ *     first call outside any stream capture.
+ *   - All calls share the one array, and it keeps what the last call left. Each call rewrites everything it
+ *     later reads, so consecutive calls on one stream are independent; two calls that may run on the GPU at the
+ *     same time (different streams, different host threads) race on it and must not be made.
+ * Inputs, outputs and all other arguments are those of rbf_b200_fwd. */
+#define RBF_B200_STATIC_SCRATCH_BYTES (20u * 1024u * 1024u)
+size_t rbf_b200_static_scratch_bytes(void);
+int rbf_b200_fwd_static(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int N, int D,
+                        const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                        const int64_t* o_strides, int dtype, int causal, int softmax, float sm_scale, void* stream);
+
 /* Synchronises `stream` and reads the device status word that the last call using `workspace` left:
  * 0 = ok, otherwise (site << 24 | block) of the bounded wait that ran out. Returns RBF_B200_ERR_DEVICE
  * when the word is non-zero. No counterpart in the reference (its kernels have no device-side waits). */

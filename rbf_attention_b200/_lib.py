@@ -50,6 +50,12 @@ SIGNATURES = {
         [ctypes.c_void_p] * 10 + [ctypes.c_size_t] + [ctypes.c_int] * 4 + [_c_i64p] * 8
         + [ctypes.c_int] * 3 + [ctypes.c_float, ctypes.c_void_p, ctypes.c_int],
     ),
+    "rbf_b200_static_scratch_bytes": (ctypes.c_size_t, []),
+    "rbf_b200_fwd_static": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 5 + [ctypes.c_int] * 4 + [_c_i64p] * 4 + [ctypes.c_int] * 3
+        + [ctypes.c_float, ctypes.c_void_p],
+    ),
     "rbf_b200_read_device_status": (
         ctypes.c_int,
         [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint)],

@@ -293,6 +293,59 @@ int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, c
                              causal, softmax, sm_scale, stream_v, RBF_B200_PHASE_ALL);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Forward without a caller-provided workspace: the scratch lives in a fixed device array of this library.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = RBF_B200_STATIC_SCRATCH_BYTES;
+// Reserved on every GPU that loads the library, until the process exits. In host code this name is only a
+// handle: the device address has to be asked for with cudaGetSymbolAddress (below), never taken with '&'.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device; looked up once per device.
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(RBF_B200_ERR_BAD_ARGUMENT, "device index %d is out of range", dev);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(RBF_B200_ERR_LAUNCH, "cudaGetSymbolAddress failed for the static scratch: %s", cudaGetErrorString(e));
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace
+
+size_t rbf_b200_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int rbf_b200_fwd_static(const void* q, const void* k, const void* v, void* out, float* lse, int B, int H, int N, int D,
+                        const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                        const int64_t* o_strides, int dtype, int causal, int softmax, float sm_scale, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_common(B, H, N, D, dtype, sm_scale))) return rc;
+  const size_t need = carve(nullptr, B, H, N, D, softmax, 0).bytes;
+  if (need > kStaticScratchBytes)
+    return fail(RBF_B200_ERR_WORKSPACE,
+                "problem needs %zu bytes of scratch but the built-in scratch holds %zu: use rbf_b200_fwd with a "
+                "caller-provided workspace", need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  if ((rc = static_scratch_for_current_device(&scratch))) return rc;
+  // The pre-pass rewrites every scratch word the main kernel reads and clears the status word, so nothing of an
+  // earlier call leaks into this one.
+  return rbf_b200_fwd_phases(q, k, v, out, lse, scratch, kStaticScratchBytes, B, H, N, D, q_strides, k_strides,
+                             v_strides, o_strides, dtype, causal, softmax, sm_scale, stream_v, RBF_B200_PHASE_ALL);
+}
+
 int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned int* code) {
   g_last_error[0] = 0;
   if (workspace == nullptr || code == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "workspace or code is NULL");
