@@ -258,12 +258,14 @@ def run_ours(args, w, rank, world, local_rank):
     with ClockSampler(local_rank) as clocks:
         ms = time_loop(torch, runner.step, args.steps)
         # per-kernel times for the roofline line (same buffers, same stream)
-        phase_ms = {
-            "fwd": time_loop(torch, lambda: runner.fwd(2), args.steps),
-            "bwd_dkdv": time_loop(torch, lambda: runner.bwd(2), args.steps),
-            "bwd_dq": time_loop(torch, lambda: runner.bwd(4), args.steps),
-            "prepass": time_loop(torch, lambda: (runner.fwd(1), runner.bwd(1)), args.steps),
-        }
+        fused = w["softmax"] and w["D"] == 64     # single-kernel backward (plus memset and dQ convert)
+        phase_ms = {"fwd": time_loop(torch, lambda: runner.fwd(2), args.steps)}
+        if fused:
+            phase_ms["bwd_fused"] = time_loop(torch, lambda: runner.bwd(2), args.steps)
+        else:
+            phase_ms["bwd_dkdv"] = time_loop(torch, lambda: runner.bwd(2), args.steps)
+            phase_ms["bwd_dq"] = time_loop(torch, lambda: runner.bwd(4), args.steps)
+        phase_ms["prepass"] = time_loop(torch, lambda: (runner.fwd(1), runner.bwd(1)), args.steps)
     barrier()
     runner.check_status()
     t = torch.tensor([ms], device=device, dtype=torch.float64)
@@ -303,7 +305,8 @@ def run_ours(args, w, rank, world, local_rank):
         peak, peak_src = measured_peaks()
         # dominant kernel: algorithmic GEMMs per launch - forward 2 (S, PV); dK/dV kernel 4 (S, dP, dV, dK);
         # dQ kernel 1 (dQ; its S and dP are recomputation and are not counted)
-        gemms = {"fwd": 2, "bwd_dkdv": 4, "bwd_dq": 1}
+        # single-kernel backward: all 5
+        gemms = {"fwd": 2, "bwd_fused": 5} if fused else {"fwd": 2, "bwd_dkdv": 4, "bwd_dq": 1}
         dom = max(gemms, key=lambda n: phase_ms[n])
         unit_flops = 2.0 * w["B"] * w["H"] * float(w["N"]) ** 2 * w["D"] * (0.5 if w["causal"] else 1.0)
         achieved = gemms[dom] * unit_flops / (phase_ms[dom] * 1e-3) / 1e12
@@ -326,8 +329,8 @@ def run_ours(args, w, rank, world, local_rank):
                                        f"{pair_s:.2f} s per pair), scaled by FLOPs"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * tensor_bytes,
                     "d2h_bytes_per_step": 4 * tensor_bytes, "ms_per_step": t.item(), "steps": e2e_steps},
-            # per step: forward = norm pre-pass(es) + main; backward = norm pre-pass(es) [+ delta] + dK/dV + dQ
-            "gpu_launches": (6 if w["softmax"] else 7) * args.steps,
+            # per step: forward = pre-pass + main; backward = pre-pass + (single kernel + dQ convert | dK/dV + dQ)
+            "gpu_launches": 5 * args.steps,
             "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
