@@ -28,6 +28,19 @@ namespace rbf {
 
 namespace bwdf {
 
+#ifdef RBF_TRACE
+// Bring-up aid (not compiled into the product): clock64 stamps of one CTA's roles per step.
+__device__ long long g_trace[4 * 64 * 16];
+#define RBF_TRACE_EVENT(role, step, ev)                                                              \
+  do {                                                                                               \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (step) < 64) g_trace[((role)*64 + (step)) * 16 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define RBF_TRACE_EVENT(role, step, ev) \
+  do {                                  \
+  } while (0)
+#endif
+
 static constexpr int D = 64;
 static constexpr int kThreads = 768;
 static constexpr int kNumComputeWarps = 16;
@@ -244,16 +257,20 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           if (n + 1 < cnt) {
             // S^T(n+1) may overwrite S^T(n) as soon as every compute warp holds it in registers
             const int st = (n + 1) % kStages;
+            RBF_TRACE_EVENT(0, n, 0);
             ok = wait_q(n + 1) && mbar_wait(s_consumed, n & 1, abort_flag, p.status, kSiteSConsumed);
             if (!ok) break;
+            RBF_TRACE_EVENT(0, n, 1);
             tc_fence_after_sync();
             issue_scores(tmem + kColS, k_kmaj, stage_of(q_kmaj0, st, kTileBytes), stage_of(lslab0, st, kSlabBytes));
             umma_commit(s_full);
             umma_commit(&q_empty[st]);
           }
           // dV += P^T dO
+          RBF_TRACE_EVENT(0, n, 2);
           ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
           if (!ok) break;
+          RBF_TRACE_EVENT(0, n, 3);
           tc_fence_after_sync();
           const SmemDesc do_n = stage_of(do_nmaj0, n % kStages, kTileBytes);
 #pragma unroll
@@ -262,6 +279,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(dv_done);
           umma_commit(&do_empty[n % kStages]);
+          RBF_TRACE_EVENT(0, n, 4);
         }
       } else {
         const SmemDesc v_kmaj = make_sdesc_parts(smem_u32(s_v), 16, 1024);
@@ -281,16 +299,20 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         for (int n = 0; n < cnt && ok; ++n) {
           if (n + 1 < cnt) {
             const int st = (n + 1) % kStages;
+            RBF_TRACE_EVENT(1, n, 0);
             ok = wait_do(n + 1) && mbar_wait(dp_consumed, n & 1, abort_flag, p.status, kSiteDPConsumed);
             if (!ok) break;
+            RBF_TRACE_EVENT(1, n, 1);
             tc_fence_after_sync();
             issue_scores(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, st, kTileBytes), stage_of(dslab0, st, kSlabBytes));
             umma_commit(dp_full);
             umma_commit(&do_empty[st]);
           }
           // dK += dS^T Q : A = dS^T tile (K-major: 64-query boxes of 128-byte rows), B = Q read N-major
+          RBF_TRACE_EVENT(1, n, 2);
           ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
           if (!ok) break;
+          RBF_TRACE_EVENT(1, n, 3);
           tc_fence_after_sync();
           const SmemDesc q_n = stage_of(q_nmaj0, n % kStages, kTileBytes);
 #pragma unroll
@@ -298,6 +320,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             umma_ss(tmem + kColDK, sdesc_at(ds_kmaj, (kk >> 2) * (kTile * 128) + (kk & 3) * 32), sdesc_at(q_n, kk * 2048),
                     idesc_acc, (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&q_empty[n % kStages]);
+          RBF_TRACE_EVENT(1, n, 4);
           // dQ_partial = dS K : A = the same tile read M-major (rows = keys = reduction index), B = K read N-major
           if (n > 0) {
             ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained);
@@ -308,6 +331,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           for (int kk = 0; kk < kTile / 16; ++kk)
             umma_ss(tmem + kColDQ, sdesc_at(ds_mmaj, kk * 2048), sdesc_at(k_nmaj, kk * 2048), idesc_dq, kk > 0);
           umma_commit(dq_full);
+          RBF_TRACE_EVENT(1, n, 5);
         }
       }
       if (ok) umma_commit(acc_done);   // both issuers arrive: the barrier counts two
@@ -319,8 +343,10 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
     for (int n = 0; n < cnt; ++n) {
+      if (r == 0) RBF_TRACE_EVENT(3, n, 0);
       ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull);
       if (!ok) break;
+      if (r == 0) RBF_TRACE_EVENT(3, n, 1);
       tc_fence_after_sync();
       const int q_row = (first + n) * kTile + r;
       float* dst = p.dq_acc + (static_cast<int64_t>(bh) * p.N + q_row) * D;
@@ -334,7 +360,6 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           tc_fence_before_sync();
           mbar_arrive_warp(dq_drained);
         }
-#ifndef RBF_SKIP_DQ_RED
         if (q_row < p.N) {
 #pragma unroll
           for (int g = 0; g < 4; ++g)
@@ -343,9 +368,6 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                          "f"(__uint_as_float(v[g * 4 + 2])), "f"(__uint_as_float(v[g * 4 + 3]))
                          : "memory");
         }
-#else
-        if (q_row < 0) dst[c] = __uint_as_float(v[0]);
-#endif
       }
     }
   } else {
@@ -358,20 +380,26 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     float ds_rowsum = 0.f;
     bool ok = true;
 
+    const bool tr = (tid == kComputeWarp0 * 32);
     for (int n = 0; n < cnt; ++n) {
+      if (tr) RBF_TRACE_EVENT(2, n, 0);
       ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
       if (!ok) break;
+      if (tr) RBF_TRACE_EVENT(2, n, 1);
       tc_fence_after_sync();
       float pr[32];
       {
         uint32_t raw[32];
         tmem_ld_x32(tmem + kColS + lane_sel + g * 32, raw);
         tmem_ld_wait();
+        if (tr) RBF_TRACE_EVENT(2, n, 8);
         tc_fence_before_sync();
         mbar_arrive_warp(s_consumed);
+        if (tr) RBF_TRACE_EVENT(2, n, 9);
         // acc = k.q - L / scale2 ; P = exp2(acc * scale2 - ksq)
 #pragma unroll
         for (int i = 0; i < 32; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(raw[i]), p.scale2, neg_ksq));
+        if (tr) RBF_TRACE_EVENT(2, n, 10);
       }
       if (p.causal && n == 0) {
         // diagonal tile: query column (32g + c) sees key row r iff column >= row
@@ -389,22 +417,27 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           if (!ok) break;
           tc_fence_after_sync();
         }
+        if (tr) RBF_TRACE_EVENT(2, n, 2);
         tmem_st_x16(tmem + kColPT + lane_sel + g * 16, packed);
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive_warp(p_full);
       }
+      if (tr) RBF_TRACE_EVENT(2, n, 3);
 
       ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull);
       if (!ok) break;
+      if (tr) RBF_TRACE_EVENT(2, n, 4);
       tc_fence_after_sync();
       uint32_t ds_packed[16];
       {
         uint32_t raw[32];
         tmem_ld_x32(tmem + kColDP + lane_sel + g * 32, raw);
         tmem_ld_wait();
+        if (tr) RBF_TRACE_EVENT(2, n, 12);
         tc_fence_before_sync();
         mbar_arrive_warp(dp_consumed);
+        if (tr) RBF_TRACE_EVENT(2, n, 13);
         // acc = v.dO - delta ; dS = P * acc
         float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
@@ -417,18 +450,22 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
         ds_rowsum += rs0 + rs1;
       }
+      if (tr) RBF_TRACE_EVENT(2, n, 5);
       // the dS^T tile is free once dK and dQ_partial of the previous step have completed
       if (n > 0) {
         ok = mbar_wait(dq_full, (n - 1) & 1, abort_flag, p.status, kSiteDsFree);
         if (!ok) break;
       }
+      if (tr) RBF_TRACE_EVENT(2, n, 11);
       // row r of the [key][query] tile, box g/2, 16-byte chunks 4(g%2) .. +3
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch)
         *reinterpret_cast<uint4*>(s_ds + (g >> 1) * (kTile * 128) + sw128_offset(r, (g & 1) * 4 + ch)) =
             make_uint4(ds_packed[ch * 4 + 0], ds_packed[ch * 4 + 1], ds_packed[ch * 4 + 2], ds_packed[ch * 4 + 3]);
+      if (tr) RBF_TRACE_EVENT(2, n, 6);
       fence_proxy_async_smem();
       mbar_arrive_warp(ds_full);
+      if (tr) RBF_TRACE_EVENT(2, n, 7);
     }
 
     uint32_t grp_phase = 0;
@@ -542,6 +579,12 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace bwdf
+
+#ifdef RBF_TRACE
+extern "C" int rbf_b200_debug_read_trace(long long* host, int count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, bwdf::g_trace, sizeof(long long) * count));
+}
+#endif
 
 cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream) {
   return bf16 ? bwdf::launch_t<true>(a, stream) : bwdf::launch_t<false>(a, stream);
