@@ -1,7 +1,7 @@
 """Benchmark of the fused RBF attention forward+backward on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload config2|config3|config3_full|config4]
-                    [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload config2|config3|config3_full|config4|config5_lm]
 
 A step is one forward + backward pass of the attention operator over one batch of seeded synthetic
 inputs. ``value`` is algorithmic TFLOP/s (4 B H N^2 D forward + 10 B H N^2 D backward, halved when causal)
@@ -9,6 +9,9 @@ with inputs resident in HBM; ``e2e`` is the same metric through the public PyTor
 (pinned) inputs and outputs, copies inside the timed region. With N > 1 every rank runs the same per-GPU
 workload on its own seed (independent batch x head pairs, no collective in the data path) and ``value``
 is the sum over ranks divided by the slowest rank's time. One JSON line is printed by rank 0.
+
+``--workload config5_lm`` runs the data-parallel language-model training step instead (tokens/s; NCCL gradient
+all-reduce through DistributedDataParallel when N > 1).
 
 ``--impl reference`` times the reference project's own CPU path (materialised-matrix PyTorch math with
 autograd, restated in oracle/rbf_oracle.py) on the host cores, one (batch, head) pair of the workload per step.
@@ -353,16 +356,155 @@ def run_profile_case(args, w):
     print(f"profile case {w}: {ms:.3f} ms per step", flush=True)
 
 
+# ---------------------------------------------------------------------------------------------
+# configuration 5: data-parallel language-model training step (tokens/s)
+# ---------------------------------------------------------------------------------------------
+LM = dict(vocab=50257, d_model=512, layers=8, heads=8, seq=1024, batch=64, registers=4)
+LM_METRIC, LM_UNIT = "lm_train_tokens_per_s", "tokens/s"
+
+
+def lm_model(attention_type, dtype, device):
+    import torch
+
+    from rbf_attention_b200 import lm
+
+    torch.manual_seed(0)
+    model = lm.CausalLM(LM["vocab"], LM["d_model"], LM["layers"], LM["heads"], max_seq_len=LM["seq"],
+                        pos_emb_type="rope", num_registers=LM["registers"], attention_type=attention_type)
+    return model.to(device=device, dtype=dtype)
+
+
+def lm_cpu_tokens_per_second(steps=1, batch=1, seq=256):
+    """The reference's CPU path for this model: fp32, materialised attention (rbf_slow), AdamW step, on all host
+    threads, on a bounded sample (batch x seq tokens per step). Returns (tokens/s, threads, description)."""
+    import torch
+
+    from rbf_attention_b200 import lm
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    model = lm_model("rbf_slow", torch.float32, "cpu")
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4)
+    ids = lm.zipf_token_ids(batch, seq + 1, LM["vocab"], seed=0)
+
+    def step():
+        logits, _ = model(ids[:, :-1])
+        loss = torch.nn.functional.cross_entropy(logits.reshape(-1, LM["vocab"]), ids[:, 1:].reshape(-1))
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+
+    step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    return batch * seq * steps / dt, threads, f"{batch} sequence(s) of {seq} tokens per step, fp32, rbf_slow attention, AdamW"
+
+
+def run_lm(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    from rbf_attention_b200 import lm
+
+    cfg = {"workload": "config5_lm", "model": f"CausalLM {LM['layers']}x{LM['d_model']}, {LM['heads']} heads x 64, "
+           f"MLP 4x, {LM['registers']} register tokens, SuSiE, vocab {LM['vocab']}", "global_batch": LM["batch"] * world,
+           "seq_len": LM["seq"], "parallelism": f"dp{world}", "optimizer": "AdamW (fused), bf16 weights"}
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        tps, threads, sample = lm_cpu_tokens_per_second(steps=max(1, min(args.steps, 3)))
+        print(json.dumps({
+            "impl": "reference", "metric": LM_METRIC, "value": tps, "unit": LM_UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
+            "cpu_baseline": {"value": tps, "unit": LM_UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": LM_UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}), flush=True)
+        return
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    model = lm_model("rbf_triton", torch.bfloat16, device)
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True) \
+        if world > 1 else model
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
+    ids_host = lm.zipf_token_ids(LM["batch"], LM["seq"] + 1, LM["vocab"], seed=100 + rank).pin_memory()
+    ids_dev = ids_host.to(device)
+    loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+
+    def step(ids):
+        logits, _ = net(ids[:, :-1])
+        loss = torch.nn.functional.cross_entropy(logits.float().view(-1, LM["vocab"]), ids[:, 1:].reshape(-1))
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(ids_dev)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        ms = time_loop(torch, lambda: step(ids_dev), args.steps)
+    barrier()
+
+    def e2e_step():
+        ids = ids_host.to(device, non_blocking=True)
+        loss_host.copy_(step(ids).detach(), non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    e2e_step()
+    barrier()
+    e2e_ms = time_loop(torch, e2e_step, e2e_steps)
+    t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tokens = LM["batch"] * LM["seq"] * world
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        n_params = sum(p.numel() for p in model.parameters())
+        dense = 6.0 * (n_params - LM["vocab"] * LM["d_model"]) * LM["batch"] * LM["seq"]     # embedding lookup is free
+        n_attn = LM["seq"] + LM["registers"]
+        attn = LM["layers"] * 14.0 * LM["batch"] * LM["heads"] * n_attn * n_attn * 64 * 0.5
+        achieved = (dense + attn) / (t[0].item() * 1e-3) / 1e12
+        cpu_tps, cores, sample = lm_cpu_tokens_per_second()
+        print(json.dumps({
+            "metric": LM_METRIC, "value": tokens / (t[0].item() * 1e-3), "unit": LM_UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t[0].item(), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
+            "roofline": {"bound": "tensor", "kernel": "whole step (cuBLAS GEMMs dominate; attention is ~9 % of the FLOPs)",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": peak_src},
+            "cpu_baseline": {"value": cpu_tps, "unit": LM_UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tokens / (t[1].item() * 1e-3), "unit": LM_UNIT,
+                    "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": 4, "ms_per_step": t[1].item()},
+            "gpu_launches": LM["layers"] * 5 * args.steps, "clocks": clocks.summary()}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS) + ["config5_lm"])
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profilers: a quarter of the workload's batch, kernels only, no JSON line")
     args = ap.parse_args()
+    if args.workload == "config5_lm":
+        return run_lm(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+                      int(os.environ.get("LOCAL_RANK", "0")))
     w = dict(WORKLOADS[args.workload])
     if args.profile_case:
         w["B"] = max(1, w["B"] // 4)

@@ -1,0 +1,86 @@
+"""Causal language model around the RBF attention block, with the reference's module and parameter names
+(``train_rbf_transformer.py:113-244``: ``token_emb``, ``register_tokens``, ``blocks.<i>.{attn, ln1, ff, ln2}``,
+``ln_f``, ``to_logits``), so that reference checkpoints load and the data-parallel training step of the benchmark
+runs the same architecture: pre-LayerNorm blocks, 4x GELU MLP, zero-initialised register tokens prepended to the
+sequence and sliced off before the final norm, untied output projection."""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .attention import CustomCausalAttention
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, emb_dim, num_heads, max_seq_len, use_rope, attention_type, use_qk_norm=False, use_xsa=False,
+                 num_registers=0):
+        super().__init__()
+        self.attention_type = attention_type
+        self.use_qk_norm = use_qk_norm
+        self.use_xsa = use_xsa
+        self.attn = CustomCausalAttention(num_heads, emb_dim, max_seq_len, use_rope, attention_type, use_qk_norm,
+                                          use_xsa, num_registers)
+        self.ln1 = nn.LayerNorm(emb_dim)
+        self.ff = nn.Sequential(nn.Linear(emb_dim, 4 * emb_dim), nn.GELU(), nn.Linear(4 * emb_dim, emb_dim))
+        self.ln2 = nn.LayerNorm(emb_dim)
+
+    def forward(self, x):
+        attn_out, attn_weights = self.attn(self.ln1(x))
+        x = x + attn_out
+        return x + self.ff(self.ln2(x)), attn_weights
+
+
+class CausalLM(nn.Module):
+    def __init__(self, vocab_size, d_model=256, num_layers=4, num_heads=4, max_seq_len=1024, pos_emb_type="none",
+                 use_qk_norm=False, num_registers=0, attention_type="standard"):
+        super().__init__()
+        if use_qk_norm and attention_type.startswith("rbf"):
+            raise AssertionError("QK-Norm requires standard attention")
+        if pos_emb_type not in ("none", "rope", "learned"):
+            raise ValueError(f"Unsupported pos_emb_type: {pos_emb_type}")
+        self.num_registers = num_registers
+        self.use_qk_norm = use_qk_norm
+        self.pos_emb_type = pos_emb_type
+        if num_registers > 0:
+            if attention_type.startswith("rbf"):
+                # zero registers start at distance |q|^2 from every query (the reference's choice for RBF)
+                init = torch.zeros(num_registers, d_model)
+            elif attention_type.startswith("standard"):
+                init = torch.randn(num_registers, d_model) * d_model**-0.5
+            else:
+                raise ValueError(f"Unsupported attention type: {attention_type}")
+            self.register_tokens = nn.Parameter(init)
+        self.token_emb = nn.Embedding(vocab_size, d_model)
+        if pos_emb_type == "learned":
+            self.pos_emb = nn.Embedding(max_seq_len, d_model)
+        self.use_rope = pos_emb_type == "rope"
+        self.blocks = nn.ModuleList(
+            TransformerBlock(d_model, num_heads, max_seq_len, self.use_rope, attention_type, use_qk_norm=use_qk_norm,
+                             use_xsa=False, num_registers=num_registers)
+            for _ in range(num_layers)
+        )
+        self.ln_f = nn.LayerNorm(d_model)
+        self.to_logits = nn.Linear(d_model, vocab_size)
+
+    def forward(self, idx):
+        bsz, seq = idx.shape
+        x = self.token_emb(idx)
+        if self.pos_emb_type == "learned":
+            x = x + self.pos_emb(torch.arange(seq, device=idx.device))
+        if self.num_registers > 0:
+            x = torch.cat([self.register_tokens.unsqueeze(0).expand(bsz, -1, -1).to(x.dtype), x], dim=1)
+        weights = []
+        for block in self.blocks:
+            x, w = block(x)
+            weights.append(w)
+        if self.num_registers > 0:
+            x = x[:, self.num_registers:, :]
+        return self.to_logits(self.ln_f(x)), weights
+
+
+def zipf_token_ids(batch, seq_len, vocab_size, exponent=1.1, seed=0):
+    """(batch, seq_len) int64 token ids with P(id = k) proportional to (k + 1)^-exponent, seeded, on the CPU."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    probs = torch.arange(1, vocab_size + 1, dtype=torch.float64).pow(-exponent)
+    return torch.multinomial(probs / probs.sum(), batch * seq_len, replacement=True, generator=g).view(batch, seq_len)

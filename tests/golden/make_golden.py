@@ -14,6 +14,8 @@ Fixtures (all fp32 unless noted):
                      rows subsampled by 16, plus per-tensor sums
   block_small.npz    CustomCausalAttention(rbf_slow / rbf_non_softmax_slow) with SuSiE positions and 4 register
                      tokens: parameters, input, output and parameter gradients
+  lm_small.npz       train_rbf_transformer.CausalLM (2 layers, d 64, 2 heads, 2 register tokens, rbf_slow): token ids,
+                     logits, loss and all parameter gradients
 """
 
 import math
@@ -123,6 +125,24 @@ def main(ref_path):
             out[f"param_{tag}.{name}"] = prm.detach().numpy()
             out[f"grad_{tag}.{name}"] = prm.grad.numpy()
     np.savez_compressed(os.path.join(HERE, "block_small.npz"), **out)
+
+    # ---- lm_small: the language model (register tokens, SuSiE positions) through the rbf_slow branch ------
+    import train_rbf_transformer as trt  # noqa: E402
+
+    torch.manual_seed(11)
+    lm = trt.CausalLM(vocab_size=97, d_model=64, num_layers=2, num_heads=2, max_seq_len=32, pos_emb_type="rope",
+                      num_registers=2, attention_type="rbf_slow")
+    with torch.no_grad():
+        lm.register_tokens.normal_(0.0, 0.02)     # the reference initialises them to zero; make them matter
+    idx = torch.randint(0, 97, (3, 12), generator=torch.Generator().manual_seed(12))
+    logits, _ = lm(idx)
+    loss = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, 97), idx[:, 1:].reshape(-1))
+    loss.backward()
+    out = {"idx": idx.numpy(), "logits": logits.detach().numpy(), "loss": np.array(loss.item())}
+    for name, prm in lm.named_parameters():
+        out[f"param.{name}"] = prm.detach().numpy()
+        out[f"grad.{name}"] = prm.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "lm_small.npz"), **out)
     print("wrote fixtures to", HERE)
 
 

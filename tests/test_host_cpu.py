@@ -142,3 +142,34 @@ def test_two_rank_partition_with_gloo(tmp_path):
     outs = [p.communicate(timeout=180)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"ok {r}" in o, o
+
+
+def test_language_model_matches_reference_fixture(golden_dir):
+    """train_rbf_transformer.CausalLM (rbf_slow, 2 register tokens, SuSiE positions): same state-dict keys, logits,
+    loss and parameter gradients."""
+    from rbf_attention_b200 import lm
+
+    g = np.load(os.path.join(golden_dir, "lm_small.npz"))
+    model = lm.CausalLM(vocab_size=97, d_model=64, num_layers=2, num_heads=2, max_seq_len=32, pos_emb_type="rope",
+                        num_registers=2, attention_type="rbf_slow")
+    state = {k[len("param."):]: torch.tensor(g[k]) for k in g.files if k.startswith("param.")}
+    assert set(state) == set(dict(model.named_parameters()))
+    model.load_state_dict(state)
+    idx = torch.tensor(g["idx"])
+    logits, weights = model(idx)
+    assert len(weights) == 2 and weights[0].shape == (3, 2, 14, 14)
+    loss = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, 97), idx[:, 1:].reshape(-1))
+    loss.backward()
+    np.testing.assert_allclose(logits.detach().numpy(), g["logits"], atol=1e-5)
+    np.testing.assert_allclose(loss.item(), g["loss"], atol=1e-6)
+    for name, prm in model.named_parameters():
+        np.testing.assert_allclose(prm.grad.numpy(), g[f"grad.{name}"], atol=2e-5, err_msg=name)
+
+
+def test_zipf_token_ids_are_seeded_and_heavy_headed():
+    from rbf_attention_b200 import lm
+
+    a = lm.zipf_token_ids(4, 257, 50257, seed=3)
+    b = lm.zipf_token_ids(4, 257, 50257, seed=3)
+    assert torch.equal(a, b) and a.shape == (4, 257) and a.max() < 50257 and a.min() >= 0
+    assert (a < 10).float().mean() > 0.2        # a Zipf(1.1) head: the ten most frequent ids carry > 20 % of the mass
