@@ -438,7 +438,7 @@ def run_lm(args, rank, world, local_rank):
 
     def step(ids):
         logits, _ = net(ids[:, :-1])
-        loss = torch.nn.functional.cross_entropy(logits.float().view(-1, LM["vocab"]), ids[:, 1:].reshape(-1))
+        loss = torch.nn.functional.cross_entropy(logits.view(-1, LM["vocab"]), ids[:, 1:].reshape(-1))
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
