@@ -14,11 +14,12 @@
 // to the output type (times 2g) afterwards. dK gets the norm-gradient term in the epilogue:
 // dK = 2g (acc - rowsum(dS^T)[key] * k).
 //
-// Roles: warps 0, 1 MMA issuers (one thread cannot issue the N = 64 products as fast as the tensor pipe retires
-// them), warp 2 TMA producer, warps 4-19 compute (thread = key row; group g owns query columns [32g, 32g+32) of the
+// Roles: warps 0, 1, 3 MMA issuers (one thread sustains one MMA per ~60 cycles, the tensor pipe retires an N = 64
+// product in 32; five issuers, one per product, measured slower than three), warp 2 TMA producer, warps 4-19 compute (thread = key row; group g owns query columns [32g, 32g+32) of the
 // tile), warps 20-23 drain dQ_partial (thread = query row). Compute warpgroups take registers from the others.
 //   issuer A: S^T(n+1) as soon as the compute warps have read S^T(n); dV(n) when P^T(n) is in TMEM
-//   issuer B: dP^T(n+1) as soon as dP^T(n) has been read; dK(n) and dQ_partial(n) when dS^T(n) is in shared memory
+//   issuer B: dP^T(n+1) as soon as dP^T(n) has been read; dK(n) when dS^T(n) is in shared memory
+//   issuer C: dQ_partial(n) when dS^T(n) is in shared memory and the drain warps have read dQ_partial(n-1)
 // so the compute warps never wait for an MMA that was not issued a full step ahead.
 // TMEM columns: S^T [0,128), dP^T [128,256), P^T [256,320), dV [320,384), dK [384,448), dQ_partial [448,512).
 #include "common.cuh"
@@ -47,6 +48,7 @@ static constexpr int kNumComputeWarps = 16;
 static constexpr int kMmaWarpA = 0;
 static constexpr int kMmaWarpB = 1;
 static constexpr int kLoadWarp = 2;
+static constexpr int kMmaWarpC = 3;
 static constexpr int kComputeWarp0 = 4;
 static constexpr int kDrainWarp0 = 20;
 // Register budget: the launch allocates 80 per thread (768 threads); setmaxnreg may only redistribute that
@@ -162,9 +164,9 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     mbar_init(p_full, kNumComputeWarps);
     mbar_init(dv_done, 1);
     mbar_init(ds_full, kNumComputeWarps);
-    mbar_init(dq_full, 1);
+    mbar_init(dq_full, 2);                    // dK (issuer B) and dQ_partial (issuer C) of the step
     mbar_init(dq_drained, 4);
-    mbar_init(acc_done, 2);
+    mbar_init(acc_done, 3);
     mbar_init(grp_sync, kNumComputeWarps);
     fence_mbar_init();
   }
@@ -187,9 +189,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   if (warp < kComputeWarp0) {
     setmaxnreg_dec<kOtherRegs>();
   }
-  if (warp == 3) {
-    // idle warp of the first warpgroup
-  } else if (warp == kLoadWarp) {
+  if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_k);
@@ -215,7 +215,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         tma_load_3d(s_dslab + st * kSlabBytes, &tm_dslab, &do_full[st], 0, row0, bh);
       }
     }
-  } else if (warp == kMmaWarpA || warp == kMmaWarpB) {
+  } else if (warp == kMmaWarpA || warp == kMmaWarpB || warp == kMmaWarpC) {
     // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(kTile, kTile, kBf16, false, false);  // keys x queries, both K-major
@@ -281,14 +281,26 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           umma_commit(&do_empty[n % kStages]);
           RBF_TRACE_EVENT(0, n, 4);
         }
+      } else if (warp == kMmaWarpC) {
+        // dQ_partial = dS K : A = the dS^T tile read M-major (rows = keys = reduction index), B = K read N-major
+        const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
+        const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);   // rows = reduction (keys)
+        for (int n = 0; n < cnt && ok; ++n) {
+          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
+          if (ok && n > 0) ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained);
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ss(tmem + kColDQ, sdesc_at(ds_mmaj, kk * 2048), sdesc_at(k_nmaj, kk * 2048), idesc_dq, kk > 0);
+          umma_commit(dq_full);                    // second arrival: dQ_partial readable, M-major reader done
+        }
       } else {
         const SmemDesc v_kmaj = make_sdesc_parts(smem_u32(s_v), 16, 1024);
         const SmemDesc do_kmaj0 = make_sdesc_parts(smem_u32(s_do), 16, 1024);
         const SmemDesc dslab0 = make_sdesc_slab32(smem_u32(s_dslab));
-        const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
         const SmemDesc q_nmaj0 = make_sdesc_parts(smem_u32(s_q), kTile * 128, 1024);
         const SmemDesc ds_kmaj = make_sdesc_parts(smem_u32(s_ds), 16, 1024);            // rows = keys, K = queries
-        const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);   // rows = reduction (keys)
         if (ok) ok = wait_do(0);
         if (ok) {
           tc_fence_after_sync();
@@ -320,21 +332,11 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             umma_ss(tmem + kColDK, sdesc_at(ds_kmaj, (kk >> 2) * (kTile * 128) + (kk & 3) * 32), sdesc_at(q_n, kk * 2048),
                     idesc_acc, (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&q_empty[n % kStages]);
+          umma_commit(dq_full);                    // first of two arrivals: the dS^T tile's K-major reader is done
           RBF_TRACE_EVENT(1, n, 4);
-          // dQ_partial = dS K : A = the same tile read M-major (rows = keys = reduction index), B = K read N-major
-          if (n > 0) {
-            ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained);
-            if (!ok) break;
-            tc_fence_after_sync();
-          }
-#pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ss(tmem + kColDQ, sdesc_at(ds_mmaj, kk * 2048), sdesc_at(k_nmaj, kk * 2048), idesc_dq, kk > 0);
-          umma_commit(dq_full);
-          RBF_TRACE_EVENT(1, n, 5);
         }
       }
-      if (ok) umma_commit(acc_done);   // both issuers arrive: the barrier counts two
+      if (ok) umma_commit(acc_done);   // every issuer arrives: the barrier counts three
     }
   } else if (warp >= kDrainWarp0) {
     // ------------------------------------------------------------------ dQ_partial drain (thread = query row)
