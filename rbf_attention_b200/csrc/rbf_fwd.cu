@@ -48,7 +48,7 @@ struct Smem {
   static constexpr int kKSlab = kV + kStages * kTileBytes;  // kStages bias slabs
   static constexpr int kOnes = kKSlab + kStages * kSlabBytes;
   static constexpr int kBars = kOnes + kSlabBytes;
-  static constexpr int kNumBars = 2 + 4 * kStages + 8;
+  static constexpr int kNumBars = 2 + 4 * kStages + 10;
   static constexpr int kMisc = kBars + kNumBars * 8;        // tmem base, abort flag
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;            // slack for 1024-byte alignment
@@ -56,7 +56,7 @@ struct Smem {
 
 enum Site : uint32_t {
   kSiteQFull = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSFull, kSitePFull, kSiteODone,
-  kSiteODoneFinal, kSiteGroup
+  kSiteODoneFinal, kSiteGroup, kSiteSConsumed, kSitePFree
 };
 
 template <int D, bool kSoftmax, bool kBf16>
@@ -71,6 +71,10 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   constexpr int kBoxes = D / 64;                 // 64-column TMA boxes per tile row
   constexpr int kBoxBytes = kTile * 128;         // one box: 128 rows x 128 bytes
   constexpr uint32_t kTileBytes = L::kTileBytes;
+  // At D = 64 TMEM has room for P in columns of its own (2 x 128 S + 2 x 64 O + 2 x 64 P = 512): S_t(j+1) is then
+  // issued as soon as the softmax group holds S_t(j) in registers and runs under the exponentials. At D = 128 P
+  // overwrites the first 64 columns of S_t and S_t(j+1) follows O_t += P_t V_j in the issue order.
+  constexpr bool kSeparateP = (D == 64);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -89,6 +93,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint64_t* p_full = s_full + 2;                 // [2]
   uint64_t* o_done = p_full + 2;                 // [2]
   uint64_t* grp_sync = o_done + 2;               // [2] rendezvous of the 4 warps of a softmax group
+  uint64_t* s_consumed = grp_sync + 2;           // [2] the softmax group holds S_t(j) in registers
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
 
@@ -129,6 +134,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(&p_full[t], 4);              // one arrival per softmax warp
       mbar_init(&o_done[t], 1);
       mbar_init(&grp_sync[t], 4);
+      mbar_init(&s_consumed[t], 4);
     }
     fence_mbar_init();
   }
@@ -150,6 +156,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t tmem = *tmem_base_s;
   const uint32_t tmem_s[2] = {tmem, tmem + 128};
   const uint32_t tmem_o[2] = {tmem + 256, tmem + 256 + D};
+  const uint32_t tmem_p[2] = {kSeparateP ? tmem + 384 : tmem_s[0], kSeparateP ? tmem + 448 : tmem_s[1]};
 
   if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA producer
@@ -210,7 +217,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         v_desc.lo += static_cast<uint32_t>(st) * (kTileBytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(tmem_o[t], tmem_s[t] + kk * 8, sdesc_at(v_desc, kk * 2048), idesc_o, kk > 0 ? 1u : accumulate);
+          umma_ts(tmem_o[t], tmem_p[t] + kk * 8, sdesc_at(v_desc, kk * 2048), idesc_o, kk > 0 ? 1u : accumulate);
         umma_commit(&o_done[t]);
       };
       bool ok = true;
@@ -244,11 +251,19 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int st_next = (j + 1) % kStages;
         bool used_k_next = false;
         if (j < my_nkt) {
+          if (kSeparateP && j + 1 < my_nkt) {
+            // next scores first: they only need S_t(j) to have been read
+            ok = wait_k(j + 1) && mbar_wait(&s_consumed[t], j & 1, abort_flag, status, kSiteSConsumed);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_s(st_next);
+            used_k_next = true;
+          }
           ok = wait_v(j) && mbar_wait(&p_full[t], j & 1, abort_flag, status, kSitePFull);
           if (!ok) break;
           tc_fence_after_sync();
           issue_o(st, j > 0 ? 1u : 0u);
-          if (j + 1 < my_nkt) {
+          if (!kSeparateP && j + 1 < my_nkt) {
             ok = wait_k(j + 1);
             if (!ok) break;
             tc_fence_after_sync();
@@ -304,6 +319,10 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tmem_ld_x32(tmem_s[t] + lane_sel + 64, c2);
         tmem_ld_x32(tmem_s[t] + lane_sel + 96, c3);
         tmem_ld_wait();
+        if (kSeparateP) {
+          tc_fence_before_sync();
+          mbar_arrive_warp(&s_consumed[t]);
+        }
       }
       if (causal && j * kTile == r0) {
         // diagonal tile: key (r0 + c) is visible to query (r0 + r) iff c <= r
@@ -352,6 +371,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         sub = row_bias;
       }
 
+      bool waited_o = !kSeparateP || j == 0;   // P's own columns are free once O_t += P_t V_(j-1) has completed
       const float neg_sub = -sub;
       float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
 #pragma unroll
@@ -367,8 +387,15 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           packed[i] = pack2<kBf16>(p0, p1);
           packed[i + 1] = pack2<kBf16>(p2, p3);
         }
-        tmem_st_x32(tmem_s[t] + lane_sel + c * 32, packed);
+        if (!waited_o) {
+          ok = mbar_wait(&o_done[t], (j - 1) & 1, abort_flag, status, kSitePFree);
+          if (!ok) break;
+          tc_fence_after_sync();
+          waited_o = true;
+        }
+        tmem_st_x32(tmem_p[t] + lane_sel + c * 32, packed);
       }
+      if (!ok) break;
       l_sum += (ps0 + ps1) + (ps2 + ps3);
       tmem_st_wait();
       tc_fence_before_sync();
