@@ -255,6 +255,8 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     const int t2 = rbf::make_tmap_slab16(&f.tm_dslab, ws.dslab, bf16, B * H, n_pad, rbf::kTile);
     if (t1 != 0 || t2 != 0)
       return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the bias slabs (codes %d, %d)", t1, t2);
+    const int t3 = rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, rbf::kTile);
+    if (t3 != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the dQ accumulator (code %d)", t3);
     f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
     f.ksq = ws.ksq; f.status = ws.status;
     f.B = B; f.H = H; f.N = N; f.n_pad = n_pad; f.causal = causal ? 1 : 0;

@@ -69,6 +69,7 @@ cudaError_t launch_bwd_dq(const BwdArgs& a, bool bf16, int D, bool softmax, cuda
 struct BwdFusedArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
   CUtensorMap tm_lslab, tm_dslab;  // (B*H, n_pad, 16) bias slabs of -L / scale2 and -delta, box 16 x 128
+  CUtensorMap tm_dq_acc;  // fp32 (B, H, N, 64) accumulator, box 32 x 128, 128-byte swizzle
   float* dq_acc;          // fp32 (B, H, N, 64) contiguous accumulator
   void* dq;               // final dQ in the operand type
   int64_t dq_strides[3];

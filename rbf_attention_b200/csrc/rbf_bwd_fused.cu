@@ -72,9 +72,10 @@ struct Smem {
   static constexpr int kLSlab = kDs + kDsBytes;
   static constexpr int kDSlab = kLSlab + kStages * kSlabBytes;
   static constexpr int kOnes = kDSlab + kStages * kSlabBytes;
-  static constexpr int kRowsum = kOnes + kSlabBytes;           // [4 groups][128] floats: partial row sums
+  static constexpr int kDqStage = kOnes + kSlabBytes;          // 32 KB fp32 dQ_partial staging, two 32-column boxes
+  static constexpr int kRowsum = kDqStage + kTile * D * 4;     // [4 groups][128] floats: partial row sums
   static constexpr int kBars = kRowsum + 4 * kTile * 4;
-  static constexpr int kNumBars = 1 + 4 * kStages + 11;
+  static constexpr int kNumBars = 1 + 4 * kStages + 12;
   static constexpr int kMisc = kBars + kNumBars * 8;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;
@@ -101,7 +102,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                      const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                      const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                      const __grid_constant__ CUtensorMap tm_lslab, const __grid_constant__ CUtensorMap tm_dslab,
-                     const Params p) {
+                     const __grid_constant__ CUtensorMap tm_dq_acc, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_k = smem + Smem::kK;
@@ -112,6 +113,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   uint8_t* s_lslab = smem + Smem::kLSlab;
   uint8_t* s_dslab = smem + Smem::kDSlab;
   uint8_t* s_ones = smem + Smem::kOnes;
+  uint8_t* s_dq = smem + Smem::kDqStage;
   float* s_rowsum = reinterpret_cast<float*>(smem + Smem::kRowsum);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
   uint64_t* kv_full = bars;
@@ -130,6 +132,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   uint64_t* dq_drained = dq_full + 1;        // drain warps have read dQ_partial(n) out of TMEM
   uint64_t* acc_done = dq_drained + 1;       // two arrivals: all MMAs of both issuers complete
   uint64_t* grp_sync = acc_done + 1;         // compute warps (16 arrivals)
+  uint64_t* drain_sync = grp_sync + 1;       // drain warps (4 arrivals)
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + Smem::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 4);
 
@@ -168,6 +171,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     mbar_init(dq_drained, 4);
     mbar_init(acc_done, 3);
     mbar_init(grp_sync, kNumComputeWarps);
+    mbar_init(drain_sync, 4);
     fence_mbar_init();
   }
   if (warp == kMmaWarpA) {
@@ -344,34 +348,46 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const int r = tid - kDrainWarp0 * 32;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
+    uint32_t dphase = 0;
     for (int n = 0; n < cnt; ++n) {
       if (r == 0) RBF_TRACE_EVENT(3, n, 0);
       ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull);
       if (!ok) break;
       if (r == 0) RBF_TRACE_EVENT(3, n, 1);
       tc_fence_after_sync();
-      const int q_row = (first + n) * kTile + r;
-      float* dst = p.dq_acc + (static_cast<int64_t>(bh) * p.N + q_row) * D;
+      // TMEM -> registers -> swizzled fp32 staging tile -> one bulk reduce-add per 32-column box
 #pragma unroll
       for (int c = 0; c < D / 16; ++c) {
         uint32_t v[16];
         tmem_ld_x16(tmem + kColDQ + lane_sel + c * 16, v);
         tmem_ld_wait();
         if (c == D / 16 - 1) {
-          // the whole row is in registers (or already on its way): the next dQ_partial MMA may overwrite TMEM
           tc_fence_before_sync();
-          mbar_arrive_warp(dq_drained);
+          mbar_arrive_warp(dq_drained);   // the next dQ_partial MMA may overwrite TMEM
         }
-        if (q_row < p.N) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c * 16 + g * 4),
-                         "f"(__uint_as_float(v[g * 4 + 0])), "f"(__uint_as_float(v[g * 4 + 1])),
-                         "f"(__uint_as_float(v[g * 4 + 2])), "f"(__uint_as_float(v[g * 4 + 3]))
-                         : "memory");
-        }
+        for (int g4 = 0; g4 < 4; ++g4)
+          *reinterpret_cast<uint4*>(s_dq + (c >> 1) * (kTile * 128) + sw128_offset(r, (c & 1) * 4 + g4)) =
+              make_uint4(v[g4 * 4 + 0], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
       }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(drain_sync);
+      ok = mbar_wait(drain_sync, dphase & 1, abort_flag, p.status, kSiteGroup);
+      ++dphase;
+      if (!ok) break;
+      if (r == 0) {
+        const int row0 = (first + n) * kTile;
+        tma_reduce_add_4d(&tm_dq_acc, s_dq, 0, row0, h, b);
+        tma_reduce_add_4d(&tm_dq_acc, s_dq + kTile * 128, 32, row0, h, b);
+        tma_store_commit();
+        tma_store_wait_read();     // the staging tile may be overwritten once the bulk engine has read it
+      }
+      mbar_arrive_warp(drain_sync);
+      ok = mbar_wait(drain_sync, dphase & 1, abort_flag, p.status, kSiteGroup);
+      ++dphase;
+      if (!ok) break;
     }
+    if (r == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ compute groups (thread = key row)
     setmaxnreg_inc<kComputeRegs>();
@@ -571,7 +587,7 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
   p.H = a.H; p.N = a.N; p.n_pad = a.n_pad; p.causal = a.causal;
   p.scale2 = a.scale2; p.grad_scale = a.grad_scale; p.slab_w = a.slab_w;
   dim3 grid((a.N + kTile - 1) / kTile, a.B * a.H);
-  kernel<<<grid, kThreads, smem, stream>>>(a.tm_k, a.tm_v, a.tm_q, a.tm_do, a.tm_dk, a.tm_dv, a.tm_lslab, a.tm_dslab, p);
+  kernel<<<grid, kThreads, smem, stream>>>(a.tm_k, a.tm_v, a.tm_q, a.tm_do, a.tm_dk, a.tm_dv, a.tm_lslab, a.tm_dslab, a.tm_dq_acc, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int64_t chunks = static_cast<int64_t>(a.B) * a.H * a.N * 8;
