@@ -38,8 +38,8 @@ struct Workspace {
   size_t bytes;
 };
 
-// The softmax backward at head dim 64 runs as one kernel that accumulates dQ in fp32 global memory.
-bool use_fused_backward(int D, int softmax) { return softmax && D == 64; }
+// The softmax backward runs as one kernel that accumulates dQ in fp32 global memory (a kernel per head dim).
+bool use_fused_backward(int D, int softmax) { return softmax && (D == 64 || D == 128); }
 
 // Constant held by the operand-side slab of a bias-slab MMA step, and the "minus infinity" the slabs use on padding
 // rows. fp16 needs the range extension: a bias up to 65504 * 256 stays representable.
@@ -107,8 +107,9 @@ int check_tensor(const char* name, const void* p, const int64_t* s, int B, int H
   return 0;
 }
 
-int make_map(CUtensorMap* m, const char* name, const void* p, const int64_t* s, bool bf16, int B, int H, int N, int D) {
-  const int r = rbf::make_tmap_bhnd(m, p, bf16, B, H, N, D, s[0], s[1], s[2], rbf::kTile);
+int make_map(CUtensorMap* m, const char* name, const void* p, const int64_t* s, bool bf16, int B, int H, int N, int D,
+             int box_rows = rbf::kTile) {
+  const int r = rbf::make_tmap_bhnd(m, p, bf16, B, H, N, D, s[0], s[1], s[2], box_rows);
   if (r != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for %s (code %d)", name, r);
   return 0;
 }
@@ -251,17 +252,23 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     if (!(phases & (RBF_B200_PHASE_MAIN | RBF_B200_PHASE_MAIN2))) return RBF_B200_OK;
     rbf::BwdFusedArgs f{};
     f.tm_q = a.tm_q; f.tm_k = a.tm_k; f.tm_v = a.tm_v; f.tm_do = a.tm_do; f.tm_dk = a.tm_dk; f.tm_dv = a.tm_dv;
-    const int t1 = rbf::make_tmap_slab16(&f.tm_lslab, ws.lslab, bf16, B * H, n_pad, rbf::kTile);
-    const int t2 = rbf::make_tmap_slab16(&f.tm_dslab, ws.dslab, bf16, B * H, n_pad, rbf::kTile);
+    // the head-dim-128 kernel streams the queries in steps of 64 rows
+    const int q_rows = D == 128 ? 64 : rbf::kTile;
+    if (q_rows != rbf::kTile) {
+      if ((rc = make_map(&f.tm_q, "q", q, q_strides, bf16, B, H, N, D, q_rows))) return rc;
+      if ((rc = make_map(&f.tm_do, "dout", dout, do_strides, bf16, B, H, N, D, q_rows))) return rc;
+    }
+    const int t1 = rbf::make_tmap_slab16(&f.tm_lslab, ws.lslab, bf16, B * H, n_pad, q_rows);
+    const int t2 = rbf::make_tmap_slab16(&f.tm_dslab, ws.dslab, bf16, B * H, n_pad, q_rows);
     if (t1 != 0 || t2 != 0)
       return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the bias slabs (codes %d, %d)", t1, t2);
-    const int t3 = rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, rbf::kTile);
+    const int t3 = rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, q_rows);
     if (t3 != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the dQ accumulator (code %d)", t3);
     f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
     f.ksq = ws.ksq; f.status = ws.status;
     f.B = B; f.H = H; f.N = N; f.n_pad = n_pad; f.causal = causal ? 1 : 0;
     f.scale2 = 2.f * c; f.grad_scale = 2.f * sm_scale; f.slab_w = slab_w(bf16);
-    e = rbf::launch_bwd_fused(f, bf16, stream);
+    e = D == 128 ? rbf::launch_bwd_fused128(f, bf16, stream) : rbf::launch_bwd_fused(f, bf16, stream);
     if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "backward launch failed: %s", cudaGetErrorString(e));
     return RBF_B200_OK;
   }

@@ -65,12 +65,14 @@ struct BwdArgs {
 cudaError_t launch_bwd_dkdv(const BwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream);
 cudaError_t launch_bwd_dq(const BwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream);
 
-// Single-kernel softmax backward for head dim 64 (five MMAs per tile pair, dQ through an fp32 accumulator).
+// Single-kernel softmax backward (five MMAs per tile pair, dQ through an fp32 accumulator). The head-dim-64 kernel
+// streams 128 query rows per step (Q, dO, slab and accumulator maps with 128-row boxes); the head-dim-128 kernel
+// streams 64 (those four maps with 64-row boxes).
 struct BwdFusedArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
   CUtensorMap tm_lslab, tm_dslab;  // (B*H, n_pad, 16) bias slabs of -L / scale2 and -delta, box 16 x 128
-  CUtensorMap tm_dq_acc;  // fp32 (B, H, N, 64) accumulator, box 32 x 128, 128-byte swizzle
-  float* dq_acc;          // fp32 (B, H, N, 64) contiguous accumulator
+  CUtensorMap tm_dq_acc;  // fp32 (B, H, N, D) accumulator, 32-column boxes, 128-byte swizzle
+  float* dq_acc;          // fp32 (B, H, N, D) contiguous accumulator
   void* dq;               // final dQ in the operand type
   int64_t dq_strides[3];
   const float* ksq;       // (B*H, n_pad)
@@ -79,6 +81,7 @@ struct BwdFusedArgs {
   int causal;
   float scale2, grad_scale, slab_w;
 };
-cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream);
+cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream);      // D = 64
+cudaError_t launch_bwd_fused128(const BwdFusedArgs& a, bool bf16, cudaStream_t stream);   // D = 128
 
 }  // namespace rbf
