@@ -10,8 +10,11 @@
 //   dV  [128 x 128] += P^T dO          TMEM x smem (P^T: 32 TMEM columns of 16-bit pairs)
 //   dK  [128 x 128] += dS^T Q          smem x smem (dS^T: a [key][query] tile of 128-byte rows)
 //   dQ^T[128 d x 64 q] = K^T dS^T      smem x smem (K read M-major, the dS^T tile read N-major)
-// dQ^T leaves the CTA transposed back through an fp32 staging tile and TMA bulk reduce-adds into a global
-// fp32 accumulator that a small kernel converts afterwards (shared with the head-dim-64 path).
+// dQ^T leaves the CTA as it is: the global fp32 accumulator is kept transposed, (B, H, D, n_pad), so that a thread
+// of the drain warps (thread = head-dim index) owns contiguous runs of queries. Each drain warp stages its own
+// 32 x 32 box and issues its own TMA bulk reduce-add, two staging boxes per warp in flight; a small kernel
+// transposes, scales and converts the accumulator afterwards. (Every SM can push about 25 bytes per clock of
+// reduce-adds into L2, measured; a step's 32 KB of dQ therefore takes as long as its MMAs and must overlap them.)
 //
 // TMEM columns: S^T [0,64), dP^T [64,128), P^T [128,160), dQ^T [160,224), dV [256,384), dK [384,512).
 // Roles: warps 0, 1, 3 MMA issuers (A: S^T(n+1), dV(n); B: dP^T(n+1), dK(n); C: dQ^T(n)), warp 2 TMA producer,
@@ -24,6 +27,20 @@ namespace rbf {
 
 namespace bwdf128 {
 
+#ifdef RBF_TRACE
+// Bring-up aid (not compiled into the product): clock64 stamps of one CTA's roles per step.
+__device__ long long g_trace128[5 * 64 * 16];
+#define RBF_TRACE_EVENT(role, step, ev)                                                                 \
+  do {                                                                                                  \
+    if (blockIdx.x == RBF_TRACE_BX && blockIdx.y == 0 && (step) < 64)                                   \
+      g_trace128[((role)*64 + (step)) * 16 + (ev)] = clock64();                                         \
+  } while (0)
+#else
+#define RBF_TRACE_EVENT(role, step, ev) \
+  do {                                  \
+  } while (0)
+#endif
+
 static constexpr int D = 128;
 static constexpr int kQStep = 64;                   // queries per step
 static constexpr int kThreads = 768;
@@ -34,10 +51,11 @@ static constexpr int kLoadWarp = 2;
 static constexpr int kMmaWarpC = 3;
 static constexpr int kComputeWarp0 = 4;
 static constexpr int kDrainWarp0 = 20;
-// setmaxnreg only redistributes the launch allocation (80 per thread): 512 * 96 + 256 * 40 <= 768 * 80.
+// setmaxnreg only redistributes the launch allocation (80 per thread): 512 * 96 + 128 * 40 + 128 * 56 = 768 * 80.
 static constexpr int kComputeRegs = 96;
 static constexpr int kOtherRegs = 40;
-static_assert(512 * kComputeRegs + 256 * kOtherRegs <= 768 * 80, "setmaxnreg budget");
+static constexpr int kDrainRegs = 56;
+static_assert(512 * kComputeRegs + 128 * kOtherRegs + 128 * kDrainRegs <= 768 * 80, "setmaxnreg budget");
 
 static constexpr int kBoxBytes = kTile * 128;             // 16 KB: 128 rows x 64 16-bit columns
 static constexpr int kKvBytes = 2 * kBoxBytes;            // K or V tile: two 64-column boxes
@@ -47,8 +65,10 @@ static constexpr int kSlabBytes = kQStep * 32;            // 2 KB: 64 rows x 16 
 static constexpr int kOnesBytes = kTile * 32;
 static constexpr int kQStages = 3;
 static constexpr int kDoStages = 2;
-static constexpr int kDsBytes = kTile * 128;              // 16 KB: dS^T as [128 keys][64 queries]
-static constexpr int kDqStageBytes = kQStep * D * 4;      // 32 KB: fp32 [64 q][128 d], four 32-column boxes
+static constexpr int kDsBytes = kTile * 128;              // 16 KB: dS^T as [128 keys][64 queries]; two buffers
+static constexpr int kDsStages = 2;
+static constexpr int kDqBoxBytes = 32 * 128;              // 4 KB: fp32 [32 d][32 q] of one drain warp
+static constexpr int kDqStageBytes = 4 * 2 * kDqBoxBytes; // 32 KB: four warps, two boxes in flight each
 
 struct Smem {
   static constexpr int kK = 0;
@@ -56,13 +76,13 @@ struct Smem {
   static constexpr int kQ = kV + kKvBytes;
   static constexpr int kDo = kQ + kQStages * kQTileBytes;
   static constexpr int kDs = kDo + kDoStages * kQTileBytes;
-  static constexpr int kDqStage = kDs + kDsBytes;
+  static constexpr int kDqStage = kDs + kDsStages * kDsBytes;
   static constexpr int kLSlab = kDqStage + kDqStageBytes;
   static constexpr int kDSlab = kLSlab + kQStages * kSlabBytes;
   static constexpr int kOnes = kDSlab + kDoStages * kSlabBytes;
   static constexpr int kRowsum = kOnes + kOnesBytes;         // [4 groups][128] floats
   static constexpr int kBars = kRowsum + 4 * kTile * 4;
-  static constexpr int kNumBars = 1 + 2 * kQStages + 2 * kDoStages + 13;
+  static constexpr int kNumBars = 1 + 2 * kQStages + 2 * kDoStages + 2 * kDsStages + 11;
   static constexpr int kMisc = kBars + kNumBars * 8;
   static constexpr int kTotal = kMisc + 16;
   static constexpr int kDynamic = kTotal + 1024;
@@ -115,12 +135,12 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   uint64_t* dp_consumed = dp_full + 1;
   uint64_t* p_full = dp_consumed + 1;
   uint64_t* dv_done = p_full + 1;
-  uint64_t* ds_full = dv_done + 1;
-  uint64_t* dq_full = ds_full + 1;           // two arrivals: dK (issuer B) and dQ^T (issuer C) of the step
+  uint64_t* ds_full = dv_done + 1;           // [kDsStages] the dS^T tile of a step is written
+  uint64_t* ds_free = ds_full + kDsStages;   // [kDsStages] two arrivals: dK (issuer B) and dQ^T (issuer C) have read it
+  uint64_t* dq_full = ds_free + kDsStages;   // dQ^T of the step is complete in TMEM
   uint64_t* dq_drained = dq_full + 1;
   uint64_t* acc_done = dq_drained + 1;       // three arrivals
   uint64_t* grp_sync = acc_done + 1;
-  uint64_t* drain_sync = grp_sync + 1;
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + Smem::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 4);
 
@@ -150,12 +170,11 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     mbar_init(dp_consumed, kNumComputeWarps);
     mbar_init(p_full, kNumComputeWarps);
     mbar_init(dv_done, 1);
-    mbar_init(ds_full, kNumComputeWarps);
-    mbar_init(dq_full, 2);
+    for (int s = 0; s < kDsStages; ++s) { mbar_init(&ds_full[s], kNumComputeWarps); mbar_init(&ds_free[s], 2); }
+    mbar_init(dq_full, 1);
     mbar_init(dq_drained, 4);
     mbar_init(acc_done, 3);
     mbar_init(grp_sync, kNumComputeWarps);
-    mbar_init(drain_sync, 4);
     fence_mbar_init();
   }
   if (warp == kMmaWarpA) {
@@ -248,16 +267,20 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         for (int n = 0; n < cnt && ok; ++n) {
           if (n + 1 < cnt) {
             const int st = (n + 1) % kQStages;
+            RBF_TRACE_EVENT(0, n, 0);
             ok = wait_q(n + 1) && mbar_wait(s_consumed, n & 1, abort_flag, p.status, kSiteSConsumed);
             if (!ok) break;
+            RBF_TRACE_EVENT(0, n, 1);
             tc_fence_after_sync();
             issue_scores(tmem + kColS, k_kmaj, stage_of(q_kmaj0, st, kQTileBytes), stage_of(lslab0, st, kSlabBytes));
             umma_commit(s_full);
             umma_commit(&q_empty[st]);
           }
           // dV += P^T dO
+          RBF_TRACE_EVENT(0, n, 2);
           ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
           if (!ok) break;
+          RBF_TRACE_EVENT(0, n, 3);
           tc_fence_after_sync();
           const SmemDesc do_n = stage_of(do_nmaj0, n % kDoStages, kQTileBytes);
 #pragma unroll
@@ -266,6 +289,7 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
                     (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(dv_done);
           umma_commit(&do_empty[n % kDoStages]);
+          RBF_TRACE_EVENT(0, n, 4);
         }
       } else if (warp == kMmaWarpB) {
         const SmemDesc v_kmaj = make_sdesc_parts(smem_u32(s_v), 16, 1024);
@@ -283,24 +307,30 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         for (int n = 0; n < cnt && ok; ++n) {
           if (n + 1 < cnt) {
             const int st = (n + 1) % kDoStages;
+            RBF_TRACE_EVENT(1, n, 0);
             ok = wait_do(n + 1) && mbar_wait(dp_consumed, n & 1, abort_flag, p.status, kSiteDPConsumed);
             if (!ok) break;
+            RBF_TRACE_EVENT(1, n, 1);
             tc_fence_after_sync();
             issue_scores(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, st, kQTileBytes), stage_of(dslab0, st, kSlabBytes));
             umma_commit(dp_full);
             umma_commit(&do_empty[st]);
           }
           // dK += dS^T Q
-          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
+          RBF_TRACE_EVENT(1, n, 2);
+          ok = mbar_wait(&ds_full[n % kDsStages], (n / kDsStages) & 1, abort_flag, p.status, kSiteDSFull);
           if (!ok) break;
+          RBF_TRACE_EVENT(1, n, 3);
           tc_fence_after_sync();
           const SmemDesc q_n = stage_of(q_nmaj0, n % kQStages, kQTileBytes);
+          const SmemDesc ds_n = stage_of(ds_kmaj, n % kDsStages, kDsBytes);
 #pragma unroll
           for (int kk = 0; kk < kQStep / 16; ++kk)
-            umma_ss(tmem + kColDK, sdesc_at(ds_kmaj, kk * 32), sdesc_at(q_n, kk * 2048), idesc_acc,
+            umma_ss(tmem + kColDK, sdesc_at(ds_n, kk * 32), sdesc_at(q_n, kk * 2048), idesc_acc,
                     (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&q_empty[n % kQStages]);
-          umma_commit(dq_full);                    // first of two arrivals: the dS^T tile's K-major reader is done
+          umma_commit(&ds_free[n % kDsStages]);    // first of two arrivals: the dS^T tile's K-major reader is done
+          RBF_TRACE_EVENT(1, n, 4);
         }
       } else {
         // dQ^T = K^T dS^T : A = K tile read M-major (rows = keys = reduction index, 64-wide d groups 16 KB apart),
@@ -308,64 +338,65 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         const SmemDesc k_mmaj = make_sdesc_parts(smem_u32(s_k), kBoxBytes, 1024);
         const SmemDesc ds_nmaj = make_sdesc_parts(smem_u32(s_ds), kBoxBytes, 1024);
         for (int n = 0; n < cnt && ok; ++n) {
-          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
+          RBF_TRACE_EVENT(4, n, 0);
+          ok = mbar_wait(&ds_full[n % kDsStages], (n / kDsStages) & 1, abort_flag, p.status, kSiteDSFull);
+          RBF_TRACE_EVENT(4, n, 1);
           if (ok && n > 0) ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained);
           if (!ok) break;
+          RBF_TRACE_EVENT(4, n, 2);
           tc_fence_after_sync();
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ss(tmem + kColDQ, sdesc_at(k_mmaj, kk * 2048), sdesc_at(ds_nmaj, kk * 2048), idesc_dq, kk > 0);
-          umma_commit(dq_full);                    // second arrival: dQ^T readable, N-major reader done
+            umma_ss(tmem + kColDQ, sdesc_at(k_mmaj, kk * 2048),
+                    sdesc_at(ds_nmaj, (n % kDsStages) * kDsBytes + kk * 2048), idesc_dq, kk > 0);
+          umma_commit(dq_full);                    // dQ^T readable
+          umma_commit(&ds_free[n % kDsStages]);    // second arrival: the N-major reader is done
+          RBF_TRACE_EVENT(4, n, 3);
         }
       }
       if (ok) umma_commit(acc_done);
     }
   } else if (warp >= kDrainWarp0) {
     // ------------------------------------------------------------------ dQ^T drain (thread = head-dim index)
-    setmaxnreg_dec<kOtherRegs>();
-    const int r = tid - kDrainWarp0 * 32;                   // d
-    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint8_t* my_box = s_dq + (r >> 5) * (kQStep * 128);     // staging box of 32 head-dim columns
-    const uint32_t f = static_cast<uint32_t>(r & 31);
+    setmaxnreg_dec<kDrainRegs>();
+    const int wq = warp & 3;                                // TMEM lane quadrant = 32 head-dim rows
+    const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+    uint8_t* my_boxes = s_dq + wq * (2 * kDqBoxBytes);      // this warp's two staging boxes
     bool ok = true;
-    uint32_t dphase = 0;
     for (int n = 0; n < cnt; ++n) {
+      if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 0);
       ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull);
       if (!ok) break;
+      if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 1);
       tc_fence_after_sync();
-      // TMEM (lane = d, column = query) -> staging tile [query][d] fp32 (transposed back), 128-byte swizzle
 #pragma unroll
-      for (int c = 0; c < kQStep / 16; ++c) {
-        uint32_t v[16];
-        tmem_ld_x16(tmem + kColDQ + lane_sel + c * 16, v);
+      for (int hh = 0; hh < 2; ++hh) {
+        // the box written two halves ago must have been read by the bulk engine
+        if (lane == 0) tma_store_wait_read1();
+        __syncwarp();
+        uint32_t v[32];
+        tmem_ld_x32(tmem + kColDQ + lane_sel + hh * 32, v);
         tmem_ld_wait();
-        if (c == kQStep / 16 - 1) {
+        if (hh == 1) {
           tc_fence_before_sync();
           mbar_arrive_warp(dq_drained);   // the next dQ^T MMA may overwrite TMEM
         }
+        // row `lane` of the box: 32 queries = 128 bytes, 128-byte swizzle
+        uint8_t* row = my_boxes + hh * kDqBoxBytes + lane * 128;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t j = static_cast<uint32_t>(c * 16 + i);   // query row of the staging tile
-          *reinterpret_cast<uint32_t*>(my_box + j * 128 + (((f >> 2) ^ (j & 7u)) << 4) + (f & 3u) * 4) = v[i];
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(row + ((c ^ (lane & 7)) << 4)) =
+              make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_4d(&tm_dq_acc, my_boxes + hh * kDqBoxBytes, (first + n) * kQStep + hh * 32, wq * 32, h, b);
+          tma_store_commit();
         }
+        if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 2 + hh);
       }
-      fence_proxy_async_smem();
-      mbar_arrive_warp(drain_sync);
-      ok = mbar_wait(drain_sync, dphase & 1, abort_flag, p.status, kSiteDrain);
-      ++dphase;
-      if (!ok) break;
-      if (r == 0) {
-        const int row0 = (first + n) * kQStep;
-        for (int x = 0; x < D / 32; ++x) tma_reduce_add_4d(&tm_dq_acc, s_dq + x * (kQStep * 128), x * 32, row0, h, b);
-        tma_store_commit();
-        tma_store_wait_read();     // the staging tile may be overwritten once the bulk engine has read it
-      }
-      mbar_arrive_warp(drain_sync);
-      ok = mbar_wait(drain_sync, dphase & 1, abort_flag, p.status, kSiteDrain);
-      ++dphase;
-      if (!ok) break;
     }
-    if (r == 0) tma_store_wait_all();
+    if (lane == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ compute groups (thread = key row)
     setmaxnreg_inc<kComputeRegs>();
@@ -377,8 +408,11 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     bool ok = true;
 
     for (int n = 0; n < cnt; ++n) {
+      const bool tr = tid == kComputeWarp0 * 32;
+      if (tr) RBF_TRACE_EVENT(2, n, 0);
       ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
       if (!ok) break;
+      if (tr) RBF_TRACE_EVENT(2, n, 1);
       tc_fence_after_sync();
       float pr[16];
       {
@@ -387,6 +421,7 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         tmem_ld_wait();
         tc_fence_before_sync();
         mbar_arrive_warp(s_consumed);
+        if (tr) RBF_TRACE_EVENT(2, n, 2);
         // acc = k.q - L / scale2 ; P = exp2(acc * scale2 - ksq)
 #pragma unroll
         for (int i = 0; i < 16; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(raw[i]), p.scale2, neg_ksq));
@@ -402,19 +437,23 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         uint32_t packed[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) packed[i] = pack2<kBf16>(pr[2 * i], pr[2 * i + 1]);
+        if (tr) RBF_TRACE_EVENT(2, n, 3);
         if (n > 0) {   // the P^T columns are free once dV of the previous step has completed
           ok = mbar_wait(dv_done, (n - 1) & 1, abort_flag, p.status, kSiteDVDone);
           if (!ok) break;
           tc_fence_after_sync();
         }
+        if (tr) RBF_TRACE_EVENT(2, n, 4);
         tmem_st_x8(tmem + kColPT + lane_sel + g * 8, packed);
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive_warp(p_full);
       }
 
+      if (tr) RBF_TRACE_EVENT(2, n, 5);
       ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull);
       if (!ok) break;
+      if (tr) RBF_TRACE_EVENT(2, n, 6);
       tc_fence_after_sync();
       uint32_t ds_packed[8];
       {
@@ -423,6 +462,7 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         tmem_ld_wait();
         tc_fence_before_sync();
         mbar_arrive_warp(dp_consumed);
+        if (tr) RBF_TRACE_EVENT(2, n, 7);
         // acc = v.dO - delta ; dS = P * acc
         float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
@@ -435,17 +475,20 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         }
         ds_rowsum += rs0 + rs1;
       }
-      if (n > 0) {   // the dS^T tile is free once dK and dQ^T of the previous step have completed
-        ok = mbar_wait(dq_full, (n - 1) & 1, abort_flag, p.status, kSiteDsFree);
+      if (tr) RBF_TRACE_EVENT(2, n, 8);
+      if (n >= kDsStages) {   // the dS^T buffer is free once dK and dQ^T of its previous step have completed
+        ok = mbar_wait(&ds_free[n % kDsStages], ((n / kDsStages) - 1) & 1, abort_flag, p.status, kSiteDsFree);
         if (!ok) break;
       }
+      if (tr) RBF_TRACE_EVENT(2, n, 9);
       // row r of the [key][query] tile: 16-byte chunks 2g and 2g + 1
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch)
-        *reinterpret_cast<uint4*>(s_ds + sw128_offset(r, g * 2 + ch)) =
+        *reinterpret_cast<uint4*>(s_ds + (n % kDsStages) * kDsBytes + sw128_offset(r, g * 2 + ch)) =
             make_uint4(ds_packed[ch * 4 + 0], ds_packed[ch * 4 + 1], ds_packed[ch * 4 + 2], ds_packed[ch * 4 + 3]);
       fence_proxy_async_smem();
-      mbar_arrive_warp(ds_full);
+      mbar_arrive_warp(&ds_full[n % kDsStages]);
+      if (tr) RBF_TRACE_EVENT(2, n, 10);
     }
 
     uint32_t grp_phase = 0;
@@ -511,27 +554,33 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   if (warp == kMmaWarpA) tmem_dealloc(tmem, 512);
 }
 
-// dq[b,h,n,:] = scale * acc[b,h,n,:]  (acc fp32 contiguous, dq 16-bit with strides); one thread per 8 elements
+// dq[b,h,n,d] = scale * acc[b,h,d,n]: the accumulator is transposed, (B*H, D, n_pad) fp32. A block turns 32 queries
+// of one head around through shared memory: coalesced 128-byte reads along n, 16-byte writes along d.
 template <bool kBf16>
 __global__ void __launch_bounds__(256) dq_convert128_kernel(const float* __restrict__ acc, void* __restrict__ dq,
-                                                            int H, int N, int64_t sb, int64_t sh, int64_t sn,
-                                                            float scale, int64_t total_chunks) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= total_chunks) return;
-  const int64_t row = i >> 4;
-  const int ch = static_cast<int>(i & 15);
-  const int64_t n = row % N;
-  const int64_t bh = row / N;
-  const int64_t b = bh / H, h = bh % H;
-  const float4* src = reinterpret_cast<const float4*>(acc + row * D + ch * 8);
-  const float4 a = src[0], c = src[1];
-  uint4 o;
-  o.x = pack2<kBf16>(a.x * scale, a.y * scale);
-  o.y = pack2<kBf16>(a.z * scale, a.w * scale);
-  o.z = pack2<kBf16>(c.x * scale, c.y * scale);
-  o.w = pack2<kBf16>(c.z * scale, c.w * scale);
-  uint16_t* dst = reinterpret_cast<uint16_t*>(dq) + b * sb + h * sh + n * sn + ch * 8;
-  *reinterpret_cast<uint4*>(dst) = o;
+                                                            int H, int N, int n_pad, int64_t sb, int64_t sh,
+                                                            int64_t sn, float scale) {
+  __shared__ float tile[32][D + 1];
+  const int bh = blockIdx.y;
+  const int q0 = blockIdx.x * 32;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const float* src = acc + static_cast<int64_t>(bh) * D * n_pad + q0 + lane;
+#pragma unroll 4
+  for (int d = w; d < D; d += 8) tile[lane][d] = src[static_cast<int64_t>(d) * n_pad];
+  __syncthreads();
+  const int b = bh / H, h = bh % H;
+  uint16_t* dst = reinterpret_cast<uint16_t*>(dq) + b * sb + h * sh;
+  for (int i = threadIdx.x; i < 32 * (D / 8); i += 256) {
+    const int row = i / (D / 8), ch = i % (D / 8);
+    if (q0 + row >= N) continue;
+    const float* t = &tile[row][ch * 8];
+    uint4 o;
+    o.x = pack2<kBf16>(t[0] * scale, t[1] * scale);
+    o.y = pack2<kBf16>(t[2] * scale, t[3] * scale);
+    o.z = pack2<kBf16>(t[4] * scale, t[5] * scale);
+    o.w = pack2<kBf16>(t[6] * scale, t[7] * scale);
+    *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(q0 + row) * sn + ch * 8) = o;
+  }
 }
 
 template <bool kBf16>
@@ -544,7 +593,7 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const size_t acc_bytes = static_cast<size_t>(a.B) * a.H * a.N * D * sizeof(float);
+  const size_t acc_bytes = static_cast<size_t>(a.B) * a.H * a.n_pad * D * sizeof(float);
   cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, stream);
   if (e != cudaSuccess) return e;
   Params p{};
@@ -556,13 +605,19 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
                                            a.tm_dq_acc, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  const int64_t chunks = static_cast<int64_t>(a.B) * a.H * a.N * (D / 8);
-  dq_convert128_kernel<kBf16><<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(
-      a.dq_acc, a.dq, a.H, a.N, a.dq_strides[0], a.dq_strides[1], a.dq_strides[2], a.grad_scale, chunks);
+  dim3 cgrid(a.n_pad / 32, a.B * a.H);
+  dq_convert128_kernel<kBf16><<<cgrid, 256, 0, stream>>>(a.dq_acc, a.dq, a.H, a.N, a.n_pad, a.dq_strides[0],
+                                                        a.dq_strides[1], a.dq_strides[2], a.grad_scale);
   return cudaGetLastError();
 }
 
 }  // namespace bwdf128
+
+#ifdef RBF_TRACE
+extern "C" int rbf_b200_debug_read_trace128(long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, bwdf128::g_trace128, sizeof(long long) * n));
+}
+#endif
 
 cudaError_t launch_bwd_fused128(const BwdFusedArgs& a, bool bf16, cudaStream_t stream) {
   return bf16 ? bwdf128::launch_t<true>(a, stream) : bwdf128::launch_t<false>(a, stream);

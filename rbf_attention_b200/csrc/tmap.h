@@ -81,4 +81,21 @@ inline int make_tmap_f32_bhnd(CUtensorMap* out, const void* base, int B, int H, 
   return static_cast<int>(r);
 }
 
+// Tensor map over a transposed contiguous fp32 accumulator (B, H, D, n_pad): queries innermost. The box is
+// 32 queries (128 bytes, the swizzle span) by `box_rows` head-dim rows.
+inline int make_tmap_f32_bhdn(CUtensorMap* out, const void* base, int B, int H, int n_pad, int D, int box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return -1;
+  cuuint64_t gdim[4] = {static_cast<cuuint64_t>(n_pad), static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(H),
+                        static_cast<cuuint64_t>(B)};
+  cuuint64_t gstr[3] = {static_cast<cuuint64_t>(n_pad) * 4, static_cast<cuuint64_t>(n_pad) * D * 4,
+                        static_cast<cuuint64_t>(H) * n_pad * D * 4};
+  cuuint32_t box[4] = {32, static_cast<cuuint32_t>(box_rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return static_cast<int>(r);
+}
+
 }  // namespace rbf
