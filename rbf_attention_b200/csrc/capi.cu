@@ -265,7 +265,7 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     if (t1 != 0 || t2 != 0)
       return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the bias slabs (codes %d, %d)", t1, t2);
     const int t3 = D == 128 ? rbf::make_tmap_f32_bhdn(&f.tm_dq_acc, ws.dq_acc, B, H, n_pad, D, 32)
-                            : rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, q_rows);
+                            : rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, 32);
     if (t3 != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the dQ accumulator (code %d)", t3);
     f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
     f.ksq = ws.ksq; f.status = ws.status;

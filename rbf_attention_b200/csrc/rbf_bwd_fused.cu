@@ -52,11 +52,13 @@ static constexpr int kMmaWarpC = 3;
 static constexpr int kComputeWarp0 = 4;
 static constexpr int kDrainWarp0 = 20;
 // Register budget: the launch allocates 80 per thread (768 threads); setmaxnreg may only redistribute that
-// total: 512 * 96 + 256 * 40 = 59392 <= 768 * 80 = 61440. (An increase beyond what the decreases released blocks
+// total: 512 * 96 + 128 * 40 + 128 * 56 = 768 * 80. (An increase beyond what the decreases released blocks
 // forever, with no timeout.)
 static constexpr int kComputeRegs = 96;
 static constexpr int kOtherRegs = 40;
-static_assert(512 * kComputeRegs + 256 * kOtherRegs <= 768 * 80, "setmaxnreg budget");
+static constexpr int kDrainRegs = 56;
+static_assert(512 * kComputeRegs + 128 * kOtherRegs + 128 * kDrainRegs <= 768 * 80, "setmaxnreg budget");
+static constexpr int kDqBoxBytes = 32 * 128;        // 4 KB: fp32 [32 queries][32 columns] of one drain warp
 
 static constexpr int kTileBytes = kTile * D * 2;    // 16 KB: one 128 x 64 16-bit tile
 static constexpr int kSlabBytes = kTile * 32;       // 4 KB: 128 rows x 16 x 16-bit
@@ -72,7 +74,7 @@ struct Smem {
   static constexpr int kLSlab = kDs + kDsBytes;
   static constexpr int kDSlab = kLSlab + kStages * kSlabBytes;
   static constexpr int kOnes = kDSlab + kStages * kSlabBytes;
-  static constexpr int kDqStage = kOnes + kSlabBytes;          // 32 KB fp32 dQ_partial staging, two 32-column boxes
+  static constexpr int kDqStage = kOnes + kSlabBytes;          // 32 KB fp32 dQ_partial staging: four warps, two boxes each
   static constexpr int kRowsum = kDqStage + kTile * D * 4;     // [4 groups][128] floats: partial row sums
   static constexpr int kBars = kRowsum + 4 * kTile * 4;
   static constexpr int kNumBars = 1 + 4 * kStages + 12;
@@ -344,50 +346,48 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     }
   } else if (warp >= kDrainWarp0) {
     // ------------------------------------------------------------------ dQ_partial drain (thread = query row)
-    setmaxnreg_dec<kOtherRegs>();
-    const int r = tid - kDrainWarp0 * 32;
-    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    // Every warp stages and reduces its own 32 query rows: a [32 rows][32 floats] box per half of the head dim, two
+    // boxes in flight, one TMA bulk reduce-add each, no synchronisation between the warps. (An SM pushes about 25
+    // bytes per clock of reduce-adds into L2, measured: the 32 KB of a step take as long as its MMAs and must
+    // overlap them.)
+    setmaxnreg_dec<kDrainRegs>();
+    const int wq = warp & 3;
+    const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
+    uint8_t* my_boxes = s_dq + wq * (2 * kDqBoxBytes);
     bool ok = true;
-    uint32_t dphase = 0;
     for (int n = 0; n < cnt; ++n) {
-      if (r == 0) RBF_TRACE_EVENT(3, n, 0);
+      if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 0);
       ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull);
       if (!ok) break;
-      if (r == 0) RBF_TRACE_EVENT(3, n, 1);
+      if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 1);
       tc_fence_after_sync();
-      // TMEM -> registers -> swizzled fp32 staging tile -> one bulk reduce-add per 32-column box
 #pragma unroll
-      for (int c = 0; c < D / 16; ++c) {
-        uint32_t v[16];
-        tmem_ld_x16(tmem + kColDQ + lane_sel + c * 16, v);
+      for (int hh = 0; hh < 2; ++hh) {
+        // the box written two halves ago must have been read by the bulk engine
+        if (lane == 0) tma_store_wait_read1();
+        __syncwarp();
+        uint32_t v[32];
+        tmem_ld_x32(tmem + kColDQ + lane_sel + hh * 32, v);
         tmem_ld_wait();
-        if (c == D / 16 - 1) {
+        if (hh == 1) {
           tc_fence_before_sync();
           mbar_arrive_warp(dq_drained);   // the next dQ_partial MMA may overwrite TMEM
         }
+        uint8_t* row = my_boxes + hh * kDqBoxBytes + lane * 128;
 #pragma unroll
-        for (int g4 = 0; g4 < 4; ++g4)
-          *reinterpret_cast<uint4*>(s_dq + (c >> 1) * (kTile * 128) + sw128_offset(r, (c & 1) * 4 + g4)) =
-              make_uint4(v[g4 * 4 + 0], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(row + ((c ^ (lane & 7)) << 4)) =
+              make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_4d(&tm_dq_acc, my_boxes + hh * kDqBoxBytes, hh * 32, (first + n) * kTile + wq * 32, h, b);
+          tma_store_commit();
+        }
+        if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 2 + hh);
       }
-      fence_proxy_async_smem();
-      mbar_arrive_warp(drain_sync);
-      ok = mbar_wait(drain_sync, dphase & 1, abort_flag, p.status, kSiteGroup);
-      ++dphase;
-      if (!ok) break;
-      if (r == 0) {
-        const int row0 = (first + n) * kTile;
-        tma_reduce_add_4d(&tm_dq_acc, s_dq, 0, row0, h, b);
-        tma_reduce_add_4d(&tm_dq_acc, s_dq + kTile * 128, 32, row0, h, b);
-        tma_store_commit();
-        tma_store_wait_read();     // the staging tile may be overwritten once the bulk engine has read it
-      }
-      mbar_arrive_warp(drain_sync);
-      ok = mbar_wait(drain_sync, dphase & 1, abort_flag, p.status, kSiteGroup);
-      ++dphase;
-      if (!ok) break;
     }
-    if (r == 0) tma_store_wait_all();
+    if (lane == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ compute groups (thread = key row)
     setmaxnreg_inc<kComputeRegs>();
