@@ -75,9 +75,7 @@ Workspace carve(void* base, int B, int H, int N, int D, int softmax, int backwar
       w.dslab = p + off;
       off += slab;
       w.dq_acc = reinterpret_cast<float*>(p + off);
-      // D = 64: (B, H, N, D); D = 128: transposed, (B, H, D, padded N)
-      const size_t acc_rows = D == 128 ? static_cast<size_t>(rbf::padded_rows(N)) : static_cast<size_t>(N);
-      off += align256(static_cast<size_t>(B) * H * acc_rows * D * sizeof(float));
+      off += align256(static_cast<size_t>(B) * H * N * D * sizeof(float));
     }
   }
   w.bytes = off;
@@ -264,9 +262,11 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     const int t2 = rbf::make_tmap_slab16(&f.tm_dslab, ws.dslab, bf16, B * H, n_pad, q_rows);
     if (t1 != 0 || t2 != 0)
       return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the bias slabs (codes %d, %d)", t1, t2);
-    const int t3 = D == 128 ? rbf::make_tmap_f32_bhdn(&f.tm_dq_acc, ws.dq_acc, B, H, n_pad, D, 32)
-                            : rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, 32);
-    if (t3 != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the dQ accumulator (code %d)", t3);
+    if (D == 64) {
+      const int t3 = rbf::make_tmap_f32_bhnd(&f.tm_dq_acc, ws.dq_acc, B, H, N, D, 32);
+      if (t3 != 0)
+        return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the dQ accumulator (code %d)", t3);
+    }
     f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
     f.ksq = ws.ksq; f.status = ws.status;
     f.B = B; f.H = H; f.N = N; f.n_pad = n_pad; f.causal = causal ? 1 : 0;

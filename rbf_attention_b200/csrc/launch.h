@@ -71,8 +71,8 @@ cudaError_t launch_bwd_dq(const BwdArgs& a, bool bf16, int D, bool softmax, cuda
 struct BwdFusedArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_do, tm_dk, tm_dv;
   CUtensorMap tm_lslab, tm_dslab;  // (B*H, n_pad, 16) bias slabs of -L / scale2 and -delta, box 16 x 128
-  CUtensorMap tm_dq_acc;  // fp32 accumulator, 128-byte boxes, 128-byte swizzle
-  float* dq_acc;          // fp32 accumulator: (B, H, N, 64), or transposed (B, H, 128, n_pad) at head dim 128
+  CUtensorMap tm_dq_acc;  // head dim 64: the accumulator as 32-float x 32-row boxes, 128-byte swizzle
+  float* dq_acc;          // fp32 (B, H, N, D) contiguous accumulator
   void* dq;               // final dQ in the operand type
   int64_t dq_strides[3];
   const float* ksq;       // (B*H, n_pad)

@@ -143,6 +143,11 @@ __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
+// Fire-and-forget fp32 add into global memory (performed in L2).
+__device__ __forceinline__ void red_add_f32(float* dst, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(v) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // tcgen05: tensor memory management
 // ---------------------------------------------------------------------------------------------

@@ -10,10 +10,11 @@
 //   dV  [128 x 128] += P^T dO          TMEM x smem (P^T: 32 TMEM columns of 16-bit pairs)
 //   dK  [128 x 128] += dS^T Q          smem x smem (dS^T: a [key][query] tile of 128-byte rows)
 //   dQ^T[128 d x 64 q] = K^T dS^T      smem x smem (K read M-major, the dS^T tile read N-major)
-// dQ^T leaves the CTA as it is: the global fp32 accumulator is kept transposed, (B, H, D, n_pad), so that a thread
-// of the drain warps (thread = head-dim index) owns contiguous runs of queries. Each drain warp stages its own
-// 32 x 32 box and issues its own TMA bulk reduce-add, two staging boxes per warp in flight; a small kernel
-// transposes, scales and converts the accumulator afterwards. (Every SM can push about 25 bytes per clock of
+// dQ^T leaves the CTA straight from registers: a drain thread owns one head-dim index, so for every query of the
+// step the 32 lanes of a warp hold 32 consecutive floats of the (B, H, N, D) fp32 accumulator and one scalar
+// red.global.add per query is a coalesced 128-byte line. No shared-memory staging: shared-memory bandwidth is
+// what bounds this kernel (the MMA operand fetch alone runs at about 120 of the 128 bytes per clock). A small
+// kernel scales and converts the accumulator afterwards. (Every SM can push about 25 bytes per clock of
 // reduce-adds into L2, measured; a step's 32 KB of dQ therefore takes as long as its MMAs and must overlap them.)
 //
 // TMEM columns: S^T [0,64), dP^T [64,128), P^T [128,160), dQ^T [160,224), dV [256,384), dK [384,512).
@@ -64,11 +65,9 @@ static constexpr int kQTileBytes = 2 * kQBoxBytes;        // Q or dO step tile
 static constexpr int kSlabBytes = kQStep * 32;            // 2 KB: 64 rows x 16 x 16-bit
 static constexpr int kOnesBytes = kTile * 32;
 static constexpr int kQStages = 3;
-static constexpr int kDoStages = 2;
+static constexpr int kDoStages = 3;
 static constexpr int kDsBytes = kTile * 128;              // 16 KB: dS^T as [128 keys][64 queries]; two buffers
 static constexpr int kDsStages = 2;
-static constexpr int kDqBoxBytes = 32 * 128;              // 4 KB: fp32 [32 d][32 q] of one drain warp
-static constexpr int kDqStageBytes = 4 * 2 * kDqBoxBytes; // 32 KB: four warps, two boxes in flight each
 
 struct Smem {
   static constexpr int kK = 0;
@@ -76,8 +75,7 @@ struct Smem {
   static constexpr int kQ = kV + kKvBytes;
   static constexpr int kDo = kQ + kQStages * kQTileBytes;
   static constexpr int kDs = kDo + kDoStages * kQTileBytes;
-  static constexpr int kDqStage = kDs + kDsStages * kDsBytes;
-  static constexpr int kLSlab = kDqStage + kDqStageBytes;
+  static constexpr int kLSlab = kDs + kDsStages * kDsBytes;
   static constexpr int kDSlab = kLSlab + kQStages * kSlabBytes;
   static constexpr int kOnes = kDSlab + kDoStages * kSlabBytes;
   static constexpr int kRowsum = kOnes + kOnesBytes;         // [4 groups][128] floats
@@ -99,6 +97,7 @@ enum Site : uint32_t {
 
 struct Params {
   const float* ksq;      // (B*H, n_pad), +inf on padding rows
+  float* dq_acc;         // fp32 (B, H, N, 128), zero-initialised
   DeviceStatus* status;
   int H, N, n_pad, causal;
   float scale2, grad_scale, slab_w;
@@ -110,7 +109,7 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
                         const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                         const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                         const __grid_constant__ CUtensorMap tm_lslab, const __grid_constant__ CUtensorMap tm_dslab,
-                        const __grid_constant__ CUtensorMap tm_dq_acc, const Params p) {
+                        const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_k = smem + Smem::kK;
@@ -118,7 +117,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   uint8_t* s_q = smem + Smem::kQ;
   uint8_t* s_do = smem + Smem::kDo;
   uint8_t* s_ds = smem + Smem::kDs;
-  uint8_t* s_dq = smem + Smem::kDqStage;
   uint8_t* s_lslab = smem + Smem::kLSlab;
   uint8_t* s_dslab = smem + Smem::kDSlab;
   uint8_t* s_ones = smem + Smem::kOnes;
@@ -361,7 +359,7 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     setmaxnreg_dec<kDrainRegs>();
     const int wq = warp & 3;                                // TMEM lane quadrant = 32 head-dim rows
     const uint32_t lane_sel = static_cast<uint32_t>(wq * 32) << 16;
-    uint8_t* my_boxes = s_dq + wq * (2 * kDqBoxBytes);      // this warp's two staging boxes
+    float* acc_col = p.dq_acc + static_cast<int64_t>(bh) * p.N * D + wq * 32 + lane;
     bool ok = true;
     for (int n = 0; n < cnt; ++n) {
       if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 0);
@@ -369,11 +367,11 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       if (!ok) break;
       if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 1);
       tc_fence_after_sync();
+      const int q0 = (first + n) * kQStep;
+      const int valid = p.N - q0;                           // queries of this step inside the sequence
+      float* dst = acc_col + static_cast<int64_t>(q0) * D;
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        // the box written two halves ago must have been read by the bulk engine
-        if (lane == 0) tma_store_wait_read1();
-        __syncwarp();
         uint32_t v[32];
         tmem_ld_x32(tmem + kColDQ + lane_sel + hh * 32, v);
         tmem_ld_wait();
@@ -381,22 +379,17 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
           tc_fence_before_sync();
           mbar_arrive_warp(dq_drained);   // the next dQ^T MMA may overwrite TMEM
         }
-        // row `lane` of the box: 32 queries = 128 bytes, 128-byte swizzle
-        uint8_t* row = my_boxes + hh * kDqBoxBytes + lane * 128;
+        if (valid >= kQStep) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(row + ((c ^ (lane & 7)) << 4)) =
-              make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_reduce_add_4d(&tm_dq_acc, my_boxes + hh * kDqBoxBytes, (first + n) * kQStep + hh * 32, wq * 32, h, b);
-          tma_store_commit();
+          for (int i = 0; i < 32; ++i) red_add_f32(dst + (hh * 32 + i) * D, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (hh * 32 + i < valid) red_add_f32(dst + (hh * 32 + i) * D, __uint_as_float(v[i]));
         }
         if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 2 + hh);
       }
     }
-    if (lane == 0) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------------ compute groups (thread = key row)
     setmaxnreg_inc<kComputeRegs>();
@@ -554,33 +547,27 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   if (warp == kMmaWarpA) tmem_dealloc(tmem, 512);
 }
 
-// dq[b,h,n,d] = scale * acc[b,h,d,n]: the accumulator is transposed, (B*H, D, n_pad) fp32. A block turns 32 queries
-// of one head around through shared memory: coalesced 128-byte reads along n, 16-byte writes along d.
+// dq[b,h,n,:] = scale * acc[b,h,n,:]  (acc fp32 contiguous, dq 16-bit with strides); one thread per 8 elements
 template <bool kBf16>
 __global__ void __launch_bounds__(256) dq_convert128_kernel(const float* __restrict__ acc, void* __restrict__ dq,
-                                                            int H, int N, int n_pad, int64_t sb, int64_t sh,
-                                                            int64_t sn, float scale) {
-  __shared__ float tile[32][D + 1];
-  const int bh = blockIdx.y;
-  const int q0 = blockIdx.x * 32;
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const float* src = acc + static_cast<int64_t>(bh) * D * n_pad + q0 + lane;
-#pragma unroll 4
-  for (int d = w; d < D; d += 8) tile[lane][d] = src[static_cast<int64_t>(d) * n_pad];
-  __syncthreads();
-  const int b = bh / H, h = bh % H;
-  uint16_t* dst = reinterpret_cast<uint16_t*>(dq) + b * sb + h * sh;
-  for (int i = threadIdx.x; i < 32 * (D / 8); i += 256) {
-    const int row = i / (D / 8), ch = i % (D / 8);
-    if (q0 + row >= N) continue;
-    const float* t = &tile[row][ch * 8];
-    uint4 o;
-    o.x = pack2<kBf16>(t[0] * scale, t[1] * scale);
-    o.y = pack2<kBf16>(t[2] * scale, t[3] * scale);
-    o.z = pack2<kBf16>(t[4] * scale, t[5] * scale);
-    o.w = pack2<kBf16>(t[6] * scale, t[7] * scale);
-    *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(q0 + row) * sn + ch * 8) = o;
-  }
+                                                            int H, int N, int64_t sb, int64_t sh, int64_t sn,
+                                                            float scale, int64_t total_chunks) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total_chunks) return;
+  const int64_t row = i >> 4;
+  const int ch = static_cast<int>(i & 15);
+  const int64_t n = row % N;
+  const int64_t bh = row / N;
+  const int64_t b = bh / H, h = bh % H;
+  const float4* src = reinterpret_cast<const float4*>(acc + row * D + ch * 8);
+  const float4 a = src[0], c = src[1];
+  uint4 o;
+  o.x = pack2<kBf16>(a.x * scale, a.y * scale);
+  o.y = pack2<kBf16>(a.z * scale, a.w * scale);
+  o.z = pack2<kBf16>(c.x * scale, c.y * scale);
+  o.w = pack2<kBf16>(c.z * scale, c.w * scale);
+  uint16_t* dst = reinterpret_cast<uint16_t*>(dq) + b * sb + h * sh + n * sn + ch * 8;
+  *reinterpret_cast<uint4*>(dst) = o;
 }
 
 template <bool kBf16>
@@ -593,21 +580,21 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const size_t acc_bytes = static_cast<size_t>(a.B) * a.H * a.n_pad * D * sizeof(float);
+  const size_t acc_bytes = static_cast<size_t>(a.B) * a.H * a.N * D * sizeof(float);
   cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, stream);
   if (e != cudaSuccess) return e;
   Params p{};
-  p.ksq = a.ksq; p.status = a.status;
+  p.ksq = a.ksq; p.dq_acc = a.dq_acc; p.status = a.status;
   p.H = a.H; p.N = a.N; p.n_pad = a.n_pad; p.causal = a.causal;
   p.scale2 = a.scale2; p.grad_scale = a.grad_scale; p.slab_w = a.slab_w;
   dim3 grid((a.N + kTile - 1) / kTile, a.B * a.H);
   kernel<<<grid, kThreads, smem, stream>>>(a.tm_k, a.tm_v, a.tm_q, a.tm_do, a.tm_dk, a.tm_dv, a.tm_lslab, a.tm_dslab,
-                                           a.tm_dq_acc, p);
+                                           p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  dim3 cgrid(a.n_pad / 32, a.B * a.H);
-  dq_convert128_kernel<kBf16><<<cgrid, 256, 0, stream>>>(a.dq_acc, a.dq, a.H, a.N, a.n_pad, a.dq_strides[0],
-                                                        a.dq_strides[1], a.dq_strides[2], a.grad_scale);
+  const int64_t chunks = static_cast<int64_t>(a.B) * a.H * a.N * (D / 8);
+  dq_convert128_kernel<kBf16><<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(
+      a.dq_acc, a.dq, a.H, a.N, a.dq_strides[0], a.dq_strides[1], a.dq_strides[2], a.grad_scale, chunks);
   return cudaGetLastError();
 }
 

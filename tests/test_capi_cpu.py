@@ -39,7 +39,7 @@ def test_abi_version_and_workspace_size(built_library):
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 0) == 256 + slab
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 0) == 256 + slab + rows
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 1) == 256 + 3 * rows + 2 * slab + 2 * 3 * 200 * 64 * 4
-    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 128, 1, 1) == 256 + 3 * rows + 2 * slab + 2 * 3 * 256 * 128 * 4
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 128, 1, 1) == 256 + 3 * rows + 2 * slab + 2 * 3 * 200 * 128 * 4
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 128, 0, 1) == 256 + 3 * rows
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 1) == 256 + 3 * rows
     assert lib.rbf_b200_workspace_bytes(0, 3, 200, 64, 1, 0) == 0
