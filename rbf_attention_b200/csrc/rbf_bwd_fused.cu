@@ -134,7 +134,6 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   uint64_t* dq_drained = dq_full + 1;        // drain warps have read dQ_partial(n) out of TMEM
   uint64_t* acc_done = dq_drained + 1;       // two arrivals: all MMAs of both issuers complete
   uint64_t* grp_sync = acc_done + 1;         // compute warps (16 arrivals)
-  uint64_t* drain_sync = grp_sync + 1;       // drain warps (4 arrivals)
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + Smem::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 4);
 
@@ -149,12 +148,22 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   const int first = p.causal ? kt : 0;             // first query tile that sees these keys
   const int cnt = n_tiles - first;
 
-  // A wait that ran out in an earlier CTA of this launch ends the whole launch quickly: later CTAs leave at once.
-  if (tid == 0) *abort_flag = (*reinterpret_cast<volatile unsigned int*>(&p.status->code) != 0u) ? 1 : 0;
-  __syncthreads();
-  if (*abort_flag) return;
-
-  if (tid == 0) {
+  // One thread (the TMA producer) sets the CTA up: it reads the launch's status word (a wait that ran out in an
+  // earlier CTA ends the whole launch quickly: later CTAs leave at once), initialises the barriers while that load
+  // is in flight, and issues the first loads before the CTA-wide synchronisation so that K, V and the first query
+  // tiles travel while TMEM is allocated and the constant slab is written.
+  auto load_step = [&](int n) {
+    const int row0 = (first + n) * kTile;
+    const int st = n % kStages;
+    mbar_arrive_expect_tx(&q_full[st], kTileBytes + kSlabBytes);
+    tma_load_4d(s_q + st * kTileBytes, &tm_q, &q_full[st], 0, row0, h, b);
+    tma_load_3d(s_lslab + st * kSlabBytes, &tm_lslab, &q_full[st], 0, row0, bh);
+    mbar_arrive_expect_tx(&do_full[st], kTileBytes + kSlabBytes);
+    tma_load_4d(s_do + st * kTileBytes, &tm_do, &do_full[st], 0, row0, h, b);
+    tma_load_3d(s_dslab + st * kSlabBytes, &tm_dslab, &do_full[st], 0, row0, bh);
+  };
+  if (tid == kLoadWarp * 32) {
+    const unsigned int earlier = *reinterpret_cast<volatile unsigned int*>(&p.status->code);
     mbar_init(kv_full, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&q_full[s], 1);
@@ -173,8 +182,20 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     mbar_init(dq_drained, 4);
     mbar_init(acc_done, 3);
     mbar_init(grp_sync, kNumComputeWarps);
-    mbar_init(drain_sync, 4);
     fence_mbar_init();
+    *abort_flag = earlier != 0u ? 1 : 0;
+    if (earlier == 0u) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_lslab);
+      tma_prefetch_desc(&tm_dslab);
+      mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
+      tma_load_4d(s_k, &tm_k, kv_full, 0, k_row0, h, b);
+      tma_load_4d(s_v, &tm_v, kv_full, 0, k_row0, h, b);
+      for (int n = 0; n < cnt && n < kStages; ++n) load_step(n);
+    }
   }
   if (warp == kMmaWarpA) {
     tmem_alloc(tmem_base_s, 512);
@@ -191,6 +212,10 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_base_s;
+  if (*abort_flag) {
+    if (warp == kMmaWarpA) tmem_dealloc(tmem, 512);
+    return;
+  }
 
   if (warp < kComputeWarp0) {
     setmaxnreg_dec<kOtherRegs>();
@@ -198,27 +223,13 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_do);
-      tma_prefetch_desc(&tm_lslab);
-      tma_prefetch_desc(&tm_dslab);
-      mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
-      tma_load_4d(s_k, &tm_k, kv_full, 0, k_row0, h, b);
-      tma_load_4d(s_v, &tm_v, kv_full, 0, k_row0, h, b);
-      for (int n = 0; n < cnt; ++n) {
-        const int row0 = (first + n) * kTile;
+      for (int n = kStages; n < cnt; ++n) {
         const int st = n % kStages;
         const uint32_t par = ((n / kStages) - 1) & 1;
-        if (n >= kStages && !mbar_wait(&q_empty[st], par, abort_flag, p.status, kSiteQEmpty)) break;
-        mbar_arrive_expect_tx(&q_full[st], kTileBytes + kSlabBytes);
-        tma_load_4d(s_q + st * kTileBytes, &tm_q, &q_full[st], 0, row0, h, b);
-        tma_load_3d(s_lslab + st * kSlabBytes, &tm_lslab, &q_full[st], 0, row0, bh);
-        if (n >= kStages && !mbar_wait(&do_empty[st], par, abort_flag, p.status, kSiteDoEmpty)) break;
-        mbar_arrive_expect_tx(&do_full[st], kTileBytes + kSlabBytes);
-        tma_load_4d(s_do + st * kTileBytes, &tm_do, &do_full[st], 0, row0, h, b);
-        tma_load_3d(s_dslab + st * kSlabBytes, &tm_dslab, &do_full[st], 0, row0, bh);
+        // the ring slot is free once the MMAs that read it have completed (both rings, in the order the loads go)
+        if (!mbar_wait(&q_empty[st], par, abort_flag, p.status, kSiteQEmpty)) break;
+        if (!mbar_wait(&do_empty[st], par, abort_flag, p.status, kSiteDoEmpty)) break;
+        load_step(n);
       }
     }
   } else if (warp == kMmaWarpA || warp == kMmaWarpB || warp == kMmaWarpC) {
@@ -529,7 +540,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       if (ok && r == 0 && (g & 1) == 0) {
         tma_store_4d(is_dk ? &tm_dk : &tm_dv, stage, 0, k_row0, h, b);
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();   // the CTA may exit once the staging tile has been read
       }
     }
   }
