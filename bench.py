@@ -261,7 +261,7 @@ def run_ours(args, w, rank, world, local_rank):
     with ClockSampler(local_rank) as clocks:
         ms = time_loop(torch, runner.step, args.steps)
         # per-kernel times for the roofline line (same buffers, same stream)
-        fused = bool(w["softmax"])               # single-kernel backward (plus memset and dQ convert)
+        fused = True                             # single-kernel backward (plus memset and dQ convert)
         phase_ms = {"fwd": time_loop(torch, lambda: runner.fwd(2), args.steps)}
         if fused:
             phase_ms["bwd_fused"] = time_loop(torch, lambda: runner.bwd(2), args.steps)
@@ -352,6 +352,10 @@ def run_ours(args, w, rank, world, local_rank):
         # dQ kernel 1 (dQ; its S and dP are recomputation and are not counted)
         # single-kernel backward: all 5
         gemms = {"fwd": 2, "bwd_fused": 5} if fused else {"fwd": 2, "bwd_dkdv": 4, "bwd_dq": 1}
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture of a quarter of the batch
+        # (profiles/ncu_full_fwd_bwd_fused_config2_quarter.md), times four: traffic grows in proportion to B
+        ncu_traffic = {("config2", "bwd_fused"): 4 * (109.632768e6 + 33.296640e6),
+                       ("config2", "fwd"): 4 * (54.691328e6 + 4.901888e6)}
         dom = max(gemms, key=lambda n: phase_ms[n])
         unit_flops = 2.0 * w["B"] * w["H"] * float(w["N"]) ** 2 * w["D"] * (0.5 if w["causal"] else 1.0)
         achieved = gemms[dom] * unit_flops / (phase_ms[dom] * 1e-3) / 1e12
@@ -367,7 +371,8 @@ def run_ours(args, w, rank, world, local_rank):
             "frac_of_peak": value / world / peak,
             "phase_ms": phase_ms,
             "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": ncu_traffic.get((args.workload, dom)),
+                         "traffic_unit": "bytes per launch (ncu, quarter batch x 4)", "peak_source": peak_src,
                          "algorithmic_gemms_per_launch": gemms[dom]},
             "cpu_baseline": {"value": cpu_tf, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"{pairs} x one (batch, head) pair at full N (fp32 PyTorch CPU math, "

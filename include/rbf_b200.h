@@ -69,7 +69,9 @@ int rbf_b200_fwd(const void* q, const void* k, const void* v, void* out, float* 
 
 /* Backward. Replaces rbf_scaled_bwd (rbf_attention.py:702-810: _bwd_preprocess, dK/dV kernel, dQ kernel)
  * when softmax = 1 and rbf_non_softmax_bwd (rbf_attention.py:1399-1480) when softmax = 0.
- *   out, lse : the forward's results; ignored (may be NULL) when softmax = 0.
+ *   out, lse : the forward's results. lse is ignored (may be NULL) when softmax = 0. out is optional when
+ *              softmax = 0 (the reference's operator does not have it): with it the backward runs as one kernel
+ *              (rowsum_j dS_ij = dO_i . O_i feeds the query-norm term), without it as the reference's two.
  *   dq, dk, dv : (B, H, N, D) in `dtype`. dk includes the gradient through the key-norm term
  *                (rbf_attention.py:447); for softmax = 0, dq includes the query-norm term (:1336). */
 int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, const float* lse, const void* dout,
@@ -80,9 +82,12 @@ int rbf_b200_bwd(const void* q, const void* k, const void* v, const void* out, c
                  float sm_scale, void* stream);
 
 /* The same calls restricted to some of their kernels, for per-kernel timing and profiling. `phases` is a
- * mask of RBF_B200_PHASE_*: the pre-passes (key / query norms, delta), the main kernel (forward; dK/dV in the
- * backward) and the backward's second kernel (dQ). Skipped phases leave the workspace contents of an earlier
- * full call in place. No counterpart in the reference, whose launchers always run every kernel. */
+ * mask of RBF_B200_PHASE_*: the pre-pass (key / query norms, delta, bias slabs; in the backward it also clears
+ * the fp32 dQ accumulator), the main kernel (forward; the single-kernel backward with its dQ conversion, or dK/dV
+ * of the two-kernel backward) and the two-kernel backward's second kernel (dQ). Skipped phases leave the workspace
+ * contents of an earlier call in place: a backward MAIN without its PREPASS adds to the accumulator of the
+ * previous call, which is fine for timing and wrong for results. No counterpart in the reference, whose launchers
+ * always run every kernel. */
 #define RBF_B200_PHASE_PREPASS 1
 #define RBF_B200_PHASE_MAIN 2
 #define RBF_B200_PHASE_MAIN2 4

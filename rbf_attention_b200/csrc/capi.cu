@@ -38,8 +38,10 @@ struct Workspace {
   size_t bytes;
 };
 
-// The softmax backward runs as one kernel that accumulates dQ in fp32 global memory (a kernel per head dim).
-bool use_fused_backward(int D, int softmax) { return softmax && (D == 64 || D == 128); }
+// The backward runs as one kernel that accumulates dQ in fp32 global memory (a kernel per head dim). The non-softmax
+// variant needs the forward output for it (rowsum_j dS_ij = dO_i . O_i); without `out` it takes the two-kernel path.
+// The workspace is sized for the single kernel in every case.
+bool use_fused_backward(int D, int softmax, bool have_out) { return (softmax || have_out) && (D == 64 || D == 128); }
 
 // Constant held by the operand-side slab of a bias-slab MMA step, and the "minus infinity" the slabs use on padding
 // rows. fp16 needs the range extension: a bias up to 65504 * 256 stays representable.
@@ -69,7 +71,7 @@ Workspace carve(void* base, int B, int H, int N, int D, int softmax, int backwar
     off += vec;
     w.delta = reinterpret_cast<float*>(p + off);
     off += vec;
-    if (use_fused_backward(D, softmax)) {
+    if (D == 64 || D == 128) {
       w.lslab = p + off;
       off += slab;
       w.dslab = p + off;
@@ -207,10 +209,11 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
   if ((rc = check_tensor("dq", dq, dq_strides, B, H, N, D))) return rc;
   if ((rc = check_tensor("dk", dk, dk_strides, B, H, N, D))) return rc;
   if ((rc = check_tensor("dv", dv, dv_strides, B, H, N, D))) return rc;
-  if (softmax) {
+  if (softmax || out != nullptr) {
     if ((rc = check_tensor("out", out, o_strides, B, H, N, D))) return rc;
-    if (lse == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "lse is NULL");
   }
+  if (softmax && lse == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "lse is NULL");
+  const bool fused = use_fused_backward(D, softmax, out != nullptr);
   if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL or not 256-byte aligned");
   const Workspace ws = carve(workspace, B, H, N, D, softmax, 1);
@@ -235,7 +238,7 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     rbf::RowStatsArgs r{};
     r.B = B; r.H = H; r.N = N; r.n_pad = n_pad; r.scale = c; r.status_to_clear = ws.status;
     r.scale2 = 2.f * c; r.slab_w = slab_w(bf16); r.slab_big = slab_big(bf16);
-    r.lslab_out = ws.lslab; r.dslab_out = ws.dslab;   // null unless the single-kernel backward runs
+    if (fused) { r.lslab_out = ws.lslab; r.dslab_out = ws.dslab; r.zero_rows = ws.dq_acc; }
     r.k = k; r.ksq_out = ws.ksq; set_strides(r.ks, k_strides);
     r.delta_out = ws.delta;                     // written as zeros when there is no O (non-softmax variant)
     if (softmax) {
@@ -243,12 +246,17 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
       r.lse = lse; r.lse_pad_out = ws.row_bias;
     } else {
       r.q = q; r.qsq_out = ws.row_bias; r.qsq_pad = INFINITY; set_strides(r.qs, q_strides);
+      if (fused) {
+        // single kernel: the L slab carries -qsq, nothing is subtracted from dP, delta feeds the dQ correction
+        r.o = out; r.dout = dout; set_strides(r.os, o_strides); set_strides(r.dos, do_strides);
+        r.lslab_from_qsq = 1; r.dslab_zero = 1;
+      }
     }
     e = rbf::launch_row_stats(r, bf16, D, stream);
     if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "pre-pass launch failed: %s", cudaGetErrorString(e));
   }
 
-  if (use_fused_backward(D, softmax)) {
+  if (fused) {
     if (!(phases & (RBF_B200_PHASE_MAIN | RBF_B200_PHASE_MAIN2))) return RBF_B200_OK;
     rbf::BwdFusedArgs f{};
     f.tm_q = a.tm_q; f.tm_k = a.tm_k; f.tm_v = a.tm_v; f.tm_do = a.tm_do; f.tm_dk = a.tm_dk; f.tm_dv = a.tm_dv;
@@ -269,6 +277,7 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     }
     f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
     f.ksq = ws.ksq; f.status = ws.status;
+    if (!softmax) { f.q_rows = q; set_strides(f.q_strides, q_strides); f.delta = ws.delta; }
     f.B = B; f.H = H; f.N = N; f.n_pad = n_pad; f.causal = causal ? 1 : 0;
     f.scale2 = 2.f * c; f.grad_scale = 2.f * sm_scale; f.slab_w = slab_w(bf16);
     e = D == 128 ? rbf::launch_bwd_fused128(f, bf16, stream) : rbf::launch_bwd_fused(f, bf16, stream);

@@ -25,6 +25,9 @@ struct RowStatsArgs {
   void* kslab_out;        // -ksq / (scale2 * slab_w); -slab_big on padding rows
   void* lslab_out;        // -lse / (scale2 * slab_w); -slab_big on padding rows
   void* dslab_out;        // -delta / slab_w; 0 on padding rows
+  float* zero_rows;       // optional (B, H, N, D) fp32 array to clear (the backward's dQ accumulator)
+  int lslab_from_qsq;     // non-softmax variant: the L slab carries -qsq / (scale2 * slab_w) instead
+  int dslab_zero;         // non-softmax variant: dS = P * dP, nothing is subtracted
   float scale2, slab_w, slab_big;
   int64_t ks[3], qs[3], os[3], dos[3];   // element strides of dims b, h, n
   int B, H, N, n_pad;
@@ -76,6 +79,10 @@ struct BwdFusedArgs {
   void* dq;               // final dQ in the operand type
   int64_t dq_strides[3];
   const float* ksq;       // (B*H, n_pad)
+  // non-softmax variant: dQ = 2 gamma (acc - delta * q) with delta = rowsum(O * dO) = rowsum_j dS_ij; null otherwise
+  const void* q_rows;
+  int64_t q_strides[3];
+  const float* delta;     // (B*H, n_pad)
   DeviceStatus* status;
   int B, H, N, n_pad;
   int causal;

@@ -551,7 +551,9 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
 template <bool kBf16>
 __global__ void __launch_bounds__(256) dq_convert128_kernel(const float* __restrict__ acc, void* __restrict__ dq,
                                                             int H, int N, int64_t sb, int64_t sh, int64_t sn,
-                                                            float scale, int64_t total_chunks) {
+                                                            float scale, int64_t total_chunks,
+                                                            const void* __restrict__ q, int64_t qsb, int64_t qsh,
+                                                            int64_t qsn, const float* __restrict__ delta, int n_pad) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total_chunks) return;
   const int64_t row = i >> 4;
@@ -560,7 +562,17 @@ __global__ void __launch_bounds__(256) dq_convert128_kernel(const float* __restr
   const int64_t bh = row / N;
   const int64_t b = bh / H, h = bh % H;
   const float4* src = reinterpret_cast<const float4*>(acc + row * D + ch * 8);
-  const float4 a = src[0], c = src[1];
+  float4 a = src[0], c = src[1];
+  if (q != nullptr) {
+    // non-softmax variant: subtract delta[row] * q[row, :]
+    const float w = delta[bh * n_pad + n];
+    const uint4 qv = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(q) + b * qsb + h * qsh +
+                                                     n * qsn + ch * 8);
+    const float2 q0 = unpack2<kBf16>(qv.x), q1 = unpack2<kBf16>(qv.y), q2 = unpack2<kBf16>(qv.z),
+                 q3 = unpack2<kBf16>(qv.w);
+    a.x = fmaf(-w, q0.x, a.x); a.y = fmaf(-w, q0.y, a.y); a.z = fmaf(-w, q1.x, a.z); a.w = fmaf(-w, q1.y, a.w);
+    c.x = fmaf(-w, q2.x, c.x); c.y = fmaf(-w, q2.y, c.y); c.z = fmaf(-w, q3.x, c.z); c.w = fmaf(-w, q3.y, c.w);
+  }
   uint4 o;
   o.x = pack2<kBf16>(a.x * scale, a.y * scale);
   o.y = pack2<kBf16>(a.z * scale, a.w * scale);
@@ -580,9 +592,8 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const size_t acc_bytes = static_cast<size_t>(a.B) * a.H * a.N * D * sizeof(float);
-  cudaError_t e = cudaMemsetAsync(a.dq_acc, 0, acc_bytes, stream);
-  if (e != cudaSuccess) return e;
+  // the pre-pass has cleared the dQ accumulator
+  cudaError_t e = cudaSuccess;
   Params p{};
   p.ksq = a.ksq; p.dq_acc = a.dq_acc; p.status = a.status;
   p.H = a.H; p.N = a.N; p.n_pad = a.n_pad; p.causal = a.causal;
@@ -594,7 +605,8 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   const int64_t chunks = static_cast<int64_t>(a.B) * a.H * a.N * (D / 8);
   dq_convert128_kernel<kBf16><<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(
-      a.dq_acc, a.dq, a.H, a.N, a.dq_strides[0], a.dq_strides[1], a.dq_strides[2], a.grad_scale, chunks);
+      a.dq_acc, a.dq, a.H, a.N, a.dq_strides[0], a.dq_strides[1], a.dq_strides[2], a.grad_scale, chunks, a.q_rows,
+      a.q_strides[0], a.q_strides[1], a.q_strides[2], a.delta, a.n_pad);
   return cudaGetLastError();
 }
 

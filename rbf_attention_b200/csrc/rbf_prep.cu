@@ -3,6 +3,8 @@
 //   qsq[row]     = c * |q_row|^2            (non-softmax variant)
 //   delta[row]   = sum_d O[row,d] dO[row,d] (softmax backward; 0 on padding rows)
 //   lse_pad[row] = lse[row]                 (softmax backward: the forward's L re-pitched to n_pad, +inf padding)
+//   the backward's fp32 dQ accumulator is cleared on the way
+//   bias slabs of -ksq, of -L (or -qsq, non-softmax variant) and of -delta (or zeros) for the MMA bias steps
 // Pure HBM streaming: D/8 lanes per row with 16-byte loads, 32/(D/8) rows per warp per iteration.
 #include "common.cuh"
 #include "launch.h"
@@ -61,6 +63,15 @@ __global__ void __launch_bounds__(256) row_stats_kernel(const RowStatsArgs a) {
   const int row_begin = blockIdx.x * rows_per_block;
   const int64_t out_base = static_cast<int64_t>(bh) * a.n_pad;
 
+  if (a.zero_rows != nullptr) {
+    // clear this block's rows of the fp32 accumulator: the writes ride along with a kernel that mostly reads
+    const int rows_here = min(rows_per_block, a.N - row_begin);
+    if (rows_here > 0) {
+      float4* dst = reinterpret_cast<float4*>(a.zero_rows + (static_cast<int64_t>(bh) * a.N + row_begin) * D);
+      const int n4 = rows_here * (D / 4);
+      for (int i = threadIdx.x; i < n4; i += 256) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   for (int it = 0; it < a.iters; ++it) {
     const int row = row_begin + (it * 8 + warp) * kRowsPerWarp + sub;
     const bool valid = row < a.N;
@@ -95,8 +106,11 @@ __global__ void __launch_bounds__(256) row_stats_kernel(const RowStatsArgs a) {
       if (a.lse_pad_out != nullptr) a.lse_pad_out[out_base + row] = lse;
       const float inv = 1.0f / (a.scale2 * a.slab_w);
       if (a.kslab_out != nullptr) store_slab_row<kBf16>(a.kslab_out, out_base + row, valid ? -ksq * a.scale * inv : -a.slab_big);
-      if (a.lslab_out != nullptr) store_slab_row<kBf16>(a.lslab_out, out_base + row, valid ? -lse * inv : -a.slab_big);
-      if (a.dslab_out != nullptr) store_slab_row<kBf16>(a.dslab_out, out_base + row, -delta / a.slab_w);
+      const float row_stat = a.lslab_from_qsq ? qsq * a.scale : lse;
+      if (a.lslab_out != nullptr)
+        store_slab_row<kBf16>(a.lslab_out, out_base + row, valid ? -row_stat * inv : -a.slab_big);
+      if (a.dslab_out != nullptr)
+        store_slab_row<kBf16>(a.dslab_out, out_base + row, a.dslab_zero ? 0.f : -delta / a.slab_w);
     }
   }
 }

@@ -106,7 +106,9 @@ def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax
     lib = _lib.load()
     cdt = _compute_dtype(q)
     qc, kc, vc, doc = (_tma_ready(t.to(cdt)) for t in (q, k, v, dout))
-    oc = _tma_ready(out.to(cdt)) if softmax else None
+    # the non-softmax variant takes the forward output when the caller has it: the single-kernel backward needs it
+    have_out = out is not None
+    oc = _tma_ready(out.to(cdt)) if have_out else None
     dq = torch.empty((B, H, N, D), dtype=cdt, device=q.device)
     dk = torch.empty_like(dq)
     dv = torch.empty_like(dq)
@@ -115,10 +117,10 @@ def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax
     with torch.cuda.device(q.device):
         rc = lib.rbf_b200_bwd(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
-            oc.data_ptr() if softmax else None, lse.data_ptr() if softmax else None, doc.data_ptr(),
+            oc.data_ptr() if have_out else None, lse.data_ptr() if softmax else None, doc.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel(),
             B, H, N, D, _lib.strides3(qc), _lib.strides3(kc), _lib.strides3(vc),
-            _lib.strides3(oc) if softmax else z3, _lib.strides3(doc),
+            _lib.strides3(oc) if have_out else z3, _lib.strides3(doc),
             _lib.strides3(dq), _lib.strides3(dk), _lib.strides3(dv),
             _DTYPE_CODE[cdt], int(bool(is_causal)), int(softmax), float(sm_scale), _stream_ptr(q.device),
         )
@@ -213,7 +215,10 @@ def rbf_non_softmax_bwd(
     is_causal: bool,
     sm_scale: float,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    return _backward(q, k, v, None, None, dout, is_causal, sm_scale, softmax=False)
+    # The reference's operator does not receive the forward output. The single-kernel backward needs it
+    # (rowsum_j dS_ij = dO_i . O_i), and recomputing it costs less than the two-kernel backward it saves.
+    out = _forward(q, k, v, is_causal, softmax=False)[0]
+    return _backward(q, k, v, out, None, dout, is_causal, sm_scale, softmax=False)
 
 
 @rbf_non_softmax_bwd.register_fake
@@ -225,16 +230,40 @@ def _(q, k, v, dout, is_causal, sm_scale):
     )
 
 
+# Same backward with the forward output passed in (no counterpart in the reference): what autograd calls, since the
+# output is at hand there.
+@torch.library.custom_op("rbf_attn_v5::non_softmax_bwd_with_out", mutates_args=())
+def rbf_non_softmax_bwd_with_out(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    dout: torch.Tensor,
+    is_causal: bool,
+    sm_scale: float,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return _backward(q, k, v, out, None, dout, is_causal, sm_scale, softmax=False)
+
+
+@rbf_non_softmax_bwd_with_out.register_fake
+def _(q, k, v, out, dout, is_causal, sm_scale):
+    return (
+        torch.empty_like(q, memory_format=torch.contiguous_format),
+        torch.empty_like(k, memory_format=torch.contiguous_format),
+        torch.empty_like(v, memory_format=torch.contiguous_format),
+    )
+
+
 def _non_softmax_setup_context(ctx, inputs, output):
     q, k, v, is_causal = inputs
-    ctx.save_for_backward(q, k, v)
+    ctx.save_for_backward(q, k, v, output)
     ctx.is_causal = is_causal
     ctx.sm_scale = 1.0 / math.sqrt(q.shape[-1])
 
 
 def _non_softmax_backward(ctx, dout):
-    q, k, v = ctx.saved_tensors
-    dq, dk, dv = torch.ops.rbf_attn_v5.non_softmax_bwd(q, k, v, dout, ctx.is_causal, ctx.sm_scale)
+    q, k, v, out = ctx.saved_tensors
+    dq, dk, dv = torch.ops.rbf_attn_v5.non_softmax_bwd_with_out(q, k, v, out, dout, ctx.is_causal, ctx.sm_scale)
     return dq, dk, dv, None
 
 

@@ -33,15 +33,15 @@ def test_abi_version_and_workspace_size(built_library):
     assert lib.rbf_b200_abi_version() == _lib.ABI_VERSION
     # forward: status block + key-norm bias slabs (32 bytes per padded row) (+ query norms, non-softmax variant)
     # backward: status block + key norms + row statistic (L re-pitched, or query norms) + delta; the single-kernel
-    # softmax backward adds two slab arrays and an fp32 (B, H, N, D) dQ accumulator
+    # backward adds two slab arrays and an fp32 (B, H, N, D) dQ accumulator
     rows = 2 * 3 * 256 * 4  # N = 200 pads to 256 rows
     slab = 2 * 3 * 256 * 32
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 0) == 256 + slab
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 0) == 256 + slab + rows
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 1, 1) == 256 + 3 * rows + 2 * slab + 2 * 3 * 200 * 64 * 4
     assert lib.rbf_b200_workspace_bytes(2, 3, 200, 128, 1, 1) == 256 + 3 * rows + 2 * slab + 2 * 3 * 200 * 128 * 4
-    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 128, 0, 1) == 256 + 3 * rows
-    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 1) == 256 + 3 * rows
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 128, 0, 1) == 256 + 3 * rows + 2 * slab + 2 * 3 * 200 * 128 * 4
+    assert lib.rbf_b200_workspace_bytes(2, 3, 200, 64, 0, 1) == 256 + 3 * rows + 2 * slab + 2 * 3 * 200 * 64 * 4
     assert lib.rbf_b200_workspace_bytes(0, 3, 200, 64, 1, 0) == 0
 
 

@@ -45,13 +45,16 @@ def cabi_forward(q, k, v, causal, softmax):
     return out, (lse if softmax else None)
 
 
-def cabi_backward(q, k, v, out, lse, do, causal, softmax):
+def cabi_backward(q, k, v, out, lse, do, causal, softmax, with_out=None):
+    """``with_out``: pass the forward output (always for softmax; for the non-softmax variant it selects the
+    single-kernel backward, default) or not (the two-kernel path)."""
+    with_out = softmax or (with_out is None or with_out)
     lib = _lib.load()
     B, H, N, D = q.shape
     dq, dk, dv = (torch.empty((B, H, N, D), dtype=q.dtype, device=q.device) for _ in range(3))
     nbytes = lib.rbf_b200_workspace_bytes(B, H, N, D, int(softmax), 1)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-    rc = lib.rbf_b200_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr() if softmax else None,
+    rc = lib.rbf_b200_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr() if with_out else None,
                           lse.data_ptr() if softmax else None, do.data_ptr(), dq.data_ptr(), dk.data_ptr(),
                           dv.data_ptr(), ws.data_ptr(), nbytes, B, H, N, D, _s3(q), _s3(k), _s3(v), _s3(out),
                           _s3(do), _s3(dq), _s3(dk), _s3(dv), 0 if q.dtype == torch.bfloat16 else 1, int(causal),
@@ -84,6 +87,8 @@ CASES = [
     (1, 2, 1000, 128, False, True),
     (1, 2, 640, 64, True, False),
     (1, 2, 1000, 128, False, False),
+    (2, 2, 1028, 128, True, False),
+    (2, 3, 333, 64, False, False),
     (1, 1, 1, 64, True, True),           # single row
 ]
 
@@ -102,6 +107,12 @@ def test_forward_backward_parity_through_c_abi(B, H, N, D, causal, softmax, dtyp
     check("dQ", dq.cpu().float(), ref_dq, tol)
     check("dK", dk.cpu().float(), ref_dk, tol)
     check("dV", dv.cpu().float(), ref_dv, tol)
+    if not softmax:
+        # without the forward output the non-softmax backward takes the reference's two-kernel split
+        dq, dk, dv = cabi_backward(qd, kd, vd, out, lse, dod, causal, softmax, with_out=False)
+        check("dQ (two kernels)", dq.cpu().float(), ref_dq, tol)
+        check("dK (two kernels)", dk.cpu().float(), ref_dk, tol)
+        check("dV (two kernels)", dv.cpu().float(), ref_dv, tol)
     if softmax:
         ref_l = oracle.torch_lse2(q, k, causal)
         assert (lse.cpu() - ref_l).abs().max().item() <= 2e-4 * max(1.0, ref_l.abs().max().item())
@@ -182,8 +193,8 @@ def test_results_are_bitwise_reproducible():
     # the two-kernel path (the non-softmax variant) is bitwise reproducible throughout
     q, k, v, do = (t.to(DEV) for t in oracle.make_inputs(1, 2, 700, 64, seed=1, dtype=torch.bfloat16, std=0.5))
     o1, l1 = cabi_forward(q, k, v, True, False)
-    g1 = cabi_backward(q, k, v, o1, l1, do, True, False)
-    g2 = cabi_backward(q, k, v, o1, l1, do, True, False)
+    g1 = cabi_backward(q, k, v, o1, l1, do, True, False, with_out=False)
+    g2 = cabi_backward(q, k, v, o1, l1, do, True, False, with_out=False)
     for a, b in zip(g1, g2):
         assert torch.equal(a, b)
 
