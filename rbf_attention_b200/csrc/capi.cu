@@ -154,9 +154,11 @@ int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, 
   const bool bf16 = dtype == 0;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   rbf::FwdArgs a{};
+  // the forward streams keys in tiles of 128 at D = 64 and of 64 at D = 128
+  const int key_rows = D == 128 ? 64 : rbf::kTile;
   if ((rc = make_map(&a.tm_q, "q", q, q_strides, bf16, B, H, N, D))) return rc;
-  if ((rc = make_map(&a.tm_k, "k", k, k_strides, bf16, B, H, N, D))) return rc;
-  if ((rc = make_map(&a.tm_v, "v", v, v_strides, bf16, B, H, N, D))) return rc;
+  if ((rc = make_map(&a.tm_k, "k", k, k_strides, bf16, B, H, N, D, key_rows))) return rc;
+  if ((rc = make_map(&a.tm_v, "v", v, v_strides, bf16, B, H, N, D, key_rows))) return rc;
   if ((rc = make_map(&a.tm_o, "out", out, o_strides, bf16, B, H, N, D))) return rc;
 
   const int n_pad = rbf::padded_rows(N);
@@ -175,7 +177,7 @@ int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, 
   }
   if (!(phases & RBF_B200_PHASE_MAIN)) return RBF_B200_OK;
 
-  const int sr = rbf::make_tmap_slab16(&a.tm_kslab, ws.kslab, bf16, B * H, n_pad, rbf::kTile);
+  const int sr = rbf::make_tmap_slab16(&a.tm_kslab, ws.kslab, bf16, B * H, n_pad, key_rows);
   if (sr != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the key-norm slabs (code %d)", sr);
   a.slab_w = slab_w(bf16);
   a.qsq = ws.row_bias; a.lse = lse; a.status = ws.status;

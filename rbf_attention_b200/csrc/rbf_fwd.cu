@@ -46,7 +46,12 @@ static constexpr int kThreads = 384;
 static constexpr int kLoadWarp = 8;
 static constexpr int kMmaWarp0 = 9;          // issuer of query tile t is warp kMmaWarp0 + t
 static constexpr float kRescaleThreshold = 8.0f;
-static constexpr int kSlabBytes = kTile * 32;   // 128 rows x 16 x 16-bit
+// Keys per streamed tile: 128 at D = 64; 64 at D = 128, where the narrower score tile leaves TMEM columns for P of
+// its own (2 x 64 S + 2 x 32 P + 2 x 128 O), so that the next scores run under the current tile's exponentials.
+template <int D>
+struct KeyTile {
+  static constexpr int kKeys = (D == 64) ? 128 : 64;
+};
 // Register budget (setmaxnreg only redistributes the launch allocation of 168 per thread):
 // 256 softmax threads * 216 + 128 other threads * 72 = 64512 = 384 * 168.
 static constexpr int kSoftmaxRegs = 216;
@@ -55,14 +60,17 @@ static_assert(256 * kSoftmaxRegs + 128 * kOtherRegs <= 384 * 168, "setmaxnreg bu
 
 template <int D>
 struct Smem {
-  static constexpr int kTileBytes = kTile * D * 2;          // one 128-row operand tile
-  static constexpr int kStages = (D == 64) ? 3 : 2;
+  static constexpr int kKeys = KeyTile<D>::kKeys;
+  static constexpr int kTileBytes = kTile * D * 2;          // one 128-row query tile
+  static constexpr int kKvBytes = kKeys * D * 2;            // one key / value tile
+  static constexpr int kSlabBytes = kKeys * 32;             // kKeys rows x 16 x 16-bit
+  static constexpr int kStages = (D == 64) ? 3 : 4;
   static constexpr int kQ = 0;                              // 2 tiles
   static constexpr int kK = kQ + 2 * kTileBytes;            // kStages tiles
-  static constexpr int kV = kK + kStages * kTileBytes;      // kStages tiles
-  static constexpr int kKSlab = kV + kStages * kTileBytes;  // kStages bias slabs
+  static constexpr int kV = kK + kStages * kKvBytes;        // kStages tiles
+  static constexpr int kKSlab = kV + kStages * kKvBytes;    // kStages bias slabs
   static constexpr int kOnes = kKSlab + kStages * kSlabBytes;
-  static constexpr int kBars = kOnes + kSlabBytes;
+  static constexpr int kBars = kOnes + kTile * 32;
   static constexpr int kNumBars = 2 + 4 * kStages + 10;
   static constexpr int kMisc = kBars + kNumBars * 8;        // tmem base, abort flag
   static constexpr int kTotal = kMisc + 16;
@@ -83,13 +91,16 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                float slab_w) {
   using L = Smem<D>;
   constexpr int kStages = L::kStages;
+  constexpr int kKeys = L::kKeys;                // keys per streamed tile
   constexpr int kBoxes = D / 64;                 // 64-column TMA boxes per tile row
-  constexpr int kBoxBytes = kTile * 128;         // one box: 128 rows x 128 bytes
+  constexpr int kBoxBytes = kTile * 128;         // one query / output box: 128 rows x 128 bytes
+  constexpr int kKvBoxBytes = kKeys * 128;       // one key / value box
   constexpr uint32_t kTileBytes = L::kTileBytes;
-  // At D = 64 TMEM has room for P in columns of its own (2 x 128 S + 2 x 64 O + 2 x 64 P = 512): S_t(j+1) is then
-  // issued as soon as the softmax group holds S_t(j) in registers and runs under the exponentials. At D = 128 P
-  // overwrites the first 64 columns of S_t and S_t(j+1) follows O_t += P_t V_j in the issue order.
-  constexpr bool kSeparateP = (D == 64);
+  constexpr uint32_t kKvBytes = L::kKvBytes;
+  constexpr int kSlabBytes = L::kSlabBytes;
+  // P has TMEM columns of its own (D = 64: 2 x 128 S + 2 x 64 O + 2 x 64 P; D = 128: 2 x 64 S + 2 x 32 P + 2 x 128 O):
+  // S_t(j+1) is issued as soon as the softmax group holds S_t(j) in registers and runs under the exponentials.
+  constexpr bool kSeparateP = true;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -124,12 +135,12 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   // heaviest causal blocks first
   const int mb = causal ? (num_blocks - 1 - static_cast<int>(blockIdx.y)) : static_cast<int>(blockIdx.x);
   const int m0 = mb * 2 * kTile;
-  const int n_key_tiles_all = (N + kTile - 1) / kTile;
+  const int n_key_tiles_all = (N + kKeys - 1) / kKeys;
   int nkt[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int r0 = m0 + t * kTile;
-    nkt[t] = (r0 >= N) ? 0 : (causal ? min(n_key_tiles_all, r0 / kTile + 1) : n_key_tiles_all);
+    nkt[t] = (r0 >= N) ? 0 : (causal ? min(n_key_tiles_all, (r0 + kTile) / kKeys) : n_key_tiles_all);
   }
   const int nkt_max = max(nkt[0], nkt[1]);
 
@@ -172,9 +183,9 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_base_s;
-  const uint32_t tmem_s[2] = {tmem, tmem + 128};
+  const uint32_t tmem_s[2] = {tmem, tmem + kKeys};
   const uint32_t tmem_o[2] = {tmem + 256, tmem + 256 + D};
-  const uint32_t tmem_p[2] = {kSeparateP ? tmem + 384 : tmem_s[0], kSeparateP ? tmem + 448 : tmem_s[1]};
+  const uint32_t tmem_p[2] = {D == 64 ? tmem + 384 : tmem + 128, D == 64 ? tmem + 448 : tmem + 160};
 
   if (warp == kLoadWarp) {
     // ------------------------------------------------------------------ TMA producer
@@ -194,14 +205,14 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int st = j % kStages;
         const uint32_t par = ((j / kStages) - 1) & 1;
         if (j >= kStages && !mbar_wait(&k_empty[st], par, abort_flag, status, kSiteKEmpty)) break;
-        mbar_arrive_expect_tx(&k_full[st], kTileBytes + kSlabBytes);
+        mbar_arrive_expect_tx(&k_full[st], kKvBytes + kSlabBytes);
         for (int x = 0; x < kBoxes; ++x)
-          tma_load_4d(s_k + st * kTileBytes + x * kBoxBytes, &tm_k, &k_full[st], x * 64, j * kTile, h, b);
-        tma_load_3d(s_kslab + st * kSlabBytes, &tm_kslab, &k_full[st], 0, j * kTile, bh);
+          tma_load_4d(s_k + st * kKvBytes + x * kKvBoxBytes, &tm_k, &k_full[st], x * 64, j * kKeys, h, b);
+        tma_load_3d(s_kslab + st * kSlabBytes, &tm_kslab, &k_full[st], 0, j * kKeys, bh);
         if (j >= kStages && !mbar_wait(&v_empty[st], par, abort_flag, status, kSiteVEmpty)) break;
-        mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+        mbar_arrive_expect_tx(&v_full[st], kKvBytes);
         for (int x = 0; x < kBoxes; ++x)
-          tma_load_4d(s_v + st * kTileBytes + x * kBoxBytes, &tm_v, &v_full[st], x * 64, j * kTile, h, b);
+          tma_load_4d(s_v + st * kKvBytes + x * kKvBoxBytes, &tm_v, &v_full[st], x * 64, j * kKeys, h, b);
       }
     }
   } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
@@ -210,31 +221,31 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (lane == 0) {
       const int t = warp - kMmaWarp0;
       const int my_nkt = nkt[t];
-      constexpr uint32_t idesc_s = make_idesc(kTile, kTile, kBf16, false, false);   // S = Q K^T
+      constexpr uint32_t idesc_s = make_idesc(kTile, kKeys, kBf16, false, false);   // S = Q K^T
       constexpr uint32_t idesc_o = make_idesc(kTile, D, kBf16, false, true);        // O += P V (V is N-major)
       const SmemDesc q_desc = make_sdesc_parts(smem_u32(s_q) + t * kTileBytes, 16, 1024);
       const SmemDesc k_desc0 = make_sdesc_parts(smem_u32(s_k), 16, 1024);
-      const SmemDesc v_desc0 = make_sdesc_parts(smem_u32(s_v), kBoxBytes, 1024);
+      const SmemDesc v_desc0 = make_sdesc_parts(smem_u32(s_v), kKvBoxBytes, 1024);
       const SmemDesc ones_desc = make_sdesc_slab32(smem_u32(s_ones));
       const SmemDesc kslab_desc0 = make_sdesc_slab32(smem_u32(s_kslab));
       auto issue_s = [&](int st) {
         SmemDesc k_desc = k_desc0;
-        k_desc.lo += static_cast<uint32_t>(st) * (kTileBytes >> 4);
+        k_desc.lo += static_cast<uint32_t>(st) * (kKvBytes >> 4);
         SmemDesc slab = kslab_desc0;
         slab.lo += static_cast<uint32_t>(st) * (kSlabBytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          umma_ss(tmem_s[t], sdesc_at(q_desc, off), sdesc_at(k_desc, off), idesc_s, kk > 0);
+          umma_ss(tmem_s[t], sdesc_at(q_desc, (kk >> 2) * kBoxBytes + (kk & 3) * 32),
+                  sdesc_at(k_desc, (kk >> 2) * kKvBoxBytes + (kk & 3) * 32), idesc_s, kk > 0);
         }
         umma_ss(tmem_s[t], sdesc_at(ones_desc, 0), sdesc_at(slab, 0), idesc_s, 1u);   // + key-norm bias
         umma_commit(&s_full[t]);
       };
       auto issue_o = [&](int st, uint32_t accumulate) {
         SmemDesc v_desc = v_desc0;
-        v_desc.lo += static_cast<uint32_t>(st) * (kTileBytes >> 4);
+        v_desc.lo += static_cast<uint32_t>(st) * (kKvBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
+        for (int kk = 0; kk < kKeys / 16; ++kk)
           umma_ts(tmem_o[t], tmem_p[t] + kk * 8, sdesc_at(v_desc, kk * 2048), idesc_o, kk > 0 ? 1u : accumulate);
         umma_commit(&o_done[t]);
       };
@@ -326,14 +337,14 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     float row_bias = 0.f;
     if (!kSoftmax && my_nkt > 0) row_bias = qsq[static_cast<int64_t>(bh) * n_pad + row];
     bool ok = true;
-    if (kSeparateP && t == 1) {
+    if (D == 64 && t == 1) {
       // The two softmax groups share the MUFU pipe. Started a few hundred cycles apart, one group's exponentials
-      // overlap the other group's loads, maxima and stores more often than they collide (measured: 3 % at D = 64).
+      // overlap the other group's loads, maxima and stores more often than they collide (measured: 3 % at D = 64;
+      // making the groups take strict turns was slower).
       const long long t_start = clock64();
       while (clock64() - t_start < 800) {
       }
     }
-
     for (int j = 0; j < my_nkt; ++j) {
       if (r == 0) RBF_FTRACE(2 + t, j, 0);
       ok = mbar_wait(&s_full[t], j & 1, abort_flag, status, kSiteSFull);
@@ -343,17 +354,12 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       RBF_WTRACE(0);
       tc_fence_after_sync();
 
-      // acc = q.k - |k|^2 / 2 for 128 keys; the logit in base-2 units is acc * scale2
-      uint32_t raw[kTile];
+      // acc = q.k - |k|^2 / 2 for the tile's keys; the logit in base-2 units is acc * scale2
+      uint32_t raw[kKeys];
       {
-        uint32_t(&c0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[0]);
-        uint32_t(&c1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[32]);
-        uint32_t(&c2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[64]);
-        uint32_t(&c3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&raw[96]);
-        tmem_ld_x32(tmem_s[t] + lane_sel + 0, c0);
-        tmem_ld_x32(tmem_s[t] + lane_sel + 32, c1);
-        tmem_ld_x32(tmem_s[t] + lane_sel + 64, c2);
-        tmem_ld_x32(tmem_s[t] + lane_sel + 96, c3);
+#pragma unroll
+        for (int c = 0; c < kKeys / 32; ++c)
+          tmem_ld_x32(tmem_s[t] + lane_sel + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&raw[c * 32]));
         tmem_ld_wait();
         if (kSeparateP) {
           tc_fence_before_sync();
@@ -362,11 +368,13 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (r == 0) RBF_FTRACE(2 + t, j, 2);
         RBF_WTRACE(1);
       }
-      if (causal && j * kTile == r0) {
-        // diagonal tile: key (r0 + c) is visible to query (r0 + r) iff c <= r
+      if (causal && (j + 1) * kKeys > r0 + 1) {
+        // tiles that reach past the block's first row: key (j * kKeys + c) is visible to query (r0 + r) iff it is
+        // not larger
+        const int c_max = r0 + r - j * kKeys;   // last visible column of this row
 #pragma unroll
-        for (int c = 0; c < kTile; ++c)
-          if (c > r) raw[c] = 0xff800000u;   // -inf
+        for (int c = 0; c < kKeys; ++c)
+          if (c > c_max) raw[c] = 0xff800000u;   // -inf
       }
 
       float sub;   // p = exp2(acc * scale2 - sub)
@@ -375,7 +383,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]), mx2 = __uint_as_float(raw[2]),
               mx3 = __uint_as_float(raw[3]);
 #pragma unroll
-        for (int c = 4; c < kTile; c += 4) {
+        for (int c = 4; c < kKeys; c += 4) {
           mx0 = fmaxf(mx0, __uint_as_float(raw[c + 0]));
           mx1 = fmaxf(mx1, __uint_as_float(raw[c + 1]));
           mx2 = fmaxf(mx2, __uint_as_float(raw[c + 2]));
@@ -415,7 +423,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const float neg_sub = -sub;
       float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kKeys / 64; ++c) {
         uint32_t packed[32];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
