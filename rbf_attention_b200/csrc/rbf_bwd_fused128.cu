@@ -8,8 +8,9 @@
 //   dP^T [128 keys x 64 q] = V dO^T (+ bias slab: -delta[query])          smem x smem
 //   P^T = exp2(S^T * 2c - ksq[key]),  dS^T = P^T * dP^T                   (registers; thread = key row)
 //   dV  [128 x 128] += P^T dO          TMEM x smem (P^T: 32 TMEM columns of 16-bit pairs)
-//   dK  [128 x 128] += dS^T Q          smem x smem (dS^T: a [key][query] tile of 128-byte rows)
-//   dQ^T[128 d x 64 q] = K^T dS^T      smem x smem (K read M-major, the dS^T tile read N-major)
+//   dK  [128 x 128] += dS^T Q          TMEM x smem (dS^T: 32 TMEM columns of 16-bit pairs)
+//   dQ^T[128 d x 64 q] = K^T dS^T      smem x smem (K read M-major; dS^T a second time, as a [key][query]
+//                                      shared-memory tile of 128-byte rows read N-major)
 // dQ^T leaves the CTA straight from registers: a drain thread owns one head-dim index, so for every query of the
 // step the 32 lanes of a warp hold 32 consecutive floats of the (B, H, N, D) fp32 accumulator and one scalar
 // red.global.add per query is a coalesced 128-byte line. No shared-memory staging: shared-memory bandwidth is
@@ -17,7 +18,7 @@
 // kernel scales and converts the accumulator afterwards. (Every SM can push about 25 bytes per clock of
 // reduce-adds into L2, measured; a step's 32 KB of dQ therefore takes as long as its MMAs and must overlap them.)
 //
-// TMEM columns: S^T [0,64), dP^T [64,128), P^T [128,160), dQ^T [160,224), dV [256,384), dK [384,512).
+// TMEM columns: S^T [0,64), dP^T [64,128), P^T [128,160), dQ^T [160,224), dS^T [224,256), dV [256,384), dK [384,512).
 // Roles: warps 0, 1, 3 MMA issuers (A: S^T(n+1), dV(n); B: dP^T(n+1), dK(n); C: dQ^T(n)), warp 2 TMA producer,
 // warps 4-19 compute (thread = key row, group g owns query columns [16g, 16g+16) of the step), warps 20-23 drain
 // dQ^T (thread = head-dim index).
@@ -87,7 +88,7 @@ struct Smem {
 };
 static_assert(Smem::kDynamic <= 232448, "shared memory budget");
 
-static constexpr int kColS = 0, kColDP = 64, kColPT = 128, kColDQ = 160, kColDV = 256, kColDK = 384;
+static constexpr int kColS = 0, kColDP = 64, kColPT = 128, kColDQ = 160, kColDST = 224, kColDV = 256, kColDK = 384;
 
 enum Site : uint32_t {
   kSiteKV = 96, kSiteQFull, kSiteDoFull, kSiteQEmpty, kSiteDoEmpty, kSiteSFull, kSiteDPFull, kSitePFull, kSiteDSFull,
@@ -134,11 +135,12 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   uint64_t* p_full = dp_consumed + 1;
   uint64_t* dv_done = p_full + 1;
   uint64_t* ds_full = dv_done + 1;           // [kDsStages] the dS^T tile of a step is written
-  uint64_t* ds_free = ds_full + kDsStages;   // [kDsStages] two arrivals: dK (issuer B) and dQ^T (issuer C) have read it
+  uint64_t* ds_free = ds_full + kDsStages;   // [kDsStages] dQ^T (issuer C) has read the shared-memory tile
   uint64_t* dq_full = ds_free + kDsStages;   // dQ^T of the step is complete in TMEM
   uint64_t* dq_drained = dq_full + 1;
   uint64_t* acc_done = dq_drained + 1;       // three arrivals
   uint64_t* grp_sync = acc_done + 1;
+  uint64_t* dk_done = grp_sync + 1;          // dK (issuer B) has read the TMEM copy of dS^T
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + Smem::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 4);
 
@@ -168,7 +170,8 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     mbar_init(dp_consumed, kNumComputeWarps);
     mbar_init(p_full, kNumComputeWarps);
     mbar_init(dv_done, 1);
-    for (int s = 0; s < kDsStages; ++s) { mbar_init(&ds_full[s], kNumComputeWarps); mbar_init(&ds_free[s], 2); }
+    for (int s = 0; s < kDsStages; ++s) { mbar_init(&ds_full[s], kNumComputeWarps); mbar_init(&ds_free[s], 1); }
+    mbar_init(dk_done, 1);
     mbar_init(dq_full, 1);
     mbar_init(dq_drained, 4);
     mbar_init(acc_done, 3);
@@ -294,7 +297,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         const SmemDesc do_kmaj0 = make_sdesc_parts(smem_u32(s_do), 16, 1024);
         const SmemDesc dslab0 = make_sdesc_slab32(smem_u32(s_dslab));
         const SmemDesc q_nmaj0 = make_sdesc_parts(smem_u32(s_q), kQBoxBytes, 1024);
-        const SmemDesc ds_kmaj = make_sdesc_parts(smem_u32(s_ds), 16, 1024);            // rows = keys, K = 64 queries
         if (ok) ok = wait_do(0);
         if (ok) {
           tc_fence_after_sync();
@@ -320,14 +322,14 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
           if (!ok) break;
           RBF_TRACE_EVENT(1, n, 3);
           tc_fence_after_sync();
+          // A = the TMEM copy of dS^T (16-bit pairs, 32 columns): only Q is fetched from shared memory
           const SmemDesc q_n = stage_of(q_nmaj0, n % kQStages, kQTileBytes);
-          const SmemDesc ds_n = stage_of(ds_kmaj, n % kDsStages, kDsBytes);
 #pragma unroll
           for (int kk = 0; kk < kQStep / 16; ++kk)
-            umma_ss(tmem + kColDK, sdesc_at(ds_n, kk * 32), sdesc_at(q_n, kk * 2048), idesc_acc,
+            umma_ts(tmem + kColDK, tmem + kColDST + kk * 8, sdesc_at(q_n, kk * 2048), idesc_acc,
                     (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&q_empty[n % kQStages]);
-          umma_commit(&ds_free[n % kDsStages]);    // first of two arrivals: the dS^T tile's K-major reader is done
+          umma_commit(dk_done);
           RBF_TRACE_EVENT(1, n, 4);
         }
       } else {
@@ -348,7 +350,7 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
             umma_ss(tmem + kColDQ, sdesc_at(k_mmaj, kk * 2048),
                     sdesc_at(ds_nmaj, (n % kDsStages) * kDsBytes + kk * 2048), idesc_dq, kk > 0);
           umma_commit(dq_full);                    // dQ^T readable
-          umma_commit(&ds_free[n % kDsStages]);    // second arrival: the N-major reader is done
+          umma_commit(&ds_free[n % kDsStages]);    // the shared-memory tile's reader is done
           RBF_TRACE_EVENT(4, n, 3);
         }
       }
@@ -480,6 +482,15 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         *reinterpret_cast<uint4*>(s_ds + (n % kDsStages) * kDsBytes + sw128_offset(r, g * 2 + ch)) =
             make_uint4(ds_packed[ch * 4 + 0], ds_packed[ch * 4 + 1], ds_packed[ch * 4 + 2], ds_packed[ch * 4 + 3]);
       fence_proxy_async_smem();
+      // second copy for dK = dS^T Q, which takes its A operand from TMEM; free once dK of the previous step is done
+      if (n > 0) {
+        ok = mbar_wait(dk_done, (n - 1) & 1, abort_flag, p.status, kSiteDsFree);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      tmem_st_x8(tmem + kColDST + lane_sel + g * 8, ds_packed);
+      tmem_st_wait();
+      tc_fence_before_sync();
       mbar_arrive_warp(&ds_full[n % kDsStages]);
       if (tr) RBF_TRACE_EVENT(2, n, 10);
     }
