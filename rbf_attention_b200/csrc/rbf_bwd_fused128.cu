@@ -419,7 +419,12 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         if (tr) RBF_TRACE_EVENT(2, n, 2);
         // acc = k.q - L / scale2 ; P = exp2(acc * scale2 - ksq)
 #pragma unroll
-        for (int i = 0; i < 16; ++i) pr[i] = ex2_approx(fmaf(__uint_as_float(raw[i]), p.scale2, neg_ksq));
+        for (int i = 0; i < 16; i += 2) {
+          float a0, a1;
+          ffma2_bcast(a0, a1, __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]), p.scale2, neg_ksq);
+          pr[i] = ex2_approx(a0);
+          pr[i + 1] = ex2_approx(a1);
+        }
       }
       const int q0 = (first + n) * kQStep;
       if (p.causal && q0 < k_row0 + kTile) {
@@ -462,10 +467,9 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float d0 = pr[2 * i] * __uint_as_float(raw[2 * i]);
-          const float d1 = pr[2 * i + 1] * __uint_as_float(raw[2 * i + 1]);
-          rs0 += d0;
-          rs1 += d1;
+          float d0, d1;
+          fmul2(d0, d1, pr[2 * i], pr[2 * i + 1], __uint_as_float(raw[2 * i]), __uint_as_float(raw[2 * i + 1]));
+          fadd2(rs0, rs1, rs0, rs1, d0, d1);
           ds_packed[i] = pack2<kBf16>(d0, d1);
         }
         ds_rowsum += rs0 + rs1;

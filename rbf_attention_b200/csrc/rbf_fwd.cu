@@ -379,16 +379,18 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
       float sub;   // p = exp2(acc * scale2 - sub)
       if constexpr (kSoftmax) {
-        // four independent maxima keep the dependency chains short
+        // four independent three-input maxima: short dependency chains, half the instructions
         float mx0 = __uint_as_float(raw[0]), mx1 = __uint_as_float(raw[1]), mx2 = __uint_as_float(raw[2]),
               mx3 = __uint_as_float(raw[3]);
 #pragma unroll
-        for (int c = 4; c < kKeys; c += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(raw[c + 0]));
-          mx1 = fmaxf(mx1, __uint_as_float(raw[c + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(raw[c + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(raw[c + 3]));
+        for (int c = 4; c + 8 <= kKeys; c += 8) {
+          mx0 = fmax3(mx0, __uint_as_float(raw[c + 0]), __uint_as_float(raw[c + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(raw[c + 2]), __uint_as_float(raw[c + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(raw[c + 4]), __uint_as_float(raw[c + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(raw[c + 6]), __uint_as_float(raw[c + 7]));
         }
+        mx0 = fmax3(mx0, __uint_as_float(raw[kKeys - 4]), __uint_as_float(raw[kKeys - 3]));
+        mx1 = fmax3(mx1, __uint_as_float(raw[kKeys - 2]), __uint_as_float(raw[kKeys - 1]));
         const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale2);
         const bool need = (m_new - m_used) > kRescaleThreshold;
         float alpha = 1.f;
@@ -427,11 +429,14 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         uint32_t packed[32];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(raw[c * 64 + 2 * i + 0]), scale2, neg_sub));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(raw[c * 64 + 2 * i + 1]), scale2, neg_sub));
-          const float p2 = ex2_approx(fmaf(__uint_as_float(raw[c * 64 + 2 * i + 2]), scale2, neg_sub));
-          const float p3 = ex2_approx(fmaf(__uint_as_float(raw[c * 64 + 2 * i + 3]), scale2, neg_sub));
-          ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
+          float a0, a1, a2, a3;
+          ffma2_bcast(a0, a1, __uint_as_float(raw[c * 64 + 2 * i + 0]), __uint_as_float(raw[c * 64 + 2 * i + 1]), scale2,
+                      neg_sub);
+          ffma2_bcast(a2, a3, __uint_as_float(raw[c * 64 + 2 * i + 2]), __uint_as_float(raw[c * 64 + 2 * i + 3]), scale2,
+                      neg_sub);
+          const float p0 = ex2_approx(a0), p1 = ex2_approx(a1), p2 = ex2_approx(a2), p3 = ex2_approx(a3);
+          fadd2(ps0, ps1, ps0, ps1, p0, p1);
+          fadd2(ps2, ps3, ps2, ps3, p2, p3);
           packed[i] = pack2<kBf16>(p0, p1);
           packed[i + 1] = pack2<kBf16>(p2, p3);
         }
