@@ -261,7 +261,7 @@ def run_ours(args, w, rank, world, local_rank):
     with ClockSampler(local_rank) as clocks:
         ms = time_loop(torch, runner.step, args.steps)
         # per-kernel times for the roofline line (same buffers, same stream)
-        fused = True                             # single-kernel backward (plus memset and dQ convert)
+        fused = True                             # single-kernel backward (plus the dQ conversion kernel)
         phase_ms = {"fwd": time_loop(torch, lambda: runner.fwd(2), args.steps)}
         if fused:
             phase_ms["bwd_fused"] = time_loop(torch, lambda: runner.bwd(2), args.steps)
