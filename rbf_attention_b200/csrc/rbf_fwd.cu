@@ -144,12 +144,25 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
   const int nkt_max = max(nkt[0], nkt[1]);
 
-  // A wait that ran out in an earlier CTA of this launch ends the whole launch quickly: later CTAs leave at once.
-  if (tid == 0) *abort_flag = (*reinterpret_cast<volatile unsigned int*>(&status->code) != 0u) ? 1 : 0;
-  __syncthreads();
-  if (*abort_flag) return;
-
-  if (tid == 0) {
+  // One thread (the TMA producer) sets the CTA up: it reads the launch's status word (a wait that ran out in an
+  // earlier CTA ends the whole launch quickly: later CTAs leave at once), initialises the barriers while that load
+  // is in flight, and issues the first loads before the CTA-wide synchronisation, so that Q and the first key tiles
+  // travel while TMEM is allocated and the constant slab is written.
+  auto load_keys = [&](int j) {
+    const int st = j % kStages;
+    mbar_arrive_expect_tx(&k_full[st], kKvBytes + kSlabBytes);
+    for (int x = 0; x < kBoxes; ++x)
+      tma_load_4d(s_k + st * kKvBytes + x * kKvBoxBytes, &tm_k, &k_full[st], x * 64, j * kKeys, h, b);
+    tma_load_3d(s_kslab + st * kSlabBytes, &tm_kslab, &k_full[st], 0, j * kKeys, bh);
+  };
+  auto load_values = [&](int j) {
+    const int st = j % kStages;
+    mbar_arrive_expect_tx(&v_full[st], kKvBytes);
+    for (int x = 0; x < kBoxes; ++x)
+      tma_load_4d(s_v + st * kKvBytes + x * kKvBoxBytes, &tm_v, &v_full[st], x * 64, j * kKeys, h, b);
+  };
+  if (tid == kLoadWarp * 32) {
+    const unsigned int earlier = *reinterpret_cast<volatile unsigned int*>(&status->code);
     mbar_init(&q_full[0], 1);
     mbar_init(&q_full[1], 1);
     for (int s = 0; s < kStages; ++s) {
@@ -166,6 +179,23 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(&s_consumed[t], 4);
     }
     fence_mbar_init();
+    *abort_flag = earlier != 0u ? 1 : 0;
+    if (earlier == 0u) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_kslab);
+      for (int t = 0; t < 2; ++t) {
+        if (nkt[t] == 0) continue;
+        mbar_arrive_expect_tx(&q_full[t], kTileBytes);
+        for (int x = 0; x < kBoxes; ++x)
+          tma_load_4d(s_q + t * kTileBytes + x * kBoxBytes, &tm_q, &q_full[t], x * 64, m0 + t * kTile, h, b);
+      }
+      for (int j = 0; j < nkt_max && j < kStages; ++j) {
+        load_keys(j);
+        load_values(j);
+      }
+    }
   }
   if (warp == kMmaWarp0) {
     tmem_alloc(tmem_base_s, 512);
@@ -183,6 +213,10 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_base_s;
+  if (*abort_flag) {
+    if (warp == kMmaWarp0) tmem_dealloc(tmem, 512);
+    return;
+  }
   const uint32_t tmem_s[2] = {tmem, tmem + kKeys};
   const uint32_t tmem_o[2] = {tmem + 256, tmem + 256 + D};
   const uint32_t tmem_p[2] = {D == 64 ? tmem + 384 : tmem + 128, D == 64 ? tmem + 448 : tmem + 160};
@@ -191,28 +225,13 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // ------------------------------------------------------------------ TMA producer
     setmaxnreg_dec<kOtherRegs>();
     if (lane == 0) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      tma_prefetch_desc(&tm_kslab);
-      for (int t = 0; t < 2; ++t) {
-        if (nkt[t] == 0) continue;
-        mbar_arrive_expect_tx(&q_full[t], kTileBytes);
-        for (int x = 0; x < kBoxes; ++x)
-          tma_load_4d(s_q + t * kTileBytes + x * kBoxBytes, &tm_q, &q_full[t], x * 64, m0 + t * kTile, h, b);
-      }
-      for (int j = 0; j < nkt_max; ++j) {
+      for (int j = kStages; j < nkt_max; ++j) {
         const int st = j % kStages;
         const uint32_t par = ((j / kStages) - 1) & 1;
-        if (j >= kStages && !mbar_wait(&k_empty[st], par, abort_flag, status, kSiteKEmpty)) break;
-        mbar_arrive_expect_tx(&k_full[st], kKvBytes + kSlabBytes);
-        for (int x = 0; x < kBoxes; ++x)
-          tma_load_4d(s_k + st * kKvBytes + x * kKvBoxBytes, &tm_k, &k_full[st], x * 64, j * kKeys, h, b);
-        tma_load_3d(s_kslab + st * kSlabBytes, &tm_kslab, &k_full[st], 0, j * kKeys, bh);
-        if (j >= kStages && !mbar_wait(&v_empty[st], par, abort_flag, status, kSiteVEmpty)) break;
-        mbar_arrive_expect_tx(&v_full[st], kKvBytes);
-        for (int x = 0; x < kBoxes; ++x)
-          tma_load_4d(s_v + st * kKvBytes + x * kKvBoxBytes, &tm_v, &v_full[st], x * 64, j * kKeys, h, b);
+        if (!mbar_wait(&k_empty[st], par, abort_flag, status, kSiteKEmpty)) break;
+        load_keys(j);
+        if (!mbar_wait(&v_empty[st], par, abort_flag, status, kSiteVEmpty)) break;
+        load_values(j);
       }
     }
   } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
@@ -490,7 +509,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (ok && r == 0) {
           for (int x = 0; x < kBoxes; ++x) tma_store_4d(&tm_o, stage + x * kBoxBytes, x * 64, r0, h, b);
           tma_store_commit();
-          tma_store_wait_all();
+          tma_store_wait_read();   // the CTA may exit once the staging tile has been read
         }
         if (kSoftmax && row < N) lse[static_cast<int64_t>(bh) * N + row] = m_used + log2f(l_sum);
       }

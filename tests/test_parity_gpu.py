@@ -308,3 +308,20 @@ def test_non_softmax_block_and_compiled_call():
 
     q, k, v, _ = (t.to(DEV) for t in oracle.make_inputs(1, 2, 256, 64, seed=2, dtype=torch.bfloat16))
     assert torch.equal(f(q, k, v), attention.run_triton_rbf(q, k, v, True))
+
+
+def test_non_softmax_backward_operators_agree():
+    """The reference-named backward operator (no forward output among its arguments: it recomputes it) and the one
+    autograd calls (forward output passed in) give the same gradients, and both match the oracle."""
+    q, k, v, do = (t.to(DEV) for t in oracle.make_inputs(2, 2, 600, 64, seed=5, dtype=torch.bfloat16, std=0.5))
+    scale = 1.0 / math.sqrt(64)
+    out = torch.ops.rbf_attn_v5.non_softmax_fwd(q, k, v, True)
+    g_ref_named = torch.ops.rbf_attn_v5.non_softmax_bwd(q, k, v, do, True, scale)
+    g_with_out = torch.ops.rbf_attn_v5.non_softmax_bwd_with_out(q, k, v, out, do, True, scale)
+    for a, b in zip(g_ref_named, g_with_out):
+        assert oracle.error_report(a.float().cpu(), b.float().cpu())["rel_l2"] <= 1e-3
+    qa, ka, va = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    attention.run_triton_non_softmax_rbf(qa, ka, va, True).backward(do)
+    ref = oracle.torch_forward_backward(q.cpu(), k.cpu(), v.cpu(), do.cpu(), True, False, dtype=torch.float32)
+    for name, got, want in zip(("dQ", "dK", "dV"), (qa.grad, ka.grad, va.grad), ref[1:]):
+        check(name, got.cpu().float(), want, REL_L2[torch.bfloat16])
