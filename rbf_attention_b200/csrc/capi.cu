@@ -116,6 +116,19 @@ int make_map(CUtensorMap* m, const char* name, const void* p, const int64_t* s, 
   return 0;
 }
 
+// SM count of the current device (cached per device)
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 void set_strides(int64_t (&dst)[3], const int64_t* src) {
   dst[0] = src[0]; dst[1] = src[1]; dst[2] = src[2];
 }
@@ -279,6 +292,10 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     }
     f.dq_acc = ws.dq_acc; f.dq = dq; set_strides(f.dq_strides, dq_strides);
     f.ksq = ws.ksq; f.status = ws.status;
+    // work counters of the persistent launch live in the status block (words 16, 17), zeroed by the pre-pass
+    f.work = reinterpret_cast<unsigned int*>(ws.status) + 16;
+    f.sm_count = sm_count();
+    if (f.sm_count <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
     if (!softmax) { f.q_rows = q; set_strides(f.q_strides, q_strides); f.delta = ws.delta; }
     f.B = B; f.H = H; f.N = N; f.n_pad = n_pad; f.causal = causal ? 1 : 0;
     f.scale2 = 2.f * c; f.grad_scale = 2.f * sm_scale; f.slab_w = slab_w(bf16);

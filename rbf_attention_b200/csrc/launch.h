@@ -34,7 +34,7 @@ struct RowStatsArgs {
   float scale;
   float qsq_pad;
   int iters;              // set by the launcher
-  DeviceStatus* status_to_clear;  // optional: zeroed by the first thread of the grid
+  DeviceStatus* status_to_clear;  // optional: the 256-byte status block (status word, work counters) is zeroed
 };
 cudaError_t launch_row_stats(const RowStatsArgs& a, bool bf16, int D, cudaStream_t stream);
 
@@ -84,6 +84,8 @@ struct BwdFusedArgs {
   int64_t q_strides[3];
   const float* delta;     // (B*H, n_pad)
   DeviceStatus* status;
+  unsigned int* work;     // two work counters of the persistent launch (zero at launch; D = 64 kernel)
+  int sm_count;
   int B, H, N, n_pad;
   int causal;
   float scale2, grad_scale, slab_w;

@@ -51,8 +51,8 @@ template <bool kBf16, int D>
 __global__ void __launch_bounds__(256) row_stats_kernel(const RowStatsArgs a) {
   constexpr int kLanesPerRow = D / 8;                 // 8 (D=64) or 16 (D=128)
   constexpr int kRowsPerWarp = 32 / kLanesPerRow;     // 4 or 2
-  if (a.status_to_clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
-    a.status_to_clear->code = 0;
+  if (a.status_to_clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 64)
+    reinterpret_cast<unsigned int*>(a.status_to_clear)[threadIdx.x] = 0u;   // status word and work counters
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int sub = lane / kLanesPerRow;                // row within the warp's group
