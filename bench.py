@@ -354,8 +354,8 @@ def run_ours(args, w, rank, world, local_rank):
         gemms = {"fwd": 2, "bwd_fused": 5} if fused else {"fwd": 2, "bwd_dkdv": 4, "bwd_dq": 1}
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture of a quarter of the batch
         # (profiles/ncu_full_fwd_bwd_fused_config2_quarter.md), times four: traffic grows in proportion to B
-        ncu_traffic = {("config2", "bwd_fused"): 4 * (109.632768e6 + 33.296640e6),
-                       ("config2", "fwd"): 4 * (54.691328e6 + 4.901888e6)}
+        ncu_traffic = {("config2", "bwd_fused"): 4 * (109.726720e6 + 30.068992e6),
+                       ("config2", "fwd"): 4 * (54.800640e6 + 2.691584e6)}
         dom = max(gemms, key=lambda n: phase_ms[n])
         unit_flops = 2.0 * w["B"] * w["H"] * float(w["N"]) ** 2 * w["D"] * (0.5 if w["causal"] else 1.0)
         achieved = gemms[dom] * unit_flops / (phase_ms[dom] * 1e-3) / 1e12
