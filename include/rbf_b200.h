@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define RBF_B200_ABI_VERSION 1
+#define RBF_B200_ABI_VERSION 2
 
 enum {
   RBF_B200_OK = 0,
@@ -126,9 +126,28 @@ int rbf_b200_fwd_static(const void* q, const void* k, const void* v, void* out, 
                         const int64_t* o_strides, int dtype, int causal, int softmax, float sm_scale, void* stream);
 
 /* Synchronises `stream` and reads the device status word that the last call using `workspace` left:
- * 0 = ok, otherwise (site << 24 | block) of the bounded wait that ran out. Returns RBF_B200_ERR_DEVICE
- * when the word is non-zero. No counterpart in the reference (its kernels have no device-side waits). */
+ * 0 = ok, otherwise (site << 24 | work unit) of the bounded wait that ran out; the work unit is the linear block
+ * index of the launch or, for the persistent backward kernel, the (key tile, batch-head) item. Returns
+ * RBF_B200_ERR_DEVICE when the word is non-zero. `workspace` = NULL reads the built-in scratch of the current
+ * device, i.e. the status the last rbf_b200_fwd_static call left. No counterpart in the reference (its kernels have
+ * no device-side waits). */
 int rbf_b200_read_device_status(const void* workspace, void* stream, unsigned int* code);
+
+/* Process-wide switch for run-to-run bitwise reproducible gradients. Off (default): the backward runs as one kernel
+ * per call whose dQ partials are added in fp32 in arrival order (dQ then differs by rounding between runs; O, L, dK,
+ * dV never do). On: the backward runs as the reference's two kernels (key-stationary dK/dV, rbf_attention.py:279-477,
+ * and query-stationary dQ, :480-642), which sum in a fixed order like the reference's, at about 7/5 of the tensor
+ * work. Returns the previous setting. */
+int rbf_b200_set_deterministic(int on);
+int rbf_b200_get_deterministic(void);
+
+/* Self-test of the bounded device waits every kernel of the library relies on: launches one block that waits, with
+ * the kernels' own wait routine, on a barrier that nothing arms. After `limit_cycles` SM clocks (at most 2e9) the
+ * wait gives up, records site 250 in the status word at the start of `workspace` (at least 256 bytes, 256-byte
+ * aligned) and the kernel returns by itself; rbf_b200_read_device_status then reports RBF_B200_ERR_DEVICE. A later
+ * forward or backward call on the same workspace clears the word. Nothing traps, faults or spins without bound.
+ * No counterpart in the reference. */
+int rbf_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, long long limit_cycles, void* stream);
 
 #ifdef __cplusplus
 }

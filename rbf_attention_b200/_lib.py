@@ -12,7 +12,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "librbf_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 STATUS_NAMES = {
     0: "ok",
@@ -59,6 +59,12 @@ SIGNATURES = {
     "rbf_b200_read_device_status": (
         ctypes.c_int,
         [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint)],
+    ),
+    "rbf_b200_set_deterministic": (ctypes.c_int, [ctypes.c_int]),
+    "rbf_b200_get_deterministic": (ctypes.c_int, []),
+    "rbf_b200_selftest_wait_timeout": (
+        ctypes.c_int,
+        [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_longlong, ctypes.c_void_p],
     ),
 }
 

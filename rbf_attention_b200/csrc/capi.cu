@@ -2,6 +2,9 @@
 // maps, and the launch sequence of each call. No device memory is allocated here.
 #include <math.h>
 #include <stdarg.h>
+
+#include <atomic>
+
 #include <stdio.h>
 #include <string.h>
 
@@ -41,7 +44,13 @@ struct Workspace {
 // The backward runs as one kernel that accumulates dQ in fp32 global memory (a kernel per head dim). The non-softmax
 // variant needs the forward output for it (rowsum_j dS_ij = dO_i . O_i); without `out` it takes the two-kernel path.
 // The workspace is sized for the single kernel in every case.
-bool use_fused_backward(int D, int softmax, bool have_out) { return (softmax || have_out) && (D == 64 || D == 128); }
+// With the deterministic flag set (rbf_b200_set_deterministic) every backward takes the two-kernel path, whose
+// summation order is fixed: the single kernel adds its dQ partials in arrival order.
+std::atomic<int> g_deterministic{0};
+bool use_fused_backward(int D, int softmax, bool have_out) {
+  if (g_deterministic.load(std::memory_order_relaxed)) return false;
+  return (softmax || have_out) && (D == 64 || D == 128);
+}
 
 // Constant held by the operand-side slab of a bias-slab MMA step, and the "minus infinity" the slabs use on padding
 // rows. fp16 needs the range extension: a bias up to 65504 * 256 stays representable.
@@ -344,7 +353,7 @@ constexpr size_t kStaticScratchBytes = RBF_B200_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_static_scratch_addr[kMaxDevices] = {};
+std::atomic<void*> g_static_scratch_addr[kMaxDevices];
 
 // Device address of the scratch array on the current device; looked up once per device.
 int static_scratch_for_current_device(void** out) {
@@ -352,14 +361,15 @@ int static_scratch_for_current_device(void** out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "cudaGetDevice failed: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= kMaxDevices) return fail(RBF_B200_ERR_BAD_ARGUMENT, "device index %d is out of range", dev);
-  if (g_static_scratch_addr[dev] == nullptr) {
-    void* ptr = nullptr;
+  void* ptr = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    // the first call on a device: this may load the library's device image there
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess || ptr == nullptr)
       return fail(RBF_B200_ERR_LAUNCH, "cudaGetSymbolAddress failed for the static scratch: %s", cudaGetErrorString(e));
-    g_static_scratch_addr[dev] = ptr;
+    g_static_scratch_addr[dev].store(ptr, std::memory_order_release);   // every thread would store the same address
   }
-  *out = g_static_scratch_addr[dev];
+  *out = ptr;
   return 0;
 }
 
@@ -388,7 +398,14 @@ int rbf_b200_fwd_static(const void* q, const void* k, const void* v, void* out, 
 
 int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned int* code) {
   g_last_error[0] = 0;
-  if (workspace == nullptr || code == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "workspace or code is NULL");
+  if (code == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "code is NULL");
+  if (workspace == nullptr) {
+    // the built-in scratch of the current device (what rbf_b200_fwd_static used)
+    void* scratch = nullptr;
+    int rc;
+    if ((rc = static_scratch_for_current_device(&scratch))) return rc;
+    workspace = scratch;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   rbf::DeviceStatus st{};
   cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(st), cudaMemcpyDeviceToHost, stream);
@@ -396,8 +413,24 @@ int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned 
   if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "status read failed: %s", cudaGetErrorString(e));
   *code = st.code;
   if (st.code != 0)
-    return fail(RBF_B200_ERR_DEVICE, "device-side wait ran out: site %u, block (%u, %u)", st.code >> 24,
-                st.code & 0xfffu, (st.code >> 12) & 0xfffu);
+    return fail(RBF_B200_ERR_DEVICE, "device-side wait ran out: site %u, work unit %u", st.code >> 24,
+                st.code & 0xffffffu);
+  return RBF_B200_OK;
+}
+
+int rbf_b200_set_deterministic(int on) { return g_deterministic.exchange(on ? 1 : 0); }
+
+int rbf_b200_get_deterministic(void) { return g_deterministic.load(); }
+
+int rbf_b200_selftest_wait_timeout(void* workspace, size_t workspace_bytes, long long limit_cycles, void* stream_v) {
+  g_last_error[0] = 0;
+  if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < kStatusBytes)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL, not 256-byte aligned or smaller than %zu bytes", kStatusBytes);
+  if (limit_cycles <= 0 || limit_cycles > 2000000000ll)
+    return fail(RBF_B200_ERR_BAD_ARGUMENT, "limit_cycles must be in (0, 2e9]");
+  const cudaError_t e = rbf::launch_wait_selftest(static_cast<rbf::DeviceStatus*>(workspace), limit_cycles,
+                                                  static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "self-test launch failed: %s", cudaGetErrorString(e));
   return RBF_B200_OK;
 }
 

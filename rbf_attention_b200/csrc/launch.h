@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace rbf {
@@ -37,6 +39,11 @@ struct RowStatsArgs {
   DeviceStatus* status_to_clear;  // optional: the 256-byte status block (status word, work counters) is zeroed
 };
 cudaError_t launch_row_stats(const RowStatsArgs& a, bool bf16, int D, cudaStream_t stream);
+
+// Self-test of the bounded waits: one block waits on a barrier that nothing arms; when the wait runs out after `limit`
+// SM clocks it records site kSiteSelfTest in `status` exactly as the attention kernels do, and the kernel returns.
+static constexpr uint32_t kSiteSelfTest = 250;
+cudaError_t launch_wait_selftest(DeviceStatus* status, long long limit, cudaStream_t stream);
 
 // Forward pass. Tensor maps use a 64-element x 128-row box with the 128-byte swizzle.
 struct FwdArgs {
@@ -92,5 +99,24 @@ struct BwdFusedArgs {
 };
 cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream);      // D = 64
 cudaError_t launch_bwd_fused128(const BwdFusedArgs& a, bool bf16, cudaStream_t stream);   // D = 128
+
+// cudaFuncSetAttribute applies to the current device only, so a kernel's dynamic shared-memory limit has to be raised
+// once on every device the process launches it on. One flag per device and kernel instantiation; devices beyond the
+// table are configured on every launch.
+struct PerDeviceFlags {
+  static constexpr int kMaxDevices = 64;
+  std::atomic<int> done[kMaxDevices];
+};
+template <class Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, PerDeviceFlags& flags) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool cached = dev >= 0 && dev < PerDeviceFlags::kMaxDevices;
+  if (cached && flags.done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && cached) flags.done[dev].store(1, std::memory_order_release);
+  return e;
+}
 
 }  // namespace rbf

@@ -17,7 +17,7 @@ namespace rbf {
 // so that all roles leave their loops, TMEM is freed and the kernel returns normally.
 // ---------------------------------------------------------------------------------------------
 struct DeviceStatus {
-  unsigned int code;   // 0 = ok; otherwise (site << 24) | (blockIdx.y & 0xfff) << 12 | (blockIdx.x & 0xfff)
+  unsigned int code;   // 0 = ok; otherwise (site << 24) | (work unit & 0xffffff), see status_unit()
 };
 
 static constexpr long long kWaitCycleLimit = 2000000000ll;  // about one second of SM clocks
@@ -68,26 +68,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. Returns false when the wait ran out or another thread of the CTA raised `abort`.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          DeviceStatus* status, uint32_t site) {
+// Work unit a status code names: the linear block index of a plain grid, or - for a persistent launch, whose
+// blocks take work items from a counter - the item the block was working on (`unit_ptr` points at it).
+__device__ __forceinline__ uint32_t status_unit(const volatile int* unit_ptr) {
+  if (unit_ptr != nullptr) return static_cast<uint32_t>(*unit_ptr);
+  return blockIdx.y * gridDim.x + blockIdx.x;
+}
+
+// Bounded wait. Returns false when the wait ran out (after `limit` SM clocks) or another thread of the CTA raised
+// `abort_flag`. The first wait of a launch that runs out records (site, work unit) in the status word.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                DeviceStatus* status, uint32_t site, long long limit,
+                                                const volatile int* unit_ptr = nullptr) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3f) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycleLimit) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
-        if (status != nullptr) {
-          atomicCAS(&status->code, 0u,
-                    (site << 24) | ((blockIdx.y & 0xfffu) << 12) | (blockIdx.x & 0xfffu));
-        }
+        if (status != nullptr) atomicCAS(&status->code, 0u, (site << 24) | (status_unit(unit_ptr) & 0xffffffu));
         return false;
       }
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          DeviceStatus* status, uint32_t site,
+                                          const volatile int* unit_ptr = nullptr) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, site, kWaitCycleLimit, unit_ptr);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -474,11 +474,10 @@ template <int D, int kMode, bool kBf16>
 static cudaError_t launch_t(const BwdArgs& a, bool softmax, cudaStream_t stream) {
   auto kernel = rbf_bwd_kernel<D, kMode, kBf16>;
   constexpr int smem = Cfg<D, kMode>::kDynamic;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
+  static PerDeviceFlags configured{};
+  {
+    const cudaError_t ce = ensure_dynamic_smem(kernel, smem, configured);
+    if (ce != cudaSuccess) return ce;
   }
   Params p{};
   p.delta = a.delta;

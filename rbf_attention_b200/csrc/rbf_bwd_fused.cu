@@ -29,18 +29,6 @@ namespace rbf {
 
 namespace bwdf {
 
-#ifdef RBF_TRACE
-// Bring-up aid (not compiled into the product): clock64 stamps of one CTA's roles per step.
-__device__ long long g_trace[4 * 64 * 16];
-#define RBF_TRACE_EVENT(role, step, ev)                                                              \
-  do {                                                                                               \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (step) < 64) g_trace[((role)*64 + (step)) * 16 + (ev)] = clock64(); \
-  } while (0)
-#else
-#define RBF_TRACE_EVENT(role, step, ev) \
-  do {                                  \
-  } while (0)
-#endif
 
 static constexpr int D = 64;
 static constexpr int kThreads = 768;
@@ -258,8 +246,8 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           const int st = n % kStages;
           const uint32_t par = ((n / kStages) - 1) & 1;
           // the ring slot is free once the MMAs that read it have completed (both rings, in the order the loads go)
-          if (!mbar_wait(&q_empty[st], par, abort_flag, p.status, kSiteQEmpty)) break;
-          if (!mbar_wait(&do_empty[st], par, abort_flag, p.status, kSiteDoEmpty)) break;
+          if (!mbar_wait(&q_empty[st], par, abort_flag, p.status, kSiteQEmpty, s_item)) break;
+          if (!mbar_wait(&do_empty[st], par, abort_flag, p.status, kSiteDoEmpty, s_item)) break;
           load_step(n);
         }
       }
@@ -287,12 +275,12 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         umma_ss(dst, sdesc_at(ones_desc, 0), sdesc_at(slab, 0), idesc_s, 1u);
       };
       auto wait_q = [&](int n) {
-        return mbar_wait(&q_full[n % kStages], (n / kStages) & 1, abort_flag, p.status, kSiteQFull);
+        return mbar_wait(&q_full[n % kStages], (n / kStages) & 1, abort_flag, p.status, kSiteQFull, s_item);
       };
       auto wait_do = [&](int n) {
-        return mbar_wait(&do_full[n % kStages], (n / kStages) & 1, abort_flag, p.status, kSiteDoFull);
+        return mbar_wait(&do_full[n % kStages], (n / kStages) & 1, abort_flag, p.status, kSiteDoFull, s_item);
       };
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kSiteKV);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kSiteKV, s_item);
 
       if (warp == kMmaWarpA) {
         const SmemDesc k_kmaj = make_sdesc_parts(smem_u32(s_k), 16, 1024);
@@ -310,20 +298,16 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           if (n + 1 < cnt) {
             // S^T(n+1) may overwrite S^T(n) as soon as every compute warp holds it in registers
             const int st = (n + 1) % kStages;
-            RBF_TRACE_EVENT(0, n, 0);
-            ok = wait_q(n + 1) && mbar_wait(s_consumed, n & 1, abort_flag, p.status, kSiteSConsumed);
+            ok = wait_q(n + 1) && mbar_wait(s_consumed, n & 1, abort_flag, p.status, kSiteSConsumed, s_item);
             if (!ok) break;
-            RBF_TRACE_EVENT(0, n, 1);
             tc_fence_after_sync();
             issue_scores(tmem + kColS, k_kmaj, stage_of(q_kmaj0, st, kTileBytes), stage_of(lslab0, st, kSlabBytes));
             umma_commit(s_full);
             umma_commit(&q_empty[st]);
           }
           // dV += P^T dO
-          RBF_TRACE_EVENT(0, n, 2);
-          ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
+          ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull, s_item);
           if (!ok) break;
-          RBF_TRACE_EVENT(0, n, 3);
           tc_fence_after_sync();
           const SmemDesc do_n = stage_of(do_nmaj0, n % kStages, kTileBytes);
 #pragma unroll
@@ -332,15 +316,14 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(dv_done);
           umma_commit(&do_empty[n % kStages]);
-          RBF_TRACE_EVENT(0, n, 4);
         }
       } else if (warp == kMmaWarpC) {
         // dQ_partial = dS K : A = the dS^T tile read M-major (rows = keys = reduction index), B = K read N-major
         const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
         const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);   // rows = reduction (keys)
         for (int n = 0; n < cnt && ok; ++n) {
-          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
-          if (ok && n > 0) ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained);
+          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull, s_item);
+          if (ok && n > 0) ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained, s_item);
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
@@ -364,20 +347,16 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         for (int n = 0; n < cnt && ok; ++n) {
           if (n + 1 < cnt) {
             const int st = (n + 1) % kStages;
-            RBF_TRACE_EVENT(1, n, 0);
-            ok = wait_do(n + 1) && mbar_wait(dp_consumed, n & 1, abort_flag, p.status, kSiteDPConsumed);
+            ok = wait_do(n + 1) && mbar_wait(dp_consumed, n & 1, abort_flag, p.status, kSiteDPConsumed, s_item);
             if (!ok) break;
-            RBF_TRACE_EVENT(1, n, 1);
             tc_fence_after_sync();
             issue_scores(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, st, kTileBytes), stage_of(dslab0, st, kSlabBytes));
             umma_commit(dp_full);
             umma_commit(&do_empty[st]);
           }
           // dK += dS^T Q : A = dS^T tile (K-major: 64-query boxes of 128-byte rows), B = Q read N-major
-          RBF_TRACE_EVENT(1, n, 2);
-          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull);
+          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull, s_item);
           if (!ok) break;
-          RBF_TRACE_EVENT(1, n, 3);
           tc_fence_after_sync();
           const SmemDesc q_n = stage_of(q_nmaj0, n % kStages, kTileBytes);
 #pragma unroll
@@ -386,7 +365,6 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     idesc_acc, (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&q_empty[n % kStages]);
           umma_commit(dq_full);                    // first of two arrivals: the dS^T tile's K-major reader is done
-          RBF_TRACE_EVENT(1, n, 4);
         }
       }
       if (ok) umma_commit(acc_done);   // every issuer arrives: the barrier counts three
@@ -407,10 +385,8 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     tmem = *tmem_base_s;
     bool ok = true;
     for (int n = 0; n < cnt; ++n) {
-      if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 0);
-      ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull);
+      ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull, s_item);
       if (!ok) break;
-      if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 1);
       tc_fence_after_sync();
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
@@ -435,7 +411,6 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           tma_reduce_add_4d(&tm_dq_acc, my_boxes + hh * kDqBoxBytes, hh * 32, (first + n) * kTile + wq * 32, h, b);
           tma_store_commit();
         }
-        if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 2 + hh);
       }
     }
     if (lane == 0) tma_store_wait_all();
@@ -453,22 +428,17 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     float ds_rowsum = 0.f;
     bool ok = true;
 
-    const bool tr = (tid == kComputeWarp0 * 32);
     for (int n = 0; n < cnt; ++n) {
-      if (tr) RBF_TRACE_EVENT(2, n, 0);
-      ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
+      ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull, s_item);
       if (!ok) break;
-      if (tr) RBF_TRACE_EVENT(2, n, 1);
       tc_fence_after_sync();
       float pr[32];
       {
         uint32_t raw[32];
         tmem_ld_x32(tmem + kColS + lane_sel + g * 32, raw);
         tmem_ld_wait();
-        if (tr) RBF_TRACE_EVENT(2, n, 8);
         tc_fence_before_sync();
         mbar_arrive_warp(s_consumed);
-        if (tr) RBF_TRACE_EVENT(2, n, 9);
         // acc = k.q - L / scale2 ; P = exp2(acc * scale2 - ksq)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -477,7 +447,6 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           pr[i] = ex2_approx(a0);
           pr[i + 1] = ex2_approx(a1);
         }
-        if (tr) RBF_TRACE_EVENT(2, n, 10);
       }
       if (p.causal && n == 0) {
         // diagonal tile: query column (32g + c) sees key row r iff column >= row
@@ -491,31 +460,26 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         for (int i = 0; i < 16; ++i) packed[i] = pack2<kBf16>(pr[2 * i], pr[2 * i + 1]);
         // the P^T columns are free once dV of the previous step has completed
         if (n > 0) {
-          ok = mbar_wait(dv_done, (n - 1) & 1, abort_flag, p.status, kSiteDVDone);
+          ok = mbar_wait(dv_done, (n - 1) & 1, abort_flag, p.status, kSiteDVDone, s_item);
           if (!ok) break;
           tc_fence_after_sync();
         }
-        if (tr) RBF_TRACE_EVENT(2, n, 2);
         tmem_st_x16(tmem + kColPT + lane_sel + g * 16, packed);
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive_warp(p_full);
       }
-      if (tr) RBF_TRACE_EVENT(2, n, 3);
 
-      ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull);
+      ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull, s_item);
       if (!ok) break;
-      if (tr) RBF_TRACE_EVENT(2, n, 4);
       tc_fence_after_sync();
       uint32_t ds_packed[16];
       {
         uint32_t raw[32];
         tmem_ld_x32(tmem + kColDP + lane_sel + g * 32, raw);
         tmem_ld_wait();
-        if (tr) RBF_TRACE_EVENT(2, n, 12);
         tc_fence_before_sync();
         mbar_arrive_warp(dp_consumed);
-        if (tr) RBF_TRACE_EVENT(2, n, 13);
         // acc = v.dO - delta ; dS = P * acc
         float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
@@ -527,32 +491,28 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
         ds_rowsum += rs0 + rs1;
       }
-      if (tr) RBF_TRACE_EVENT(2, n, 5);
       // the dS^T tile is free once dK and dQ_partial of the previous step have completed
       if (n > 0) {
-        ok = mbar_wait(dq_full, (n - 1) & 1, abort_flag, p.status, kSiteDsFree);
+        ok = mbar_wait(dq_full, (n - 1) & 1, abort_flag, p.status, kSiteDsFree, s_item);
         if (!ok) break;
       }
-      if (tr) RBF_TRACE_EVENT(2, n, 11);
       // row r of the [key][query] tile, box g/2, 16-byte chunks 4(g%2) .. +3
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch)
         *reinterpret_cast<uint4*>(s_ds + (g >> 1) * (kTile * 128) + sw128_offset(r, (g & 1) * 4 + ch)) =
             make_uint4(ds_packed[ch * 4 + 0], ds_packed[ch * 4 + 1], ds_packed[ch * 4 + 2], ds_packed[ch * 4 + 3]);
-      if (tr) RBF_TRACE_EVENT(2, n, 6);
       fence_proxy_async_smem();
       mbar_arrive_warp(ds_full);
-      if (tr) RBF_TRACE_EVENT(2, n, 7);
     }
 
     uint32_t grp_phase = 0;
     auto group_sync = [&]() -> bool {
       mbar_arrive_warp(grp_sync);
-      const bool done = mbar_wait(grp_sync, grp_phase & 1, abort_flag, p.status, kSiteGroup);
+      const bool done = mbar_wait(grp_sync, grp_phase & 1, abort_flag, p.status, kSiteGroup, s_item);
       ++grp_phase;
       return done;
     };
-    if (ok) ok = mbar_wait(acc_done, 0, abort_flag, p.status, kSiteAccDone);
+    if (ok) ok = mbar_wait(acc_done, 0, abort_flag, p.status, kSiteAccDone, s_item);
     if (ok) {
       tc_fence_after_sync();
       s_rowsum[g * kTile + r] = ds_rowsum;      // every group holds a quarter of rowsum(dS^T)
@@ -654,11 +614,10 @@ template <bool kBf16>
 static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
   auto kernel = rbf_bwd_fused_kernel<kBf16>;
   constexpr int smem = Smem::kDynamic;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
+  static PerDeviceFlags configured{};
+  {
+    const cudaError_t ce = ensure_dynamic_smem(kernel, smem, configured);
+    if (ce != cudaSuccess) return ce;
   }
   // the pre-pass has cleared the dQ accumulator
   cudaError_t e = cudaSuccess;
@@ -681,11 +640,6 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
 
 }  // namespace bwdf
 
-#ifdef RBF_TRACE
-extern "C" int rbf_b200_debug_read_trace(long long* host, int count) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, bwdf::g_trace, sizeof(long long) * count));
-}
-#endif
 
 cudaError_t launch_bwd_fused(const BwdFusedArgs& a, bool bf16, cudaStream_t stream) {
   return bf16 ? bwdf::launch_t<true>(a, stream) : bwdf::launch_t<false>(a, stream);

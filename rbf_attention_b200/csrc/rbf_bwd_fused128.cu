@@ -29,19 +29,6 @@ namespace rbf {
 
 namespace bwdf128 {
 
-#ifdef RBF_TRACE
-// Bring-up aid (not compiled into the product): clock64 stamps of one CTA's roles per step.
-__device__ long long g_trace128[5 * 64 * 16];
-#define RBF_TRACE_EVENT(role, step, ev)                                                                 \
-  do {                                                                                                  \
-    if (blockIdx.x == RBF_TRACE_BX && blockIdx.y == 0 && (step) < 64)                                   \
-      g_trace128[((role)*64 + (step)) * 16 + (ev)] = clock64();                                         \
-  } while (0)
-#else
-#define RBF_TRACE_EVENT(role, step, ev) \
-  do {                                  \
-  } while (0)
-#endif
 
 static constexpr int D = 128;
 static constexpr int kQStep = 64;                   // queries per step
@@ -268,20 +255,16 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         for (int n = 0; n < cnt && ok; ++n) {
           if (n + 1 < cnt) {
             const int st = (n + 1) % kQStages;
-            RBF_TRACE_EVENT(0, n, 0);
             ok = wait_q(n + 1) && mbar_wait(s_consumed, n & 1, abort_flag, p.status, kSiteSConsumed);
             if (!ok) break;
-            RBF_TRACE_EVENT(0, n, 1);
             tc_fence_after_sync();
             issue_scores(tmem + kColS, k_kmaj, stage_of(q_kmaj0, st, kQTileBytes), stage_of(lslab0, st, kSlabBytes));
             umma_commit(s_full);
             umma_commit(&q_empty[st]);
           }
           // dV += P^T dO
-          RBF_TRACE_EVENT(0, n, 2);
           ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull);
           if (!ok) break;
-          RBF_TRACE_EVENT(0, n, 3);
           tc_fence_after_sync();
           const SmemDesc do_n = stage_of(do_nmaj0, n % kDoStages, kQTileBytes);
 #pragma unroll
@@ -290,7 +273,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
                     (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(dv_done);
           umma_commit(&do_empty[n % kDoStages]);
-          RBF_TRACE_EVENT(0, n, 4);
         }
       } else if (warp == kMmaWarpB) {
         const SmemDesc v_kmaj = make_sdesc_parts(smem_u32(s_v), 16, 1024);
@@ -307,20 +289,16 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         for (int n = 0; n < cnt && ok; ++n) {
           if (n + 1 < cnt) {
             const int st = (n + 1) % kDoStages;
-            RBF_TRACE_EVENT(1, n, 0);
             ok = wait_do(n + 1) && mbar_wait(dp_consumed, n & 1, abort_flag, p.status, kSiteDPConsumed);
             if (!ok) break;
-            RBF_TRACE_EVENT(1, n, 1);
             tc_fence_after_sync();
             issue_scores(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, st, kQTileBytes), stage_of(dslab0, st, kSlabBytes));
             umma_commit(dp_full);
             umma_commit(&do_empty[st]);
           }
           // dK += dS^T Q
-          RBF_TRACE_EVENT(1, n, 2);
           ok = mbar_wait(&ds_full[n % kDsStages], (n / kDsStages) & 1, abort_flag, p.status, kSiteDSFull);
           if (!ok) break;
-          RBF_TRACE_EVENT(1, n, 3);
           tc_fence_after_sync();
           // A = the TMEM copy of dS^T (16-bit pairs, 32 columns): only Q is fetched from shared memory
           const SmemDesc q_n = stage_of(q_nmaj0, n % kQStages, kQTileBytes);
@@ -330,7 +308,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
                     (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&q_empty[n % kQStages]);
           umma_commit(dk_done);
-          RBF_TRACE_EVENT(1, n, 4);
         }
       } else {
         // dQ^T = K^T dS^T : A = K tile read M-major (rows = keys = reduction index, 64-wide d groups 16 KB apart),
@@ -338,12 +315,9 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         const SmemDesc k_mmaj = make_sdesc_parts(smem_u32(s_k), kBoxBytes, 1024);
         const SmemDesc ds_nmaj = make_sdesc_parts(smem_u32(s_ds), kBoxBytes, 1024);
         for (int n = 0; n < cnt && ok; ++n) {
-          RBF_TRACE_EVENT(4, n, 0);
           ok = mbar_wait(&ds_full[n % kDsStages], (n / kDsStages) & 1, abort_flag, p.status, kSiteDSFull);
-          RBF_TRACE_EVENT(4, n, 1);
           if (ok && n > 0) ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained);
           if (!ok) break;
-          RBF_TRACE_EVENT(4, n, 2);
           tc_fence_after_sync();
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
@@ -351,7 +325,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
                     sdesc_at(ds_nmaj, (n % kDsStages) * kDsBytes + kk * 2048), idesc_dq, kk > 0);
           umma_commit(dq_full);                    // dQ^T readable
           umma_commit(&ds_free[n % kDsStages]);    // the shared-memory tile's reader is done
-          RBF_TRACE_EVENT(4, n, 3);
         }
       }
       if (ok) umma_commit(acc_done);
@@ -364,10 +337,8 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     float* acc_col = p.dq_acc + static_cast<int64_t>(bh) * p.N * D + wq * 32 + lane;
     bool ok = true;
     for (int n = 0; n < cnt; ++n) {
-      if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 0);
       ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull);
       if (!ok) break;
-      if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 1);
       tc_fence_after_sync();
       const int q0 = (first + n) * kQStep;
       const int valid = p.N - q0;                           // queries of this step inside the sequence
@@ -389,7 +360,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
           for (int i = 0; i < 32; ++i)
             if (hh * 32 + i < valid) red_add_f32(dst + (hh * 32 + i) * D, __uint_as_float(v[i]));
         }
-        if (tid == kDrainWarp0 * 32) RBF_TRACE_EVENT(3, n, 2 + hh);
       }
     }
   } else {
@@ -403,11 +373,8 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     bool ok = true;
 
     for (int n = 0; n < cnt; ++n) {
-      const bool tr = tid == kComputeWarp0 * 32;
-      if (tr) RBF_TRACE_EVENT(2, n, 0);
       ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
       if (!ok) break;
-      if (tr) RBF_TRACE_EVENT(2, n, 1);
       tc_fence_after_sync();
       float pr[16];
       {
@@ -416,7 +383,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         tmem_ld_wait();
         tc_fence_before_sync();
         mbar_arrive_warp(s_consumed);
-        if (tr) RBF_TRACE_EVENT(2, n, 2);
         // acc = k.q - L / scale2 ; P = exp2(acc * scale2 - ksq)
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
@@ -437,23 +403,19 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         uint32_t packed[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) packed[i] = pack2<kBf16>(pr[2 * i], pr[2 * i + 1]);
-        if (tr) RBF_TRACE_EVENT(2, n, 3);
         if (n > 0) {   // the P^T columns are free once dV of the previous step has completed
           ok = mbar_wait(dv_done, (n - 1) & 1, abort_flag, p.status, kSiteDVDone);
           if (!ok) break;
           tc_fence_after_sync();
         }
-        if (tr) RBF_TRACE_EVENT(2, n, 4);
         tmem_st_x8(tmem + kColPT + lane_sel + g * 8, packed);
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive_warp(p_full);
       }
 
-      if (tr) RBF_TRACE_EVENT(2, n, 5);
       ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull);
       if (!ok) break;
-      if (tr) RBF_TRACE_EVENT(2, n, 6);
       tc_fence_after_sync();
       uint32_t ds_packed[8];
       {
@@ -462,7 +424,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         tmem_ld_wait();
         tc_fence_before_sync();
         mbar_arrive_warp(dp_consumed);
-        if (tr) RBF_TRACE_EVENT(2, n, 7);
         // acc = v.dO - delta ; dS = P * acc
         float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
@@ -474,12 +435,10 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
         }
         ds_rowsum += rs0 + rs1;
       }
-      if (tr) RBF_TRACE_EVENT(2, n, 8);
       if (n >= kDsStages) {   // the dS^T buffer is free once dK and dQ^T of its previous step have completed
         ok = mbar_wait(&ds_free[n % kDsStages], ((n / kDsStages) - 1) & 1, abort_flag, p.status, kSiteDsFree);
         if (!ok) break;
       }
-      if (tr) RBF_TRACE_EVENT(2, n, 9);
       // row r of the [key][query] tile: 16-byte chunks 2g and 2g + 1
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch)
@@ -496,7 +455,6 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive_warp(&ds_full[n % kDsStages]);
-      if (tr) RBF_TRACE_EVENT(2, n, 10);
     }
 
     uint32_t grp_phase = 0;
@@ -601,11 +559,10 @@ template <bool kBf16>
 static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
   auto kernel = rbf_bwd_fused128_kernel<kBf16>;
   constexpr int smem = Smem::kDynamic;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
+  static PerDeviceFlags configured{};
+  {
+    const cudaError_t ce = ensure_dynamic_smem(kernel, smem, configured);
+    if (ce != cudaSuccess) return ce;
   }
   // the pre-pass has cleared the dQ accumulator
   cudaError_t e = cudaSuccess;
@@ -627,11 +584,6 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
 
 }  // namespace bwdf128
 
-#ifdef RBF_TRACE
-extern "C" int rbf_b200_debug_read_trace128(long long* host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, bwdf128::g_trace128, sizeof(long long) * n));
-}
-#endif
 
 cudaError_t launch_bwd_fused128(const BwdFusedArgs& a, bool bf16, cudaStream_t stream) {
   return bf16 ? bwdf128::launch_t<true>(a, stream) : bwdf128::launch_t<false>(a, stream);

@@ -27,19 +27,6 @@ namespace rbf {
 
 namespace fwd {
 
-#ifdef RBF_TRACE
-// Bring-up aid (not compiled into the product): clock64 stamps of one CTA's roles per key tile.
-__device__ long long g_trace_fwd[12 * 64 * 16];
-#define RBF_FTRACE(role, step, ev)                                                                   \
-  do {                                                                                               \
-    if (blockIdx.x == RBF_TRACE_BX && blockIdx.y == 0 && (step) < 64)                                \
-      g_trace_fwd[((role)*64 + (step)) * 16 + (ev)] = clock64();                                     \
-  } while (0)
-#else
-#define RBF_FTRACE(role, step, ev) \
-  do {                             \
-  } while (0)
-#endif
 
 
 static constexpr int kThreads = 384;
@@ -301,23 +288,17 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (j < my_nkt) {
           if (kSeparateP && j + 1 < my_nkt) {
             // next scores first: they only need S_t(j) to have been read
-            RBF_FTRACE(t, j, 0);
             ok = wait_k(j + 1) && mbar_wait(&s_consumed[t], j & 1, abort_flag, status, kSiteSConsumed);
             if (!ok) break;
-            RBF_FTRACE(t, j, 1);
             tc_fence_after_sync();
             issue_s(st_next);
             used_k_next = true;
-            RBF_FTRACE(t, j, 2);
           }
           ok = wait_v(j);
-          RBF_FTRACE(t, j, 5);
           ok = ok && mbar_wait(&p_full[t], j & 1, abort_flag, status, kSitePFull);
           if (!ok) break;
-          RBF_FTRACE(t, j, 3);
           tc_fence_after_sync();
           issue_o(st, j > 0 ? 1u : 0u);
-          RBF_FTRACE(t, j, 4);
           if (!kSeparateP && j + 1 < my_nkt) {
             ok = wait_k(j + 1);
             if (!ok) break;
@@ -365,12 +346,8 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
     for (int j = 0; j < my_nkt; ++j) {
-      if (r == 0) RBF_FTRACE(2 + t, j, 0);
       ok = mbar_wait(&s_full[t], j & 1, abort_flag, status, kSiteSFull);
       if (!ok) break;
-      if (r == 0) RBF_FTRACE(2 + t, j, 1);
-#define RBF_WTRACE(ev) do { if ((tid & 31) == 0) RBF_FTRACE(4 + warp, j, ev); } while (0)
-      RBF_WTRACE(0);
       tc_fence_after_sync();
 
       // acc = q.k - |k|^2 / 2 for the tile's keys; the logit in base-2 units is acc * scale2
@@ -384,8 +361,6 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_before_sync();
           mbar_arrive_warp(&s_consumed[t]);
         }
-        if (r == 0) RBF_FTRACE(2 + t, j, 2);
-        RBF_WTRACE(1);
       }
       if (causal && (j + 1) * kKeys > r0 + 1) {
         // tiles that reach past the block's first row: key (j * kKeys + c) is visible to query (r0 + r) iff it is
@@ -438,8 +413,6 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         sub = row_bias;
       }
 
-      if (r == 0) RBF_FTRACE(2 + t, j, 3);
-      RBF_WTRACE(2);
       bool waited_o = !kSeparateP || j == 0;   // P's own columns are free once O_t += P_t V_(j-1) has completed
       const float neg_sub = -sub;
       float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
@@ -459,26 +432,19 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           packed[i] = pack2<kBf16>(p0, p1);
           packed[i + 1] = pack2<kBf16>(p2, p3);
         }
-        if (r == 0) RBF_FTRACE(2 + t, j, 4 + 3 * c);
-        RBF_WTRACE(3 + 2 * c);
         if (!waited_o) {
           ok = mbar_wait(&o_done[t], (j - 1) & 1, abort_flag, status, kSitePFree);
           if (!ok) break;
           tc_fence_after_sync();
           waited_o = true;
         }
-        if (r == 0) RBF_FTRACE(2 + t, j, 5 + 3 * c);
         tmem_st_x32(tmem_p[t] + lane_sel + c * 32, packed);
-        if (r == 0) RBF_FTRACE(2 + t, j, 6 + 3 * c);
-        RBF_WTRACE(4 + 2 * c);
       }
       if (!ok) break;
       l_sum += (ps0 + ps1) + (ps2 + ps3);
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive_warp(&p_full[t]);
-      if (r == 0) RBF_FTRACE(2 + t, j, 10);
-      RBF_WTRACE(7);
     }
 
     if (ok && my_nkt > 0) {
@@ -536,11 +502,10 @@ template <int D, bool kSoftmax, bool kBf16>
 static cudaError_t launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
   auto kernel = fwd::rbf_fwd_kernel<D, kSoftmax, kBf16>;
   constexpr int smem = fwd::Smem<D>::kDynamic;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
+  static PerDeviceFlags configured{};
+  {
+    const cudaError_t ce = ensure_dynamic_smem(kernel, smem, configured);
+    if (ce != cudaSuccess) return ce;
   }
   const unsigned blocks = (a.N + 2 * kTile - 1) / (2 * kTile), heads = a.B * a.H;
   dim3 grid(a.causal ? heads : blocks, a.causal ? blocks : heads);
@@ -564,10 +529,5 @@ cudaError_t launch_fwd(const FwdArgs& a, bool bf16, int D, bool softmax, cudaStr
   return cudaErrorInvalidValue;
 }
 
-#ifdef RBF_TRACE
-extern "C" int rbf_b200_debug_read_trace_fwd(long long* host, int count) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, rbf::fwd::g_trace_fwd, sizeof(long long) * count));
-}
-#endif
 
 }  // namespace rbf

@@ -125,6 +125,27 @@ static cudaError_t launch_row_stats_t(RowStatsArgs a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+__global__ void __launch_bounds__(32) wait_selftest_kernel(DeviceStatus* status, long long limit) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    abort_flag = 0;
+  }
+  __syncwarp();
+  // nothing ever arrives on `bar`: the first lane whose limit runs out records the status and raises the flag, the
+  // other lanes leave on the flag, and the block returns
+  mbar_wait_limit(&bar, 0, &abort_flag, status, kSiteSelfTest, limit);
+  __syncwarp();
+  if (threadIdx.x == 0) mbar_inval(&bar);
+}
+
+cudaError_t launch_wait_selftest(DeviceStatus* status, long long limit, cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_row_stats(const RowStatsArgs& a, bool bf16, int D, cudaStream_t stream) {
   if (D == 64) return bf16 ? launch_row_stats_t<true, 64>(a, stream) : launch_row_stats_t<false, 64>(a, stream);
   return bf16 ? launch_row_stats_t<true, 128>(a, stream) : launch_row_stats_t<false, 128>(a, stream);

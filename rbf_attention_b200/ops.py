@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -71,6 +72,88 @@ def _workspace(B, H, N, D, softmax, backward, device) -> torch.Tensor:
     return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
 
+class _StatusMonitor:
+    """Surfaces device-side wait timeouts of the operator path without synchronising.
+
+    Every kernel bounds its waits; one that runs out leaves a non-zero status word at the start of the call's
+    workspace and the kernels return with incomplete results. After each launch the word is copied (asynchronously,
+    on the launch stream) into a ring of pinned host slots; later calls look at the slots whose copy has completed
+    and raise ``RuntimeError`` for a non-zero one. A timeout is therefore reported by a later operator call or by
+    ``check_device_status()``, not by the call that suffered it. ``RBF_B200_SYNC_STATUS=1`` makes every call
+    synchronise and check its own status (for debugging). Nothing is recorded while a CUDA graph is being captured.
+    """
+
+    SLOTS = 64
+
+    def __init__(self, device):
+        self.device = device
+        self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        self.events = [None] * self.SLOTS
+        self.what = [""] * self.SLOTS
+        self.oldest = 0        # the pending entries are the slots oldest, oldest + 1, ..., next - 1 (mod SLOTS)
+        self.next = 0
+        self.pending = 0
+
+    def _retire_oldest(self):
+        i = self.oldest
+        self.events[i] = None
+        self.oldest = (i + 1) % self.SLOTS
+        self.pending -= 1
+        code = int(self.host[i]) & 0xFFFFFFFF
+        if code != 0:
+            self.host[i] = 0
+            raise RuntimeError(
+                f"{self.what[i]}: a device-side wait ran out (site {code >> 24}, work unit {code & 0xFFFFFF}); "
+                "the results of that call are incomplete"
+            )
+
+    def poll(self, wait=False):
+        """Checks the entries whose copy has completed, oldest first (all of them after waiting when ``wait``)."""
+        while self.pending:
+            ev = self.events[self.oldest]
+            if wait:
+                ev.synchronize()
+            elif not ev.query():
+                break
+            self._retire_oldest()
+
+    def record(self, ws, what):
+        if torch.cuda.is_current_stream_capturing():
+            return
+        if self.pending == self.SLOTS:          # the ring is full: wait for its oldest entry
+            self.events[self.oldest].synchronize()
+            self._retire_oldest()
+        i = self.next
+        self.host[i : i + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i], self.what[i] = ev, what
+        self.next = (i + 1) % self.SLOTS
+        self.pending += 1
+        if _SYNC_STATUS:
+            self.poll(wait=True)
+
+
+_SYNC_STATUS = os.environ.get("RBF_B200_SYNC_STATUS", "0") not in ("", "0")
+_monitors: dict = {}
+
+
+def _monitor(device) -> _StatusMonitor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    m = _monitors.get(key)
+    if m is None:
+        m = _monitors[key] = _StatusMonitor(device)
+    return m
+
+
+def check_device_status(device=None) -> None:
+    """Waits for every operator call made so far on ``device`` (default: the current one) and raises
+    ``RuntimeError`` if one of them ended with a device-side wait that ran out."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    _monitor(torch.device(device)).poll(wait=True)
+
+
 def _forward(q, k, v, is_causal: bool, softmax: bool):
     _validate("q", q)
     _validate("k", k, q)
@@ -84,6 +167,8 @@ def _forward(q, k, v, is_causal: bool, softmax: bool):
     out = torch.empty((B, H, N, D), dtype=cdt, device=q.device)
     lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device) if softmax else None
     ws = _workspace(B, H, N, D, softmax, False, q.device)
+    mon = _monitor(q.device)
+    mon.poll()
     with torch.cuda.device(q.device):
         rc = lib.rbf_b200_fwd(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
@@ -91,7 +176,8 @@ def _forward(q, k, v, is_causal: bool, softmax: bool):
             B, H, N, D, _lib.strides3(qc), _lib.strides3(kc), _lib.strides3(vc), _lib.strides3(out),
             _DTYPE_CODE[cdt], int(bool(is_causal)), int(softmax), 1.0 / math.sqrt(D), _stream_ptr(q.device),
         )
-    _lib.check(rc, "rbf_b200_fwd")
+        _lib.check(rc, "rbf_b200_fwd")
+        mon.record(ws, "rbf_b200_fwd")
     if cdt != q.dtype:
         out = out.to(q.dtype)
     return out, lse
@@ -114,6 +200,10 @@ def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax
     dv = torch.empty_like(dq)
     ws = _workspace(B, H, N, D, softmax, True, q.device)
     z3 = (ctypes.c_int64 * 3)(0, 0, 0)
+    mon = _monitor(q.device)
+    mon.poll()
+    # torch.use_deterministic_algorithms(True) selects the backward whose summation order is fixed
+    lib.rbf_b200_set_deterministic(int(torch.are_deterministic_algorithms_enabled()))
     with torch.cuda.device(q.device):
         rc = lib.rbf_b200_bwd(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
@@ -124,7 +214,8 @@ def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax
             _lib.strides3(dq), _lib.strides3(dk), _lib.strides3(dv),
             _DTYPE_CODE[cdt], int(bool(is_causal)), int(softmax), float(sm_scale), _stream_ptr(q.device),
         )
-    _lib.check(rc, "rbf_b200_bwd")
+        _lib.check(rc, "rbf_b200_bwd")
+        mon.record(ws, "rbf_b200_bwd")
     if cdt != q.dtype:
         dq, dk, dv = dq.to(q.dtype), dk.to(q.dtype), dv.to(q.dtype)
     return dq, dk, dv

@@ -66,3 +66,17 @@ def test_bad_arguments_are_rejected_before_any_launch(built_library):
         _lib.check(1, "x")
     with pytest.raises(RuntimeError):
         _lib.check(3, "x")
+
+
+def test_deterministic_switch_and_selftest_arguments(built_library):
+    lib = _lib.load()
+    assert lib.rbf_b200_get_deterministic() == 0
+    assert lib.rbf_b200_set_deterministic(1) == 0 and lib.rbf_b200_get_deterministic() == 1
+    assert lib.rbf_b200_set_deterministic(0) == 1 and lib.rbf_b200_get_deterministic() == 0
+    # the wait self-test validates before it launches
+    assert lib.rbf_b200_selftest_wait_timeout(None, 256, 1000, None) == 3
+    assert lib.rbf_b200_selftest_wait_timeout(0x10000, 64, 1000, None) == 3
+    assert lib.rbf_b200_selftest_wait_timeout(0x10000, 256, 0, None) == 1
+    assert lib.rbf_b200_selftest_wait_timeout(0x10000, 256, 3_000_000_000, None) == 1
+    code = ctypes.c_uint(5)
+    assert lib.rbf_b200_read_device_status(0x10000, None, None) == 1

@@ -144,6 +144,68 @@ def test_two_rank_partition_with_gloo(tmp_path):
         assert p.returncode == 0 and f"ok {r}" in o, o
 
 
+_DP_WORKER = r"""
+import os, sys
+sys.path.insert(0, sys.argv[1])
+import torch, torch.distributed as dist
+import torch.nn.functional as F
+from rbf_attention_b200 import lm
+rank, world = int(sys.argv[3]), 2
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:" + sys.argv[2], rank=rank, world_size=world)
+VOCAB = 211
+def make():
+    torch.manual_seed(0)
+    m = lm.CausalLM(VOCAB, d_model=64, num_layers=2, num_heads=2, max_seq_len=32, pos_emb_type="rope",
+                    num_registers=2, attention_type="rbf_slow")
+    with torch.no_grad():
+        m.register_tokens.normal_(0.0, 0.3)
+    return m
+def loss_of(model, ids):
+    logits, _ = model(ids[:, :-1])
+    return F.cross_entropy(logits.reshape(-1, VOCAB), ids[:, 1:].reshape(-1))
+ids_all = lm.zipf_token_ids(4, 33, VOCAB, seed=1)          # the global batch; every rank takes two sequences
+mine = ids_all[2 * rank: 2 * rank + 2]
+model = make()
+ddp = torch.nn.parallel.DistributedDataParallel(model)
+opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+loss_of(ddp, mine).backward()                              # gradients are averaged over the ranks by the all-reduce
+grads = [p.grad.clone() for p in model.parameters()]
+# (1) both ranks hold the same gradients
+for g in grads:
+    other = [torch.empty_like(g) for _ in range(world)]
+    dist.all_gather(other, g)
+    assert torch.equal(other[0], other[1])
+# (2) they equal the single-process gradients on the concatenated batch (mean over 4 sequences of equal length)
+single = make()
+loss_of(single, ids_all).backward()
+for (name, p), g in zip(single.named_parameters(), grads):
+    assert torch.allclose(p.grad, g, atol=2e-6, rtol=1e-4), (name, (p.grad - g).abs().max().item())
+# (3) after the optimizer step the replicas are still identical
+opt.step()
+for p in model.parameters():
+    other = [torch.empty_like(p.data) for _ in range(world)]
+    dist.all_gather(other, p.data)
+    assert torch.equal(other[0], other[1])
+dist.barrier()
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_two_rank_data_parallel_training_step_with_gloo(tmp_path):
+    """The data-parallel step of the end-to-end configuration on two CPU ranks (materialised-matrix attention, which
+    needs no GPU): gradient all-reduce through DistributedDataParallel, AdamW step (train_rbf_transformer.py:258-349
+    trains one replica; the all-reduce is what the multi-GPU benchmark adds)."""
+    script = tmp_path / "dp_worker.py"
+    script.write_text(_DP_WORKER)
+    port = str(31500 + os.getpid() % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, port, str(r)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"ok {r}" in o, o
+
+
 def test_language_model_matches_reference_fixture(golden_dir):
     """train_rbf_transformer.CausalLM (rbf_slow, 2 register tokens, SuSiE positions): same state-dict keys, logits,
     loss and parameter gradients."""

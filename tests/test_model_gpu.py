@@ -1,0 +1,102 @@
+"""The language model of the end-to-end configuration on the sm_100a kernels, against the reference's
+materialised-matrix attention with the same weights; the same model under ``torch.compile`` (the reference
+compiles its model, train_rbf_transformer.py:280); and the reference's own parity script, unmodified.
+
+Tolerances: bf16 weights and activations through two transformer layers against fp32 math: logits relative L2
+<= 3e-2, loss |diff| <= 2e-2, parameter gradients relative L2 <= 8e-2 (measured values are printed with -s).
+Compiled against eager, both on the kernels: equal up to the non-reproducible fp32 summation order of dQ and
+inductor's fusion of the surrounding elementwise work (relative L2 <= 2e-2 on every gradient).
+"""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import rbf_oracle as oracle
+from rbf_attention_b200 import lm
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+VOCAB = 1000
+
+
+def _models():
+    """Configuration 5 at reduced depth and vocabulary: d_model 512, 8 heads x 64, 4 register tokens, SuSiE
+    positions, 1024 text tokens (attention length 1028, a ragged last tile)."""
+    torch.manual_seed(0)
+    kw = dict(d_model=512, num_layers=2, num_heads=8, max_seq_len=1024, pos_emb_type="rope", num_registers=4)
+    slow = lm.CausalLM(VOCAB, attention_type="rbf_slow", **kw)
+    # zero-initialised register tokens and default parameters give the register rows little to do: perturb them
+    with torch.no_grad():
+        slow.register_tokens.normal_(0.0, 0.3)
+    fast = lm.CausalLM(VOCAB, attention_type="rbf_triton", **kw)
+    fast.load_state_dict(slow.state_dict())
+    return slow, fast.to(DEV, torch.bfloat16)
+
+
+def _loss(model, ids):
+    logits, _ = model(ids[:, :-1])
+    return F.cross_entropy(logits.float().view(-1, VOCAB), ids[:, 1:].reshape(-1)), logits
+
+
+def test_language_model_on_the_kernels_matches_materialised_attention():
+    slow, fast = _models()
+    ids = lm.zipf_token_ids(2, 1025, VOCAB, seed=3)
+    loss_s, logits_s = _loss(slow, ids)
+    loss_s.backward()
+    loss_f, logits_f = _loss(fast, ids.to(DEV))
+    loss_f.backward()
+    rep = oracle.error_report(logits_f.detach().float().cpu(), logits_s.detach())
+    print("logits", rep, "loss", loss_f.item(), loss_s.item())
+    assert rep["rel_l2"] <= 3e-2, rep
+    assert abs(loss_f.item() - loss_s.item()) <= 2e-2
+    names = dict(slow.named_parameters())
+    assert {"register_tokens", "blocks.0.attn.pos_weight", "blocks.0.attn.reg_pos_emb"} <= set(names)
+    for name, pf in fast.named_parameters():
+        assert pf.grad is not None, name
+        rep = oracle.error_report(pf.grad.float().cpu(), names[name].grad)
+        print(name, rep)
+        assert rep["rel_l2"] <= 8e-2, (name, rep)
+
+
+def test_compiled_training_step_equals_the_eager_one():
+    _, eager = _models()
+    _, compiled_src = _models()
+    compiled = torch.compile(compiled_src)
+    ids = lm.zipf_token_ids(2, 1025, VOCAB, seed=5).to(DEV)
+    results = []
+    for model, params in ((eager, eager), (compiled, compiled_src)):
+        opt = torch.optim.AdamW(params.parameters(), lr=1e-3)
+        loss, _ = _loss(model, ids)
+        loss.backward()
+        grads = {n: p.grad.detach().float().clone() for n, p in params.named_parameters()}
+        opt.step()
+        loss2, _ = _loss(model, ids)
+        results.append((loss.item(), loss2.item(), grads))
+    (l0, l0b, g0), (l1, l1b, g1) = results
+    assert abs(l0 - l1) <= 5e-3 and abs(l0b - l1b) <= 2e-2, (l0, l1, l0b, l1b)
+    assert l0b < l0            # the step reduced the loss
+    for name in g0:
+        rep = oracle.error_report(g1[name].cpu(), g0[name].cpu())
+        assert rep["rel_l2"] <= 2e-2, (name, rep)
+
+
+def test_reference_parity_script_runs_unmodified():
+    """baseline/_ref/scripts/test_equivalence.py is a byte copy of the reference's script (placed there by
+    ``__graft_entry__.build()`` where the reference checkout exists; it is not part of this repository). With this
+    repository first on the module path its ``from rbf_attention import ...`` resolves to the drop-in module; the
+    script prints one PASS / FAIL verdict per tensor and implementation, for fp16 and for fp32 inputs."""
+    script = os.path.join(ROOT, "baseline", "_ref", "scripts", "test_equivalence.py")
+    if not os.path.exists(script):
+        pytest.skip("the reference's script is not staged under baseline/_ref/scripts")
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), PYTHONIOENCODING="utf-8")
+    r = subprocess.run([sys.executable, script], capture_output=True, text=True, env=env, timeout=900, cwd=ROOT)
+    print(r.stdout[-3000:], r.stderr[-2000:])
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.count("PASS") == 16 and "FAIL" not in r.stdout, r.stdout

@@ -118,6 +118,113 @@ def test_forward_backward_parity_through_c_abi(B, H, N, D, causal, softmax, dtyp
         assert (lse.cpu() - ref_l).abs().max().item() <= 2e-4 * max(1.0, ref_l.abs().max().item())
 
 
+@pytest.mark.parametrize("causal,softmax", [(True, True), (False, True), (True, False)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_persistent_backward_with_ragged_tiles_and_many_items(causal, softmax, dtype):
+    """B4 H12 N1000 D64: 8 key tiles x 48 pairs = 384 work items for at most 148 resident blocks, so every block of
+    the persistent head-dim-64 backward takes several items in a row, each ending in a ragged tile (1000 = 7 x 128 +
+    104). Three pairs are compared with the oracle."""
+    B, H, N, D = 4, 12, 1000, 64
+    std = 1.0 if softmax else 0.5
+    q, k, v, do = oracle.make_inputs(B, H, N, D, seed=11, dtype=dtype, std=std, key_norm_sigma=0.3 if softmax else 0.0)
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+    out, lse = cabi_forward(qd, kd, vd, causal, softmax)
+    dq, dk, dv = cabi_backward(qd, kd, vd, out, lse, dod, causal, softmax)
+    for t in (out, dq, dk, dv):
+        assert torch.isfinite(t).all()
+    for (b, h) in [(0, 0), (2, 7), (3, 11)]:
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        ref = oracle.torch_forward_backward(q[sl], k[sl], v[sl], do[sl], causal, softmax, dtype=torch.float32)
+        for name, got, want in zip(("O", "dQ", "dK", "dV"), (out, dq, dk, dv), ref):
+            check(f"{name}[{b},{h}]", got[sl].cpu().float(), want, REL_L2[dtype])
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_deterministic_switch_gives_bitwise_reproducible_gradients(D):
+    """rbf_b200_set_deterministic(1): the softmax backward runs as two kernels with a fixed summation order; dQ is
+    then bitwise equal between runs (the single kernel's is not) and still matches the oracle."""
+    lib = _lib.load()
+    q, k, v, do = oracle.make_inputs(2, 2, 700, D, seed=4, dtype=torch.bfloat16, key_norm_sigma=0.3)
+    ref = oracle.torch_forward_backward(q, k, v, do, True, True, dtype=torch.float32)
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+    out, lse = cabi_forward(qd, kd, vd, True, True)
+    assert lib.rbf_b200_set_deterministic(1) == 0
+    try:
+        assert lib.rbf_b200_get_deterministic() == 1
+        g1 = cabi_backward(qd, kd, vd, out, lse, dod, True, True)
+        g2 = cabi_backward(qd, kd, vd, out, lse, dod, True, True)
+    finally:
+        assert lib.rbf_b200_set_deterministic(0) == 1
+    for a, b in zip(g1, g2):
+        assert torch.equal(a, b)
+    for name, got, want in zip(("dQ", "dK", "dV"), g1, ref[1:]):
+        check(name, got.cpu().float(), want, REL_L2[torch.bfloat16])
+    # the operator path follows torch's own switch
+    qa, ka, va = (t.detach().clone().requires_grad_(True) for t in (qd, kd, vd))
+    torch.use_deterministic_algorithms(True)
+    try:
+        ops.run_triton_rbf(qa, ka, va, True).backward(dod)
+    finally:
+        torch.use_deterministic_algorithms(False)
+        lib.rbf_b200_set_deterministic(0)
+    assert torch.equal(qa.grad, g1[0])
+
+
+def test_bounded_wait_runs_out_and_the_workspace_recovers():
+    """A wait that nothing satisfies gives up after its limit, records (site, work unit) in the status word and the
+    kernel returns by itself. A forward main kernel launched on a workspace whose status word is set leaves at once
+    (block by block, through the abort teardown); the next complete call clears the word and is correct."""
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    B, H, N, D = 1, 2, 300, 64
+    q, k, v, do = oracle.make_inputs(B, H, N, D, seed=9, dtype=torch.bfloat16)
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    nbytes = lib.rbf_b200_workspace_bytes(B, H, N, D, 1, 0)
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+    code = ctypes.c_uint(0)
+    assert lib.rbf_b200_selftest_wait_timeout(ws.data_ptr(), nbytes, 200_000, stream) == 0, lib.rbf_b200_last_error()
+    rc = lib.rbf_b200_read_device_status(ws.data_ptr(), stream, ctypes.byref(code))     # synchronises: the kernel is back
+    assert rc == 6 and code.value >> 24 == 250 and code.value & 0xFFFFFF == 0
+    assert b"wait ran out" in lib.rbf_b200_last_error()
+    # main kernel only (no pre-pass, which would clear the word): every block sees the word and leaves
+    out = torch.full((B, H, N, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    lse = torch.full((B, H, N), 7.0, dtype=torch.float32, device=DEV)
+    rc = lib.rbf_b200_fwd_phases(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                 ws.data_ptr(), nbytes, B, H, N, D, _s3(qd), _s3(kd), _s3(vd), _s3(out), 0, 1, 1,
+                                 1.0 / math.sqrt(D), stream, 2)
+    assert rc == 0, lib.rbf_b200_last_error()
+    assert lib.rbf_b200_read_device_status(ws.data_ptr(), stream, ctypes.byref(code)) == 6
+    assert (out == 7.0).all() and (lse == 7.0).all()          # nothing was computed, nothing was written
+    # a complete call on the same workspace clears the status and is correct
+    rc = lib.rbf_b200_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), lse.data_ptr(), ws.data_ptr(),
+                          nbytes, B, H, N, D, _s3(qd), _s3(kd), _s3(vd), _s3(out), 0, 1, 1, 1.0 / math.sqrt(D), stream)
+    assert rc == 0, lib.rbf_b200_last_error()
+    assert lib.rbf_b200_read_device_status(ws.data_ptr(), stream, ctypes.byref(code)) == 0 and code.value == 0
+    ref_o = oracle.torch_forward_backward(q, k, v, do, True, True, dtype=torch.float32)[0]
+    check("O after recovery", out.cpu().float(), ref_o, REL_L2[torch.bfloat16])
+    # the operator path reports a status word it finds set (here: planted in a workspace by hand)
+    mon = ops._monitor(torch.device(DEV))
+    ws[:4] = torch.tensor([1, 0, 0, 250], dtype=torch.uint8, device=DEV)
+    mon.record(ws, "planted")
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        ops.check_device_status()
+    ops.check_device_status()          # reported once
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_second_device_of_one_process():
+    """Kernel attributes are per device: a process that has used cuda:0 must be able to launch on cuda:1."""
+    q, k, v, do = oracle.make_inputs(1, 2, 300, 64, seed=2, dtype=torch.bfloat16)
+    ref = oracle.torch_forward_backward(q, k, v, do, True, True, dtype=torch.float32)
+    for dev in ("cuda:0", "cuda:1"):
+        qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+        out = ops.run_triton_rbf(qd, kd, vd, True)
+        out.backward(do.to(dev))
+        ops.check_device_status(dev)
+        for name, got, want in zip(("O", "dQ", "dK", "dV"), (out, qd.grad, kd.grad, vd.grad), ref):
+            check(f"{name} on {dev}", got.detach().cpu().float(), want, REL_L2[torch.bfloat16])
+
+
 def test_golden_fixture_small(golden_dir):
     """attn_small.npz holds the reference's fp32 results; the kernel sees the same inputs rounded to bf16."""
     g = np.load(os.path.join(golden_dir, "attn_small.npz"))
@@ -236,9 +343,11 @@ def test_full_size_config2_properties():
 
 
 @pytest.mark.parametrize("causal", [True, False])
-def test_full_length_config3_properties(causal):
-    """N = 16384, D = 128 (batch x heads reduced to keep the check short): properties + oracle on one pair."""
-    _properties(1, 4, 16384, 128, causal, 0.0, [(0, 3)] if causal else [])
+def test_full_length_config3_b1_h4_properties(causal):
+    """N = 16384, D = 128, causal and full attention, at B1 H4 instead of the configuration's B2 H32 (every
+    (batch, head) pair is independent; the reduction keeps the check short): properties + the oracle on one pair
+    at the full sequence length in both mask modes."""
+    _properties(1, 4, 16384, 128, causal, 0.0, [(0, 3)])
 
 
 def test_config4_non_softmax_slice_against_oracle():

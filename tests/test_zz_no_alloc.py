@@ -60,6 +60,10 @@ def test_static_scratch_forward_matches_regular_forward_twice_in_a_row():
             pairs.append((q, k, v, torch.empty_like(q), torch.empty(shape[:3], dtype=torch.float32, device=DEV)))
         for q, k, v, out, lse in pairs:
             assert _static(lib, q, k, v, out, lse, causal, softmax) == 0, lib.rbf_b200_last_error()
+        # workspace = NULL names the built-in scratch of the current device: the status word both calls left there
+        code = ctypes.c_uint(1)
+        assert lib.rbf_b200_read_device_status(None, torch.cuda.current_stream().cuda_stream, ctypes.byref(code)) == 0
+        assert code.value == 0
         torch.cuda.synchronize()
         for q, k, v, out, lse in pairs:
             ref_out, ref_lse = _regular(lib, q, k, v, causal, softmax)
