@@ -11,7 +11,13 @@ workload on its own seed (independent batch x head pairs, no collective in the d
 is the sum over ranks divided by the slowest rank's time. One JSON line is printed by rank 0.
 
 ``--workload config5_lm`` runs the data-parallel language-model training step instead (tokens/s; NCCL gradient
-all-reduce through DistributedDataParallel when N > 1).
+all-reduce through DistributedDataParallel when N > 1; ``--compile`` wraps the model in ``torch.compile`` as the
+reference's training script does).
+
+The default line also carries, under ``"also"``, the other benchmark configurations timed with the same event loop
+(configuration 3 causal and full, configuration 4, the reference's own micro-benchmark shape; at N = 1) and the
+language-model step (at every N), and under ``"gpu_baselines"`` the reference's Triton operators and its SDPA
+formulation timed on the same GPU when the reference project is staged under ``baseline/_ref/reference``.
 
 ``--impl reference`` times the reference project's own CPU path (materialised-matrix PyTorch math with
 autograd, restated in oracle/rbf_oracle.py) on the host cores, one (batch, head) pair of the workload per step.
@@ -46,6 +52,25 @@ def flops(w, forward=True, backward=True):
     per = (4.0 if forward else 0.0) + (10.0 if backward else 0.0)
     f = per * w["B"] * w["H"] * float(w["N"]) ** 2 * w["D"]
     return f * 0.5 if w["causal"] else f
+
+
+def config_of(name, w, world):
+    """The ``config`` object of the JSON line; both arms build it here so that they describe the same workload."""
+    return {"workload": name, **{k_: w[k_] for k_ in ("B", "H", "N", "D", "causal", "softmax")},
+            "parallelism": f"bh-shard x{world}, no collective"}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the named kernel, from ncu captures of a reduced batch
+# scaled to the full batch (traffic grows in proportion to B): (read, write) bytes, batch divisor of the capture.
+NCU_DRAM_BYTES = {
+    ("config2", "bwd_fused"): (109.726720e6, 30.068992e6, 4),
+    ("config2", "fwd"): (54.800640e6, 2.691584e6, 4),
+}
+
+
+def ncu_traffic(workload, kernel):
+    rec = NCU_DRAM_BYTES.get((workload, kernel))
+    return None if rec is None else (rec[0] + rec[1]) * rec[2]
 
 
 def measured_peaks():
@@ -160,8 +185,7 @@ def run_reference(args, w, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": args.warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, **{k_: w[k_] for k_ in ("B", "H", "N", "D", "causal", "softmax")},
-                   "timed_on": "host CPU"},
+        "config": config_of(args.workload, w, args.gpus), "timed_on": "host CPU",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -173,20 +197,34 @@ def run_reference(args, w, rank, world):
 # our arm
 # ---------------------------------------------------------------------------------------------
 class DeviceRunner:
-    """Pre-allocated device buffers and raw C-ABI calls (no allocation inside the timed region)."""
+    """Pre-allocated device buffers and raw C-ABI calls (no allocation inside the timed region). ``host=True`` draws
+    the inputs on the CPU (seeded) and keeps pinned copies for the end-to-end leg; ``host=False`` draws them on the
+    device from a seeded generator (the other configurations, which have no end-to-end leg)."""
 
-    def __init__(self, w, device, seed):
+    def __init__(self, w, device, seed, host=True, dtype=None):
         import torch
 
         from rbf_attention_b200 import _lib, synthetic
 
         self.torch, self.w, self.lib = torch, w, _lib.load()
         self._libmod = _lib
+        dtype = dtype or torch.bfloat16
+        self.dtype_code = 0 if dtype == torch.bfloat16 else 1
         B, H, N, D = w["B"], w["H"], w["N"], w["D"]
-        host = synthetic.make_inputs(B, H, N, D, seed=seed, dtype=torch.bfloat16, std=w["std"],
-                                     key_norm_sigma=w["key_norm_sigma"])
-        self.host = [t.pin_memory() for t in host]
-        self.q, self.k, self.v, self.do = (t.to(device) for t in host)
+        if host:
+            tensors = synthetic.make_inputs(B, H, N, D, seed=seed, dtype=dtype, std=w["std"],
+                                            key_norm_sigma=w["key_norm_sigma"])
+            self.host = [t.pin_memory() for t in tensors]
+            self.q, self.k, self.v, self.do = (t.to(device) for t in tensors)
+        else:
+            g = torch.Generator(device=device).manual_seed(seed)
+            self.host = None
+            self.q, self.k, self.v = ((torch.randn(B, H, N, D, device=device, generator=g) * w["std"]).to(dtype)
+                                      for _ in range(3))
+            self.do = torch.randn(B, H, N, D, device=device, generator=g).to(dtype)
+            if w["key_norm_sigma"] > 0:
+                f = torch.exp(torch.randn(B, H, N, 1, device=device, generator=g) * w["key_norm_sigma"])
+                self.k = (self.k.float() * f).to(dtype)
         self.out = torch.empty_like(self.q)
         self.lse = torch.empty((B, H, N), dtype=torch.float32, device=device)
         self.dq, self.dk, self.dv = (torch.empty_like(self.q) for _ in range(3))
@@ -201,8 +239,8 @@ class DeviceRunner:
         w = self.w
         rc = self.lib.rbf_b200_fwd_phases(
             self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.out.data_ptr(), self.lse.data_ptr(),
-            self.ws.data_ptr(), self.ws.numel(), w["B"], w["H"], w["N"], w["D"], self.s, self.s, self.s, self.s, 0,
-            int(w["causal"]), int(w["softmax"]), self.scale, self.stream, phases)
+            self.ws.data_ptr(), self.ws.numel(), w["B"], w["H"], w["N"], w["D"], self.s, self.s, self.s, self.s,
+            self.dtype_code, int(w["causal"]), int(w["softmax"]), self.scale, self.stream, phases)
         self._libmod.check(rc, "rbf_b200_fwd")
 
     def bwd(self, phases=7):
@@ -211,7 +249,7 @@ class DeviceRunner:
             self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.out.data_ptr(), self.lse.data_ptr(),
             self.do.data_ptr(), self.dq.data_ptr(), self.dk.data_ptr(), self.dv.data_ptr(), self.ws.data_ptr(),
             self.ws.numel(), w["B"], w["H"], w["N"], w["D"], self.s, self.s, self.s, self.s, self.s, self.s, self.s,
-            self.s, 0, int(w["causal"]), int(w["softmax"]), self.scale, self.stream, phases)
+            self.s, self.dtype_code, int(w["causal"]), int(w["softmax"]), self.scale, self.stream, phases)
         self._libmod.check(rc, "rbf_b200_bwd")
 
     def step(self):
@@ -235,6 +273,190 @@ def time_loop(torch, fn, steps):
     return e0.elapsed_time(e1) / steps
 
 
+# Kernel launches of one step: forward = (pre-pass) + main; backward = pre-pass + single kernel + dQ conversion.
+LAUNCHES_PER_STEP = 5
+# Algorithmic GEMMs per launch of the two main kernels: forward S and PV; the single-kernel backward all five.
+GEMMS = {"fwd": 2, "bwd_fused": 5}
+
+
+def timed_workload(torch, runner, w, steps, warmup, local_rank):
+    """Warm-up, then the whole step and its phases with CUDA events. Returns (ms per step, phase times, clocks)."""
+    for _ in range(max(warmup, 3)):
+        runner.step()
+    runner.check_status()
+    with ClockSampler(local_rank) as clocks:
+        ms = time_loop(torch, runner.step, steps)
+        phase_ms = {"fwd": time_loop(torch, lambda: runner.fwd(2), steps),
+                    "bwd_fused": time_loop(torch, lambda: runner.bwd(2), steps),
+                    "prepass": time_loop(torch, lambda: (runner.fwd(1), runner.bwd(1)), steps)}
+    runner.check_status()
+    return ms, phase_ms, clocks.summary()
+
+
+def roofline_of(workload, w, phase_ms, peak, peak_src):
+    dom = max(GEMMS, key=lambda n: phase_ms[n])
+    unit_flops = 2.0 * w["B"] * w["H"] * float(w["N"]) ** 2 * w["D"] * (0.5 if w["causal"] else 1.0)
+    achieved = GEMMS[dom] * unit_flops / (phase_ms[dom] * 1e-3) / 1e12
+    return {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak, "traffic": ncu_traffic(workload, dom),
+            "traffic_unit": "bytes per launch (ncu capture of a reduced batch, scaled to the full batch)",
+            "peak_source": peak_src, "algorithmic_gemms_per_launch": GEMMS[dom]}
+
+
+def also_attention(torch, device, local_rank, peak, peak_src, steps):
+    """The other attention configurations, device-resident, each with its own clock record."""
+    out = {}
+    for name in ("config3", "config3_full", "config4"):
+        w = dict(WORKLOADS[name])
+        try:
+            runner = DeviceRunner(w, device, seed=2000, host=False)
+            ms, phase_ms, clocks = timed_workload(torch, runner, w, steps, 3, local_rank)
+            value = flops(w) / (ms * 1e-3) / 1e12
+            out[name] = {"value": value, "unit": UNIT, "ms_per_step": ms, "steps": steps, "phase_ms": phase_ms,
+                         "frac_of_peak": value / peak, "roofline": roofline_of(name, w, phase_ms, peak, peak_src),
+                         "clocks": clocks, "config": config_of(name, w, 1)}
+            del runner
+        except Exception as exc:   # the headline must survive a failure here
+            out[name] = {"error": repr(exc)[:300]}
+        torch.cuda.empty_cache()
+    # The reference's own micro-benchmark shape (its rbf_attention.py: B4 H8 D64 fp16 causal, N = 1024 ... 8192),
+    # forward and backward milliseconds like its plots: backward = (forward + backward) - forward.
+    shape = {}
+    for n in (1024, 2048, 4096, 8192):
+        w = dict(B=4, H=8, N=n, D=64, causal=True, softmax=True, std=1.0, key_norm_sigma=0.0)
+        try:
+            runner = DeviceRunner(w, device, seed=3000 + n, host=False, dtype=torch.float16)
+            for _ in range(5):
+                runner.step()
+            fwd = time_loop(torch, runner.fwd, 20)
+            both = time_loop(torch, runner.step, 20)
+            runner.check_status()
+            shape[str(n)] = {"fwd_ms": fwd, "bwd_ms": both - fwd, "tflops": flops(w) / (both * 1e-3) / 1e12}
+            del runner
+        except Exception as exc:
+            shape[str(n)] = {"error": repr(exc)[:300]}
+    out["reference_benchmark_shape"] = {"dtype": "fp16", "B": 4, "H": 8, "D": 64, "causal": True, "by_N": shape}
+    torch.cuda.empty_cache()
+    return out
+
+
+def gpu_baselines(torch, w, runner, steps=10):
+    """The reference project's own GPU implementations on this GPU and workload, for comparison only: its Triton
+    operators (JIT-compiled and autotuned here by the installed Triton) and its SDPA formulation on an augmented
+    head dim. Needs the reference staged under baseline/_ref/reference; the first call pays JIT and autotuning."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref", "reference")
+    if not os.path.exists(os.path.join(ref_dir, "rbf_attention.py")):
+        return {"unavailable": "the reference project is not staged under baseline/_ref/reference"}
+    import importlib.util
+    import types
+
+    for name in ("matplotlib", "matplotlib.pyplot"):       # the reference imports it for its plots; not installed
+        sys.modules.setdefault(name, types.ModuleType(name))
+    try:
+        spec = importlib.util.spec_from_file_location("rbf_attention_reference", os.path.join(ref_dir, "rbf_attention.py"))
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+    except Exception as exc:
+        return {"unavailable": f"import of the reference failed: {exc!r}"[:300]}
+    q, k, v = (t.detach().clone().requires_grad_(True) for t in (runner.q, runner.k, runner.v))
+    arms = {"triton_reference": (ref.run_triton_rbf if w["softmax"] else ref.run_triton_non_softmax_rbf)}
+    if w["softmax"]:
+        arms["sdpa_augmented"] = ref.rbf_math_forward
+    out = {}
+    for name, fn in arms.items():
+        def step():
+            o = fn(q, k, v, w["causal"])
+            o.backward(runner.do)
+            q.grad = k.grad = v.grad = None
+
+        try:
+            t0 = time.perf_counter()
+            step()
+            torch.cuda.synchronize()
+            first = time.perf_counter() - t0
+            for _ in range(3):
+                step()
+            with torch.no_grad():
+                fwd = time_loop(torch, lambda: fn(q, k, v, w["causal"]), steps)
+            ms = time_loop(torch, step, steps)
+            out[name] = {"value": flops(w) / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "fwd_ms": fwd,
+                         "first_call_s": first}
+        except Exception as exc:
+            out[name] = {"unavailable": repr(exc)[:300]}
+    return out
+
+
+def e2e_leg(torch, dist, runner, w, device, world, steps):
+    """End to end through the public operator with host buffers. Three streams, double-buffered device inputs: the
+    host->device copy of step s+1, the kernels of step s and the device->host copy of step s-1 overlap (PCIe is full
+    duplex). Every step moves all of its inputs and all of its results across the bus inside the timed region.
+    Returns (ms per step, ms per step of the same loop with the kernels left out = the copy floor)."""
+    from rbf_attention_b200 import ops
+
+    fn = ops.run_triton_rbf if w["softmax"] else ops.run_triton_non_softmax_rbf
+    hq, hk, hv, hdo = runner.host
+    outs_host = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    s_main = torch.cuda.current_stream(device)
+    dev_in = [[torch.empty_like(runner.q) for _ in range(4)] for _ in range(2)]
+    dev_out = [torch.empty_like(runner.q) for _ in range(4)]          # stand-in results of the copy-only loop
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    keep = [None, None]
+    counter = [0]
+
+    def step(compute=True):
+        i = counter[0] & 1
+        counter[0] += 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(in_free[i])            # kernels of the step that last used this buffer set are done
+            for dst, src in zip(dev_in[i], (hq, hk, hv, hdo)):
+                dst.copy_(src, non_blocking=True)
+            in_ready[i].record(s_in)
+        s_main.wait_event(in_ready[i])
+        if compute:
+            q, k, v = (t_.detach().requires_grad_(True) for t_ in dev_in[i][:3])
+            out = fn(q, k, v, w["causal"])
+            out.backward(dev_in[i][3])
+            results = (out.detach(), q.grad, k.grad, v.grad)
+        else:
+            results = tuple(dev_out)
+        in_free[i].record(s_main)
+        keep[i] = results                           # keep the tensors alive until their copy has run
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(in_free[i])
+            s_out.wait_event(out_done[i ^ 1])       # one device->host copy at a time into the pinned result buffers
+            for dst, src in zip(outs_host, results):
+                dst.copy_(src, non_blocking=True)
+                src.record_stream(s_out)
+            out_done[i].record(s_out)
+        s_main.wait_event(out_done[i ^ 1])          # the timed stream ends only after the previous step's read-back
+
+    def flush():
+        s_main.wait_event(out_done[(counter[0] - 1) & 1])
+
+    def timed(compute):
+        for ev in in_free + out_done:
+            ev.record(s_main)
+        for _ in range(2):
+            step(compute)
+        flush()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            step(compute)
+        flush()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    return timed(True), timed(False)
+
+
 def run_ours(args, w, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -246,143 +468,80 @@ def run_ours(args, w, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    runner = DeviceRunner(w, device, seed=1000 + rank)
-    for _ in range(max(args.warmup, 3)):
-        runner.step()
-    runner.check_status()
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(values):
+        t = torch.tensor(values, device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    peak, peak_src = measured_peaks()
+    runner = DeviceRunner(w, device, seed=1000 + rank)
+    for _ in range(max(args.warmup, 3)):
+        runner.step()
+    runner.check_status()
+
     # ---- device-resident throughput: exactly K steps, max over ranks --------------------------
     barrier()
-    with ClockSampler(local_rank) as clocks:
-        ms = time_loop(torch, runner.step, args.steps)
-        # per-kernel times for the roofline line (same buffers, same stream)
-        fused = True                             # single-kernel backward (plus the dQ conversion kernel)
-        phase_ms = {"fwd": time_loop(torch, lambda: runner.fwd(2), args.steps)}
-        if fused:
-            phase_ms["bwd_fused"] = time_loop(torch, lambda: runner.bwd(2), args.steps)
-        else:
-            phase_ms["bwd_dkdv"] = time_loop(torch, lambda: runner.bwd(2), args.steps)
-            phase_ms["bwd_dq"] = time_loop(torch, lambda: runner.bwd(4), args.steps)
-        phase_ms["prepass"] = time_loop(torch, lambda: (runner.fwd(1), runner.bwd(1)), args.steps)
+    ms, phase_ms, clocks = timed_workload(torch, runner, w, args.steps, 0, local_rank)
     barrier()
-    runner.check_status()
-    t = torch.tensor([ms], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = t.item()
+    (ms_max,) = max_over_ranks([ms])
     total_flops = flops(w) * world
     value = total_flops / (ms_max * 1e-3) / 1e12
 
     # ---- end to end through the public operator with host buffers -----------------------------
-    from rbf_attention_b200 import ops
-
-    fn = ops.run_triton_rbf if w["softmax"] else ops.run_triton_non_softmax_rbf
-    hq, hk, hv, hdo = runner.host
-    outs_host = [torch.empty_like(hq).pin_memory() for _ in range(4)]
-
-    # Three streams, double-buffered device inputs: the host->device copy of step s+1, the kernels of step s and the
-    # device->host copy of step s-1 overlap (PCIe is full duplex). Every step still moves all of its inputs and all
-    # of its results across the bus inside the timed region.
-    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
-    s_main = torch.cuda.current_stream(device)
-    dev_in = [[torch.empty_like(runner.q) for _ in range(4)] for _ in range(2)]
-    in_ready = [torch.cuda.Event() for _ in range(2)]
-    in_free = [torch.cuda.Event() for _ in range(2)]
-    out_done = [torch.cuda.Event() for _ in range(2)]
-    keep = [None, None]
-    counter = [0]
-
-    def e2e_step():
-        i = counter[0] & 1
-        counter[0] += 1
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(in_free[i])            # kernels of the step that last used this buffer set are done
-            for dst, src in zip(dev_in[i], (hq, hk, hv, hdo)):
-                dst.copy_(src, non_blocking=True)
-            in_ready[i].record(s_in)
-        s_main.wait_event(in_ready[i])
-        q, k, v = (t_.detach().requires_grad_(True) for t_ in dev_in[i][:3])
-        out = fn(q, k, v, w["causal"])
-        out.backward(dev_in[i][3])
-        in_free[i].record(s_main)
-        results = (out.detach(), q.grad, k.grad, v.grad)
-        keep[i] = results                           # keep the tensors alive until their copy has run
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(in_free[i])
-            s_out.wait_event(out_done[i ^ 1])       # one device->host copy at a time into the pinned result buffers
-            for dst, src in zip(outs_host, results):
-                dst.copy_(src, non_blocking=True)
-                src.record_stream(s_out)
-            out_done[i].record(s_out)
-        s_main.wait_event(out_done[i ^ 1])          # the timed stream ends only after the previous step's read-back
-
-    def e2e_flush():
-        s_main.wait_event(out_done[(counter[0] - 1) & 1])
-
-    for ev in in_free + out_done:
-        ev.record(s_main)
     e2e_steps = max(2, min(args.steps, 10))
-    for _ in range(2):
-        e2e_step()
-    e2e_flush()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2e_flush()
-    e1.record()
-    torch.cuda.synchronize()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = total_flops / (t.item() * 1e-3) / 1e12
-    tensor_bytes = hq.numel() * hq.element_size()
+    e2e_ms, floor_ms = max_over_ranks(list(e2e_leg(torch, dist, runner, w, device, world, e2e_steps)))
+    tensor_bytes = runner.q.numel() * runner.q.element_size()
+
+    # ---- the other configurations ---------------------------------------------------------------
+    also = {}
+    baselines = None
+    if args.also and args.workload == "config2":
+        if world == 1:
+            baselines = gpu_baselines(torch, w, runner)
+        del runner
+        torch.cuda.empty_cache()
+        if world == 1:
+            also.update(also_attention(torch, device, local_rank, peak, peak_src, max(10, min(args.steps, 20))))
+        barrier()
+        try:
+            also["config5_lm"] = lm_step_record(torch, dist, rank, world, local_rank, steps=8, warmup=3, compile_model=False)
+        except Exception as exc:
+            also["config5_lm"] = {"error": repr(exc)[:300]}
 
     if rank == 0:
-        peak, peak_src = measured_peaks()
-        # dominant kernel: algorithmic GEMMs per launch - forward 2 (S, PV); dK/dV kernel 4 (S, dP, dV, dK);
-        # dQ kernel 1 (dQ; its S and dP are recomputation and are not counted)
-        # single-kernel backward: all 5
-        gemms = {"fwd": 2, "bwd_fused": 5} if fused else {"fwd": 2, "bwd_dkdv": 4, "bwd_dq": 1}
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture of a quarter of the batch
-        # (profiles/ncu_full_fwd_bwd_fused_config2_quarter.md), times four: traffic grows in proportion to B
-        ncu_traffic = {("config2", "bwd_fused"): 4 * (109.726720e6 + 30.068992e6),
-                       ("config2", "fwd"): 4 * (54.800640e6 + 2.691584e6)}
-        dom = max(gemms, key=lambda n: phase_ms[n])
-        unit_flops = 2.0 * w["B"] * w["H"] * float(w["N"]) ** 2 * w["D"] * (0.5 if w["causal"] else 1.0)
-        achieved = gemms[dom] * unit_flops / (phase_ms[dom] * 1e-3) / 1e12
         cpu_tf, cores, pairs, pair_s = cpu_pairs_per_second(w)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, **{k_: w[k_] for k_ in ("B", "H", "N", "D", "causal", "softmax")},
-                       "per_gpu_batch_heads": w["B"] * w["H"], "parallelism": f"bh-shard x{world}, no collective",
-                       "l2": "inputs+outputs per step (>= 0.5 GB) exceed the 126 MB L2",
-                       "tolerance": "bf16 operands, fp32 accumulate; rel-L2 <= 6e-3 vs fp32 oracle (tests/)"},
+            "config": config_of(args.workload, w, world),
+            "per_gpu_batch_heads": w["B"] * w["H"],
+            "l2": "inputs+outputs per step (>= 0.5 GB) exceed the 126 MB L2",
+            "tolerance": "bf16 operands, fp32 accumulate; rel-L2 <= 6e-3 vs fp32 oracle (tests/)",
             "frac_of_peak": value / world / peak,
             "phase_ms": phase_ms,
-            "roofline": {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": ncu_traffic.get((args.workload, dom)),
-                         "traffic_unit": "bytes per launch (ncu, quarter batch x 4)", "peak_source": peak_src,
-                         "algorithmic_gemms_per_launch": gemms[dom]},
+            "roofline": roofline_of(args.workload, w, phase_ms, peak, peak_src),
             "cpu_baseline": {"value": cpu_tf, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"{pairs} x one (batch, head) pair at full N (fp32 PyTorch CPU math, "
                                        f"{pair_s:.2f} s per pair), scaled by FLOPs"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 4 * tensor_bytes,
-                    "d2h_bytes_per_step": 4 * tensor_bytes, "ms_per_step": t.item(), "steps": e2e_steps},
-            # per step: forward = pre-pass + main; backward = pre-pass + (single kernel + dQ convert | dK/dV + dQ)
-            "gpu_launches": 5 * args.steps,
-            "clocks": clocks.summary(),
+            "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+                    "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    # the same three-stream loop with the kernels left out: what the host link alone costs per step
+                    "copy_floor_ms": floor_ms},
+            "gpu_launches": LAUNCHES_PER_STEP * args.steps,
+            "clocks": clocks,
         }
+        if also:
+            line["also"] = also
+        if baselines is not None:
+            line["gpu_baselines"] = baselines
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -395,7 +554,7 @@ def run_profile_case(args, w):
 
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    runner = DeviceRunner(w, device, seed=1000)
+    runner = DeviceRunner(w, device, seed=1000, host=False)
     for _ in range(args.warmup):
         runner.step()
     ms = time_loop(torch, runner.step, args.steps)
@@ -419,6 +578,13 @@ def lm_model(attention_type, dtype, device):
     model = lm.CausalLM(LM["vocab"], LM["d_model"], LM["layers"], LM["heads"], max_seq_len=LM["seq"],
                         pos_emb_type="rope", num_registers=LM["registers"], attention_type=attention_type)
     return model.to(device=device, dtype=dtype)
+
+
+def lm_config(world, compile_model):
+    return {"workload": "config5_lm", "model": f"CausalLM {LM['layers']}x{LM['d_model']}, {LM['heads']} heads x 64, "
+            f"MLP 4x, {LM['registers']} register tokens, SuSiE, vocab {LM['vocab']}", "global_batch": LM["batch"] * world,
+            "seq_len": LM["seq"], "parallelism": f"dp{world}", "optimizer": "AdamW (fused), bf16 weights",
+            "torch_compile": bool(compile_model)}
 
 
 def lm_cpu_tokens_per_second(steps=1, batch=1, seq=256):
@@ -449,35 +615,18 @@ def lm_cpu_tokens_per_second(steps=1, batch=1, seq=256):
     return batch * seq * steps / dt, threads, f"{batch} sequence(s) of {seq} tokens per step, fp32, rbf_slow attention, AdamW"
 
 
-def run_lm(args, rank, world, local_rank):
-    import torch
-    import torch.distributed as dist
-
+def lm_step_record(torch, dist, rank, world, local_rank, steps, warmup, compile_model):
+    """Times the data-parallel training step (the process group, if any, is already initialised). Returns the record
+    on every rank (times are the maximum over ranks)."""
     from rbf_attention_b200 import lm
 
-    cfg = {"workload": "config5_lm", "model": f"CausalLM {LM['layers']}x{LM['d_model']}, {LM['heads']} heads x 64, "
-           f"MLP 4x, {LM['registers']} register tokens, SuSiE, vocab {LM['vocab']}", "global_batch": LM["batch"] * world,
-           "seq_len": LM["seq"], "parallelism": f"dp{world}", "optimizer": "AdamW (fused), bf16 weights"}
-    if args.impl == "reference":
-        if rank != 0:
-            return
-        tps, threads, sample = lm_cpu_tokens_per_second(steps=max(1, min(args.steps, 3)))
-        print(json.dumps({
-            "impl": "reference", "metric": LM_METRIC, "value": tps, "unit": LM_UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg,
-            "cpu_baseline": {"value": tps, "unit": LM_UNIT, "cores": threads, "kind": "port", "sample": sample},
-            "e2e": {"value": tps, "unit": LM_UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}), flush=True)
-        return
-
     device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
     model = lm_model("rbf_triton", torch.bfloat16, device)
-    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True) \
-        if world > 1 else model
+    net = model
+    if world > 1:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True)
+    if compile_model:
+        net = torch.compile(net)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True)
     ids_host = lm.zipf_token_ids(LM["batch"], LM["seq"] + 1, LM["vocab"], seed=100 + rank).pin_memory()
     ids_dev = ids_host.to(device)
@@ -496,44 +645,71 @@ def run_lm(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step(ids_dev)
     barrier()
     with ClockSampler(local_rank) as clocks:
-        ms = time_loop(torch, lambda: step(ids_dev), args.steps)
+        ms = time_loop(torch, lambda: step(ids_dev), steps)
     barrier()
 
     def e2e_step():
         ids = ids_host.to(device, non_blocking=True)
         loss_host.copy_(step(ids).detach(), non_blocking=True)
 
-    e2e_steps = max(2, min(args.steps, 10))
+    e2e_steps = max(2, min(steps, 10))
     e2e_step()
     barrier()
     e2e_ms = time_loop(torch, e2e_step, e2e_steps)
     t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
     tokens = LM["batch"] * LM["seq"] * world
-    if rank == 0:
-        peak, peak_src = measured_peaks()
-        n_params = sum(p.numel() for p in model.parameters())
-        dense = 6.0 * (n_params - LM["vocab"] * LM["d_model"]) * LM["batch"] * LM["seq"]     # embedding lookup is free
-        n_attn = LM["seq"] + LM["registers"]
-        attn = LM["layers"] * 14.0 * LM["batch"] * LM["heads"] * n_attn * n_attn * 64 * 0.5
-        achieved = (dense + attn) / (t[0].item() * 1e-3) / 1e12
-        cpu_tps, cores, sample = lm_cpu_tokens_per_second()
+    peak, peak_src = measured_peaks()
+    n_params = sum(p.numel() for p in model.parameters())
+    dense = 6.0 * (n_params - LM["vocab"] * LM["d_model"]) * LM["batch"] * LM["seq"]     # embedding lookup is free
+    n_attn = LM["seq"] + LM["registers"]
+    attn = LM["layers"] * 14.0 * LM["batch"] * LM["heads"] * n_attn * n_attn * 64 * 0.5
+    achieved = (dense + attn) / (ms * 1e-3) / 1e12          # per GPU
+    return {
+        "metric": LM_METRIC, "value": tokens / (ms * 1e-3), "unit": LM_UNIT, "n_gpus": world, "steps": steps,
+        "warmup": max(warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": lm_config(world, compile_model),
+        "roofline": {"bound": "tensor", "kernel": "whole step (cuBLAS GEMMs dominate; attention is ~9 % of the FLOPs)",
+                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": LM_UNIT, "h2d_bytes_per_step": ids_host.numel() * 8,
+                "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
+        "gpu_launches": LM["layers"] * LAUNCHES_PER_STEP * steps, "clocks": clocks.summary()}
+
+
+def run_lm(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        tps, threads, sample = lm_cpu_tokens_per_second(steps=max(1, min(args.steps, 3)))
         print(json.dumps({
-            "metric": LM_METRIC, "value": tokens / (t[0].item() * 1e-3), "unit": LM_UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t[0].item(), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
-            "roofline": {"bound": "tensor", "kernel": "whole step (cuBLAS GEMMs dominate; attention is ~9 % of the FLOPs)",
-                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                         "peak_source": peak_src},
-            "cpu_baseline": {"value": cpu_tps, "unit": LM_UNIT, "cores": cores, "kind": "port", "sample": sample},
-            "e2e": {"value": tokens / (t[1].item() * 1e-3), "unit": LM_UNIT,
-                    "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": 4, "ms_per_step": t[1].item()},
-            "gpu_launches": LM["layers"] * 5 * args.steps, "clocks": clocks.summary()}), flush=True)
+            "impl": "reference", "metric": LM_METRIC, "value": tps, "unit": LM_UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": lm_config(args.gpus, args.compile),
+            "cpu_baseline": {"value": tps, "unit": LM_UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": LM_UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}), flush=True)
+        return
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    rec = lm_step_record(torch, dist, rank, world, local_rank, args.steps, args.warmup, args.compile)
+    if rank == 0:
+        cpu_tps, cores, sample = lm_cpu_tokens_per_second()
+        rec["cpu_baseline"] = {"value": cpu_tps, "unit": LM_UNIT, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(rec), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -546,19 +722,21 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="config2", choices=sorted(WORKLOADS) + ["config5_lm"])
+    ap.add_argument("--compile", action="store_true", help="config5_lm: wrap the model in torch.compile")
+    ap.add_argument("--no-also", dest="also", action="store_false",
+                    help="headline workload only: skip the other configurations and the GPU comparison arms")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profilers: a quarter of the workload's batch, kernels only, no JSON line")
     args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload == "config5_lm":
-        return run_lm(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
-                      int(os.environ.get("LOCAL_RANK", "0")))
+        return run_lm(args, rank, world, local_rank)
     w = dict(WORKLOADS[args.workload])
     if args.profile_case:
         w["B"] = max(1, w["B"] // 4)
         return run_profile_case(args, w)
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, w, rank, world)
     else:

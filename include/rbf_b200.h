@@ -125,6 +125,33 @@ int rbf_b200_fwd_static(const void* q, const void* k, const void* v, void* out, 
                         const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                         const int64_t* o_strides, int dtype, int causal, int softmax, float sm_scale, void* stream);
 
+/* Fused preparation of the attention block's operands. Replaces the torch ops between the fused projection and the
+ * attention call in CustomCausalAttention.forward (rbf_attention.py:1659-1688; parameters :1642-1654): it reads the
+ * projection output `qkv` (B, S, 3, H, D contiguous: the reference's "b s (qkv h n)" layout), adds to q and k the
+ * SuSiE position term `susie_table[t, :] * [w_h | w_h]` on the text rows (w_h = row h of `pos_weight`, (H, D/2); t
+ * counts text rows, which follow the R register rows) and row (h, r) of `reg_pos_emb` (H, R, D) on the register rows,
+ * and writes q', k' as (B, H, S, D) tensors through `q_strides`, `k_strides` (v needs nothing: pass the v part of
+ * `qkv` to the forward as a strided view). In the same pass it fills `fwd_workspace` (rbf_b200_workspace_bytes(...,
+ * backward = 0) bytes) with what the forward's pre-pass would compute from k' (and q' when softmax = 0) and clears its
+ * status word, so that the forward that follows runs as rbf_b200_fwd_phases(..., RBF_B200_PHASE_MAIN) alone.
+ * `params_fp32` != 0: the two parameter arrays are fp32 (autocast training); otherwise they have type `dtype`.
+ * `susie_table` is fp32, (at least S - R, D), [sin | cos] as rbf_attention.py:1539-1544 builds it. */
+int rbf_b200_qkv_prep(const void* qkv, const void* pos_weight, const void* reg_pos_emb, int params_fp32,
+                      const float* susie_table, void* q_out, void* k_out, const int64_t* q_strides,
+                      const int64_t* k_strides, void* fwd_workspace, size_t fwd_workspace_bytes, int B, int S, int H,
+                      int D, int R, int dtype, int softmax, float sm_scale, void* stream);
+
+/* Gradients of the block's position parameters from dq', dk' (the attention backward's dq, dk; (B, H, S, D) through
+ * strides): d_pos_weight (H, D/2) and d_reg_pos_emb (H, R, D), both fp32, summed in a fixed order (bitwise
+ * reproducible). Replaces what autograd derives from rbf_attention.py:1667-1688 (broadcast sums over batch and
+ * sequence). The gradient of the fused projection output is dq', dk', dv themselves: let the attention backward
+ * write them into one (B, S, 3, H, D) buffer through its output strides. `workspace`: at least
+ * rbf_b200_qkv_prep_bwd_workspace_bytes() bytes, 256-byte aligned. */
+size_t rbf_b200_qkv_prep_bwd_workspace_bytes(int B, int S, int H, int D, int R);
+int rbf_b200_qkv_prep_bwd(const void* dq, const void* dk, const int64_t* dq_strides, const int64_t* dk_strides,
+                          const float* susie_table, float* d_pos_weight, float* d_reg_pos_emb, void* workspace,
+                          size_t workspace_bytes, int B, int S, int H, int D, int R, int dtype, void* stream);
+
 /* Synchronises `stream` and reads the device status word that the last call using `workspace` left:
  * 0 = ok, otherwise (site << 24 | work unit) of the bounded wait that ran out; the work unit is the linear block
  * index of the launch or, for the persistent backward kernel, the (key tile, batch-head) item. Returns

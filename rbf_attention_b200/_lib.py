@@ -60,6 +60,17 @@ SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint)],
     ),
+    "rbf_b200_qkv_prep": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 3 + [ctypes.c_int] + [ctypes.c_void_p] * 3 + [_c_i64p] * 2 + [ctypes.c_void_p, ctypes.c_size_t]
+        + [ctypes.c_int] * 7 + [ctypes.c_float, ctypes.c_void_p],
+    ),
+    "rbf_b200_qkv_prep_bwd_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int] * 5),
+    "rbf_b200_qkv_prep_bwd": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 2 + [_c_i64p] * 2 + [ctypes.c_void_p] * 4 + [ctypes.c_size_t] + [ctypes.c_int] * 6
+        + [ctypes.c_void_p],
+    ),
     "rbf_b200_set_deterministic": (ctypes.c_int, [ctypes.c_int]),
     "rbf_b200_get_deterministic": (ctypes.c_int, []),
     "rbf_b200_selftest_wait_timeout": (

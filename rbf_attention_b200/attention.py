@@ -26,7 +26,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .ops import run_triton_non_softmax_rbf, run_triton_rbf
+from .ops import run_triton_non_softmax_rbf, run_triton_rbf, susie_block_attention
 
 __all__ = [
     "CustomCausalAttention",
@@ -194,9 +194,39 @@ class CustomCausalAttention(nn.Module):
         return torch.cat([q[:, :, :r], q_text], dim=2), torch.cat([k[:, :, :r], k_text], dim=2)
 
     # -- forward ---------------------------------------------------------------------------------
+    def _susie_table_f32(self) -> torch.Tensor:
+        """The position table as the block operator reads it (fp32, on the buffer's device), converted once: the
+        values are those of the buffer in its current dtype, as in the operator-by-operator path."""
+        src = self.susie_cache
+        key = (src.data_ptr(), src.dtype, src.device)
+        cached = getattr(self, "_table_f32", None)
+        if cached is None or cached[0] != key:
+            cached = (key, src.detach().float().contiguous())
+            self._table_f32 = cached
+        return cached[1]
+
+    def _fused_block(self, qkv: torch.Tensor) -> bool:
+        """Whether the RBF branch runs as the single block operator (position terms, key norms and attention fused,
+        projection layouts read and written in place); everything else takes the operator-by-operator path."""
+        return (
+            self.attention_type in ("rbf_triton", "rbf_flex", "rbf_non_softmax")
+            and self.positional_encoding_type == "susie"
+            and not self.use_qk_norm
+            and not self.apply_xsa
+            and qkv.is_cuda
+            and qkv.dtype in (torch.bfloat16, torch.float16)
+            and self.head_dim in (64, 128)
+        )
+
     def forward(self, x):
         bsz, seq_len, emb = x.shape
-        qkv = self.qkv_proj(x).view(bsz, seq_len, 3, self.num_heads, self.head_dim)
+        qkv = self.qkv_proj(x)
+        if self._fused_block(qkv):
+            reg = self.reg_pos_emb.squeeze(0) if self.num_registers > 0 else None
+            out = susie_block_attention(qkv, self.pos_weight.view(self.num_heads, -1), reg, self._susie_table_f32(),
+                                        self.num_heads, softmax=self.attention_type != "rbf_non_softmax")
+            return self.proj(out), None
+        qkv = qkv.view(bsz, seq_len, 3, self.num_heads, self.head_dim)
         q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)      # each (B, H, S, D), views of the fused buffer
 
         if self.use_qk_norm:

@@ -396,6 +396,76 @@ int rbf_b200_fwd_static(const void* q, const void* k, const void* v, void* out, 
                              v_strides, o_strides, dtype, causal, softmax, sm_scale, stream_v, RBF_B200_PHASE_ALL);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fused q/k preparation of the attention block and the gradients of its position parameters
+// ---------------------------------------------------------------------------------------------
+int rbf_b200_qkv_prep(const void* qkv, const void* pos_weight, const void* reg_pos_emb, int params_fp32,
+                      const float* susie_table, void* q_out, void* k_out, const int64_t* q_strides,
+                      const int64_t* k_strides, void* fwd_workspace, size_t fwd_workspace_bytes, int B, int S, int H,
+                      int D, int R, int dtype, int softmax, float sm_scale, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_common(B, H, S, D, dtype, sm_scale))) return rc;
+  if (R < 0 || R > S) return fail(RBF_B200_ERR_BAD_ARGUMENT, "register rows R = %d must be in [0, S = %d]", R, S);
+  if (qkv == nullptr || pos_weight == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "qkv or pos_weight is NULL");
+  if (R > 0 && reg_pos_emb == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "reg_pos_emb is NULL with R = %d", R);
+  if (S > R && susie_table == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "susie_table is NULL");
+  if (reinterpret_cast<uintptr_t>(qkv) % 16 != 0 || reinterpret_cast<uintptr_t>(susie_table) % 16 != 0)
+    return fail(RBF_B200_ERR_BAD_LAYOUT, "qkv and susie_table must be 16-byte aligned");
+  if ((rc = check_tensor("q_out", q_out, q_strides, B, H, S, D))) return rc;
+  if ((rc = check_tensor("k_out", k_out, k_strides, B, H, S, D))) return rc;
+  if (fwd_workspace == nullptr || reinterpret_cast<uintptr_t>(fwd_workspace) % 256 != 0)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL or not 256-byte aligned");
+  const Workspace ws = carve(fwd_workspace, B, H, S, D, softmax, 0);
+  if (fwd_workspace_bytes < ws.bytes)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", fwd_workspace_bytes, ws.bytes);
+  const bool bf16 = dtype == 0;
+  const float c = sm_scale * rbf::kLog2e;
+  rbf::QkvPrepArgs a{};
+  a.qkv = qkv; a.pos_weight = pos_weight; a.reg_pos = reg_pos_emb; a.params_fp32 = params_fp32 ? 1 : 0;
+  a.table = susie_table; a.q_out = q_out; a.k_out = k_out;
+  set_strides(a.qo, q_strides); set_strides(a.ko, k_strides);
+  a.kslab_out = ws.kslab; a.qsq_out = softmax ? nullptr : ws.row_bias; a.status_to_clear = ws.status;
+  a.B = B; a.S = S; a.H = H; a.D = D; a.R = R; a.n_pad = rbf::padded_rows(S);
+  a.scale = c; a.scale2 = 2.f * c; a.slab_w = slab_w(bf16); a.slab_big = slab_big(bf16);
+  const cudaError_t e = rbf::launch_qkv_prep(a, bf16, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "q/k preparation launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+size_t rbf_b200_qkv_prep_bwd_workspace_bytes(int B, int S, int H, int D, int R) {
+  if (B <= 0 || S <= 0 || H <= 0 || D <= 0 || R < 0 || R > S) return 0;
+  const size_t chunks = static_cast<size_t>(rbf::qkv_prep_bwd_chunks(S, R));
+  return align256((chunks > 0 ? chunks : 1) * B * H * (D / 2) * sizeof(float));
+}
+
+int rbf_b200_qkv_prep_bwd(const void* dq, const void* dk, const int64_t* dq_strides, const int64_t* dk_strides,
+                          const float* susie_table, float* d_pos_weight, float* d_reg_pos_emb, void* workspace,
+                          size_t workspace_bytes, int B, int S, int H, int D, int R, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_common(B, H, S, D, dtype, 1.0f))) return rc;
+  if (R < 0 || R > S) return fail(RBF_B200_ERR_BAD_ARGUMENT, "register rows R = %d must be in [0, S = %d]", R, S);
+  if ((rc = check_tensor("dq", dq, dq_strides, B, H, S, D))) return rc;
+  if ((rc = check_tensor("dk", dk, dk_strides, B, H, S, D))) return rc;
+  if (d_pos_weight == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "d_pos_weight is NULL");
+  if (R > 0 && d_reg_pos_emb == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "d_reg_pos_emb is NULL with R = %d", R);
+  if (S > R && (susie_table == nullptr || reinterpret_cast<uintptr_t>(susie_table) % 16 != 0))
+    return fail(RBF_B200_ERR_BAD_ARGUMENT, "susie_table is NULL or not 16-byte aligned");
+  if (H * (D / 8) > 1024) return fail(RBF_B200_ERR_BAD_ARGUMENT, "H * D = %d exceeds 8192", H * D);
+  const size_t need = rbf_b200_qkv_prep_bwd_workspace_bytes(B, S, H, D, R);
+  if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < need)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL, not 256-byte aligned or smaller than %zu bytes", need);
+  rbf::QkvPrepBwdArgs a{};
+  a.dq = dq; a.dk = dk; set_strides(a.dqs, dq_strides); set_strides(a.dks, dk_strides);
+  a.table = susie_table; a.partials = static_cast<float*>(workspace);
+  a.d_pos_weight = d_pos_weight; a.d_reg_pos = d_reg_pos_emb;
+  a.B = B; a.S = S; a.H = H; a.D = D; a.R = R;
+  const cudaError_t e = rbf::launch_qkv_prep_bwd(a, dtype == 0, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "position-gradient launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
 int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned int* code) {
   g_last_error[0] = 0;
   if (code == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "code is NULL");

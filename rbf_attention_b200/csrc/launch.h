@@ -40,6 +40,46 @@ struct RowStatsArgs {
 };
 cudaError_t launch_row_stats(const RowStatsArgs& a, bool bf16, int D, cudaStream_t stream);
 
+// Fused preparation of the attention block's operands (the reference does this with torch ops, rbf_attention.py:
+// 1659-1688): splits the fused projection output qkv (B, S, 3, H, D), adds the SuSiE position term to the text rows
+// of q and k (table[t, :] * [w | w] with one learnable weight row w per head) and the learned register-position
+// rows to the first R rows, writes q' and k' through strides, and in the same pass emits what the forward's pre-pass
+// would compute from k' (and q'): the key-norm bias slabs and, for the non-softmax variant, the query norms.
+struct QkvPrepArgs {
+  const void* qkv;          // (B, S, 3, H, D) contiguous, 16-bit
+  const void* pos_weight;   // (H, D/2)
+  const void* reg_pos;      // (H, R, D); unused when R == 0
+  int params_fp32;          // the two parameter arrays are fp32 (otherwise the 16-bit type of qkv)
+  const float* table;       // (>= S - R, D) fp32 SuSiE table [sin | cos], row t for text position t
+  void* q_out;              // (B, H, S, D) through strides qo (elements, dims b, h, n)
+  void* k_out;
+  int64_t qo[3], ko[3];
+  void* kslab_out;          // (B*H, n_pad, 16) bias slabs of -c|k'|^2 / (scale2 * slab_w); -slab_big on padding rows
+  float* qsq_out;           // optional (B*H, n_pad): c|q'|^2, 0 on padding rows
+  DeviceStatus* status_to_clear;
+  int B, S, H, D, R, n_pad;
+  float scale, scale2, slab_w, slab_big;
+};
+cudaError_t launch_qkv_prep(const QkvPrepArgs& a, bool bf16, cudaStream_t stream);
+
+// Gradients of the SuSiE parameters from the gradients of q' and k' (both (B, H, S, D) through strides):
+//   d_pos_weight[h, i] = sum_{b, t} (dq' + dk')[b, h, R + t, i] * sin-part[t, i] + (dq' + dk')[b, h, R + t, i + D/2] * cos-part[t, i]
+//   d_reg_pos[h, r, :] = sum_b (dq' + dk')[b, h, r, :]
+// in two launches with a fixed summation order (block partials in `partials`, then one sum per output element).
+struct QkvPrepBwdArgs {
+  const void* dq;
+  const void* dk;
+  int64_t dqs[3], dks[3];
+  const float* table;
+  float* partials;          // (B * chunks, H * D/2) fp32 scratch
+  float* d_pos_weight;      // (H, D/2) fp32
+  float* d_reg_pos;         // (H, R, D) fp32; unused when R == 0
+  int B, S, H, D, R;
+  int chunks;               // set by the launcher
+};
+int qkv_prep_bwd_chunks(int S, int R);
+cudaError_t launch_qkv_prep_bwd(QkvPrepBwdArgs a, bool bf16, cudaStream_t stream);
+
 // Self-test of the bounded waits: one block waits on a barrier that nothing arms; when the wait runs out after `limit`
 // SM clocks it records site kSiteSelfTest in `status` exactly as the attention kernels do, and the kernel returns.
 static constexpr uint32_t kSiteSelfTest = 250;

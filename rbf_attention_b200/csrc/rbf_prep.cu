@@ -125,6 +125,210 @@ static cudaError_t launch_row_stats_t(RowStatsArgs a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fused q/k preparation of the attention block (see QkvPrepArgs)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float load_param(const void* base, int64_t index, bool fp32, bool bf16) {
+  if (fp32) return reinterpret_cast<const float*>(base)[index];
+  const uint16_t raw = reinterpret_cast<const uint16_t*>(base)[index];
+  if (bf16) return __uint_as_float(static_cast<uint32_t>(raw) << 16);
+  return __half2float(__ushort_as_half(raw));
+}
+
+template <bool kBf16>
+__device__ __forceinline__ uint4 add_round8(const uint4& x, const float (&e)[8], float& sumsq) {
+  const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = unpack2<kBf16>(xw[i]);
+    ow[i] = pack2<kBf16>(f.x + e[2 * i], f.y + e[2 * i + 1]);
+    const float2 r = unpack2<kBf16>(ow[i]);          // the norms are those of the rounded rows the kernels will read
+    sumsq = fmaf(r.x, r.x, sumsq);
+    sumsq = fmaf(r.y, r.y, sumsq);
+  }
+  return make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
+static constexpr int kPrepRowsPerBlock = 8;      // sequence positions per block (all heads)
+
+template <bool kBf16, int D>
+__global__ void __launch_bounds__(256) qkv_prep_kernel(const QkvPrepArgs a) {
+  constexpr int kLanesPerRow = D / 8;
+  if (a.status_to_clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 64)
+    reinterpret_cast<unsigned int*>(a.status_to_clear)[threadIdx.x] = 0u;
+  const int b = blockIdx.y;
+  const int s0 = blockIdx.x * kPrepRowsPerBlock;
+  const int per_pos = a.H * kLanesPerRow;                 // 16-byte chunks of q (or k) per sequence position
+  const int items = kPrepRowsPerBlock * per_pos;
+  const int64_t E = static_cast<int64_t>(a.H) * D;
+  const float inv = 1.0f / (a.scale2 * a.slab_w);
+  // whole warps stay in the loop: a row's lanes reduce with shuffles
+  for (int base = 0; base < items; base += 256) {
+    const int idx = base + threadIdx.x;
+    const int s = s0 + idx / per_pos;
+    const int rem = idx % per_pos;
+    const int h = rem / kLanesPerRow, part = rem % kLanesPerRow;
+    const bool in_range = idx < items && s < a.n_pad;
+    const bool valid = in_range && s < a.S;
+    float ksq = 0.f, qsq = 0.f;
+    if (valid) {
+      float e[8];
+      if (s < a.R) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          e[j] = load_param(a.reg_pos, (static_cast<int64_t>(h) * a.R + s) * D + part * 8 + j, a.params_fp32, kBf16);
+      } else {
+        const float* trow = a.table + static_cast<int64_t>(s - a.R) * D + part * 8;
+        const int i0 = (part * 8) % (D / 2);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          e[j] = trow[j] * load_param(a.pos_weight, static_cast<int64_t>(h) * (D / 2) + i0 + j, a.params_fp32, kBf16);
+      }
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(a.qkv) + (static_cast<int64_t>(b) * a.S + s) * 3 * E +
+                            static_cast<int64_t>(h) * D + part * 8;
+      const uint4 qv = *reinterpret_cast<const uint4*>(src);
+      const uint4 kv = *reinterpret_cast<const uint4*>(src + E);
+      const uint4 qn = add_round8<kBf16>(qv, e, qsq);
+      const uint4 kn = add_round8<kBf16>(kv, e, ksq);
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.q_out) + b * a.qo[0] + h * a.qo[1] +
+                                static_cast<int64_t>(s) * a.qo[2] + part * 8) = qn;
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.k_out) + b * a.ko[0] + h * a.ko[1] +
+                                static_cast<int64_t>(s) * a.ko[2] + part * 8) = kn;
+    }
+#pragma unroll
+    for (int o = kLanesPerRow / 2; o > 0; o >>= 1) {
+      ksq += __shfl_xor_sync(0xffffffffu, ksq, o);
+      qsq += __shfl_xor_sync(0xffffffffu, qsq, o);
+    }
+    if (in_range && part == 0) {
+      const int64_t row = (static_cast<int64_t>(b) * a.H + h) * a.n_pad + s;
+      if (a.kslab_out != nullptr) store_slab_row<kBf16>(a.kslab_out, row, valid ? -ksq * a.scale * inv : -a.slab_big);
+      if (a.qsq_out != nullptr) a.qsq_out[row] = valid ? qsq * a.scale : 0.f;
+    }
+  }
+}
+
+cudaError_t launch_qkv_prep(const QkvPrepArgs& a, bool bf16, cudaStream_t stream) {
+  dim3 grid((a.n_pad + kPrepRowsPerBlock - 1) / kPrepRowsPerBlock, a.B);
+  if (a.D == 64) {
+    if (bf16) qkv_prep_kernel<true, 64><<<grid, 256, 0, stream>>>(a);
+    else qkv_prep_kernel<false, 64><<<grid, 256, 0, stream>>>(a);
+  } else {
+    if (bf16) qkv_prep_kernel<true, 128><<<grid, 256, 0, stream>>>(a);
+    else qkv_prep_kernel<false, 128><<<grid, 256, 0, stream>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+// ---- backward: gradients of pos_weight and of the register-position rows -----------------------------------------
+static constexpr int kPrepBwdRows = 64;          // text rows per block of the first stage
+static constexpr int kPrepBwdMaxSlots = 4;       // (head, chunk) columns per thread: H * D / 8 <= 1024
+
+int qkv_prep_bwd_chunks(int S, int R) { return (S - R + kPrepBwdRows - 1) / kPrepBwdRows; }
+
+template <bool kBf16>
+__global__ void __launch_bounds__(256) qkv_prep_bwd_partial_kernel(const QkvPrepBwdArgs a) {
+  extern __shared__ float s_cols[];              // H * D column sums of this block
+  const int D = a.D;
+  const int lanes = D / 8;
+  const int cols = a.H * lanes;
+  const int b = blockIdx.y;
+  const int t0 = blockIdx.x * kPrepBwdRows;
+  const int t1 = min(t0 + kPrepBwdRows, a.S - a.R);
+  float acc[kPrepBwdMaxSlots][8];
+#pragma unroll
+  for (int u = 0; u < kPrepBwdMaxSlots; ++u)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+#pragma unroll
+  for (int u = 0; u < kPrepBwdMaxSlots; ++u) {
+    const int c = threadIdx.x + u * 256;
+    if (c >= cols) break;
+    const int h = c / lanes, part = c % lanes;
+    const uint16_t* pq = reinterpret_cast<const uint16_t*>(a.dq) + b * a.dqs[0] + h * a.dqs[1] + part * 8;
+    const uint16_t* pk = reinterpret_cast<const uint16_t*>(a.dk) + b * a.dks[0] + h * a.dks[1] + part * 8;
+    for (int t = t0; t < t1; ++t) {
+      const uint4 x = *reinterpret_cast<const uint4*>(pq + static_cast<int64_t>(a.R + t) * a.dqs[2]);
+      const uint4 y = *reinterpret_cast<const uint4*>(pk + static_cast<int64_t>(a.R + t) * a.dks[2]);
+      const float4 w0 = *reinterpret_cast<const float4*>(a.table + static_cast<int64_t>(t) * D + part * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(a.table + static_cast<int64_t>(t) * D + part * 8 + 4);
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<kBf16>(xw[i]), g = unpack2<kBf16>(yw[i]);
+        acc[u][2 * i] = fmaf(f.x + g.x, w[2 * i], acc[u][2 * i]);
+        acc[u][2 * i + 1] = fmaf(f.y + g.y, w[2 * i + 1], acc[u][2 * i + 1]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_cols[c * 8 + j] = acc[u][j];
+  }
+  __syncthreads();
+  // fold the sine half and the cosine half of every head onto the head's D/2 weights
+  const int half = D / 2;
+  float* dst = a.partials + (static_cast<int64_t>(b) * gridDim.x + blockIdx.x) * a.H * half;
+  for (int o = threadIdx.x; o < a.H * half; o += 256) {
+    const int h = o / half, i = o % half;
+    dst[o] = s_cols[h * D + i] + s_cols[h * D + half + i];
+  }
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(256) qkv_prep_bwd_final_kernel(const QkvPrepBwdArgs a) {
+  // blocks [0, nw): 32 weight gradients each, 8 lanes per output striding over the block partials;
+  // the remaining blocks: register-position gradients, one thread per element, summed over the batch
+  const int half = a.D / 2;
+  const int n_out = a.H * half;
+  const int nw = (n_out + 31) / 32;
+  if (static_cast<int>(blockIdx.x) < nw) {
+    __shared__ float s_part[8][32];
+    const int o = blockIdx.x * 32 + (threadIdx.x & 31);
+    const int lane8 = threadIdx.x >> 5;
+    const int n_blocks = a.B * a.chunks;
+    float sum = 0.f;
+    if (o < n_out)
+      for (int p = lane8; p < n_blocks; p += 8) sum += a.partials[static_cast<int64_t>(p) * n_out + o];
+    s_part[lane8][threadIdx.x & 31] = sum;
+    __syncthreads();
+    if (threadIdx.x < 32 && o < n_out) {
+      float total = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) total += s_part[i][threadIdx.x];
+      a.d_pos_weight[o] = total;
+    }
+  } else {
+    const int e = (blockIdx.x - nw) * 256 + threadIdx.x;
+    if (e >= a.H * a.R * a.D) return;
+    const int d = e % a.D, r = (e / a.D) % a.R, h = e / (a.D * a.R);
+    float sum = 0.f;
+    for (int b = 0; b < a.B; ++b) {
+      const uint16_t x = reinterpret_cast<const uint16_t*>(a.dq)[b * a.dqs[0] + h * a.dqs[1] + r * a.dqs[2] + d];
+      const uint16_t y = reinterpret_cast<const uint16_t*>(a.dk)[b * a.dks[0] + h * a.dks[1] + r * a.dks[2] + d];
+      sum += kBf16 ? __uint_as_float(static_cast<uint32_t>(x) << 16) + __uint_as_float(static_cast<uint32_t>(y) << 16)
+                   : __half2float(__ushort_as_half(x)) + __half2float(__ushort_as_half(y));
+    }
+    a.d_reg_pos[e] = sum;
+  }
+}
+
+cudaError_t launch_qkv_prep_bwd(QkvPrepBwdArgs a, bool bf16, cudaStream_t stream) {
+  if (a.H * (a.D / 8) > 256 * kPrepBwdMaxSlots) return cudaErrorInvalidValue;
+  a.chunks = qkv_prep_bwd_chunks(a.S, a.R);
+  const int smem = a.H * a.D * sizeof(float);
+  dim3 grid(a.chunks, a.B);
+  if (bf16) qkv_prep_bwd_partial_kernel<true><<<grid, 256, smem, stream>>>(a);
+  else qkv_prep_bwd_partial_kernel<false><<<grid, 256, smem, stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int nw = (a.H * (a.D / 2) + 31) / 32;
+  const int nr = (a.H * a.R * a.D + 255) / 256;
+  if (bf16) qkv_prep_bwd_final_kernel<true><<<nw + nr, 256, 0, stream>>>(a);
+  else qkv_prep_bwd_final_kernel<false><<<nw + nr, 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
 __global__ void __launch_bounds__(32) wait_selftest_kernel(DeviceStatus* status, long long limit) {
   __shared__ uint64_t bar;
   __shared__ int abort_flag;

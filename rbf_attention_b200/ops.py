@@ -364,6 +364,182 @@ torch.library.register_autograd(
 
 
 # ---------------------------------------------------------------------------------------------
+# The attention block's RBF branch as one operator: fused q/k preparation (SuSiE positions, register-position rows,
+# key norms) + attention, reading and writing the projection layouts in place. Replaces, for the "rbf_triton" and
+# "rbf_non_softmax" attention types with SuSiE positions, the torch ops of rbf_attention.py:1659-1688 and :1761
+# (split, broadcast adds, concatenation, transpose copy) and their autograd.
+# ---------------------------------------------------------------------------------------------
+def _bhsd_view(t: torch.Tensor) -> torch.Tensor:
+    """(B, S, H, D) memory seen as (B, H, S, D), no copy."""
+    return t.permute(0, 2, 1, 3)
+
+
+@torch.library.custom_op("rbf_attn_b200::susie_block_fwd", mutates_args=())
+def susie_block_fwd(
+    qkv: torch.Tensor,
+    pos_weight: torch.Tensor,
+    reg_pos_emb: torch.Tensor | None,
+    table: torch.Tensor,
+    num_heads: int,
+    softmax: bool,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """qkv (B, S, 3 H D), pos_weight (H, D/2), reg_pos_emb (H, R, D) or None, table (>= S - R, D) ->
+    (out (B, S, H D), L (B, H, S) fp32 [empty when softmax is False], qk (2, B, S, H, D) = the prepared q', k')."""
+    if not qkv.is_cuda:
+        raise RuntimeError("qkv must be a CUDA tensor: rbf_attention_b200 has no CPU path")
+    if qkv.dtype not in _DTYPE_CODE:
+        raise ValueError(f"unsupported dtype {qkv.dtype} (bfloat16 or float16)")
+    B, S, E3 = qkv.shape
+    E = E3 // 3
+    H = num_heads
+    D = E // H
+    R = 0 if reg_pos_emb is None else reg_pos_emb.shape[-2]
+    if D not in (64, 128):
+        raise ValueError(f"head dim {D} is not supported (64 or 128)")
+    lib = _lib.load()
+    dev = qkv.device
+    qkv = qkv.contiguous()
+    params_fp32 = pos_weight.dtype == torch.float32
+    if not params_fp32 and pos_weight.dtype != qkv.dtype:
+        raise ValueError("pos_weight must be float32 or have the dtype of qkv")
+    pw = pos_weight.contiguous()
+    rp = None if R == 0 else reg_pos_emb.to(pw.dtype).contiguous()
+    table = table.to(device=dev, dtype=torch.float32).contiguous()
+    if table.shape[0] < S - R:
+        raise ValueError(f"the position table holds {table.shape[0]} rows, {S - R} text positions are needed")
+    qk = torch.empty((2, B, S, H, D), dtype=qkv.dtype, device=dev)
+    out = torch.empty((B, S, H, D), dtype=qkv.dtype, device=dev)
+    lse = torch.empty((B, H, S) if softmax else (0,), dtype=torch.float32, device=dev)
+    q, k = _bhsd_view(qk[0]), _bhsd_view(qk[1])
+    v = _bhsd_view(qkv.view(B, S, 3, H, D)[:, :, 2])
+    o = _bhsd_view(out)
+    ws = _workspace(B, H, S, D, softmax, False, dev)
+    scale = 1.0 / math.sqrt(D)
+    mon = _monitor(dev)
+    mon.poll()
+    with torch.cuda.device(dev):
+        stream = _stream_ptr(dev)
+        rc = lib.rbf_b200_qkv_prep(
+            qkv.data_ptr(), pw.data_ptr(), None if rp is None else rp.data_ptr(), int(params_fp32), table.data_ptr(),
+            q.data_ptr(), k.data_ptr(), _lib.strides3(q), _lib.strides3(k), ws.data_ptr(), ws.numel(),
+            B, S, H, D, R, _DTYPE_CODE[qkv.dtype], int(softmax), scale, stream)
+        _lib.check(rc, "rbf_b200_qkv_prep")
+        rc = lib.rbf_b200_fwd_phases(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr() if softmax else None,
+            ws.data_ptr(), ws.numel(), B, H, S, D, _lib.strides3(q), _lib.strides3(k), _lib.strides3(v),
+            _lib.strides3(o), _DTYPE_CODE[qkv.dtype], 1, int(softmax), scale, stream, 2)
+        _lib.check(rc, "rbf_b200_fwd")
+        mon.record(ws, "rbf_b200_fwd (attention block)")
+    return out.view(B, S, E), lse, qk
+
+
+@susie_block_fwd.register_fake
+def _(qkv, pos_weight, reg_pos_emb, table, num_heads, softmax):
+    B, S, E3 = qkv.shape
+    E = E3 // 3
+    D = E // num_heads
+    return (
+        qkv.new_empty((B, S, E)),
+        qkv.new_empty((B, num_heads, S) if softmax else (0,), dtype=torch.float32),
+        qkv.new_empty((2, B, S, num_heads, D)),
+    )
+
+
+@torch.library.custom_op("rbf_attn_b200::susie_block_bwd", mutates_args=())
+def susie_block_bwd(
+    qkv: torch.Tensor,
+    qk: torch.Tensor,
+    out: torch.Tensor,
+    lse: torch.Tensor,
+    dout: torch.Tensor,
+    table: torch.Tensor,
+    num_registers: int,
+    softmax: bool,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """-> (dqkv (B, S, 3 H D), d_pos_weight (H, D/2) fp32, d_reg_pos_emb (H, R, D) fp32)."""
+    _, B, S, H, D = qk.shape
+    E = H * D
+    R = num_registers
+    lib = _lib.load()
+    dev = qkv.device
+    dt = _DTYPE_CODE[qkv.dtype]
+    qkv = qkv.contiguous()
+    dout = dout.to(qkv.dtype).contiguous()
+    table = table.to(device=dev, dtype=torch.float32).contiguous()
+    q, k = _bhsd_view(qk[0]), _bhsd_view(qk[1])
+    v = _bhsd_view(qkv.view(B, S, 3, H, D)[:, :, 2])
+    o = _bhsd_view(out.view(B, S, H, D))
+    do = _bhsd_view(dout.view(B, S, H, D))
+    dqkv = torch.empty((B, S, 3, H, D), dtype=qkv.dtype, device=dev)
+    dq, dk, dv = (_bhsd_view(dqkv[:, :, i]) for i in range(3))
+    d_pw = torch.empty((H, D // 2), dtype=torch.float32, device=dev)
+    d_rp = torch.empty((H, R, D), dtype=torch.float32, device=dev)
+    ws = _workspace(B, H, S, D, softmax, True, dev)
+    nb2 = lib.rbf_b200_qkv_prep_bwd_workspace_bytes(B, S, H, D, R)
+    ws2 = torch.empty(nb2, dtype=torch.uint8, device=dev)
+    mon = _monitor(dev)
+    mon.poll()
+    lib.rbf_b200_set_deterministic(int(torch.are_deterministic_algorithms_enabled()))
+    with torch.cuda.device(dev):
+        stream = _stream_ptr(dev)
+        rc = lib.rbf_b200_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr() if softmax else None,
+            do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel(), B, H, S, D,
+            _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(o), _lib.strides3(do),
+            _lib.strides3(dq), _lib.strides3(dk), _lib.strides3(dv), dt, 1, int(softmax), 1.0 / math.sqrt(D), stream)
+        _lib.check(rc, "rbf_b200_bwd")
+        mon.record(ws, "rbf_b200_bwd (attention block)")
+        rc = lib.rbf_b200_qkv_prep_bwd(
+            dq.data_ptr(), dk.data_ptr(), _lib.strides3(dq), _lib.strides3(dk), table.data_ptr(), d_pw.data_ptr(),
+            d_rp.data_ptr() if R > 0 else None, ws2.data_ptr(), nb2, B, S, H, D, R, dt, stream)
+        _lib.check(rc, "rbf_b200_qkv_prep_bwd")
+    return dqkv.view(B, S, 3 * E), d_pw, d_rp
+
+
+@susie_block_bwd.register_fake
+def _(qkv, qk, out, lse, dout, table, num_registers, softmax):
+    _, B, S, H, D = qk.shape
+    return (
+        qkv.new_empty((B, S, 3 * H * D)),
+        qkv.new_empty((H, D // 2), dtype=torch.float32),
+        qkv.new_empty((H, num_registers, D), dtype=torch.float32),
+    )
+
+
+def _susie_block_setup_context(ctx, inputs, output):
+    qkv, pos_weight, reg_pos_emb, table, num_heads, softmax = inputs
+    out, lse, qk = output
+    ctx.save_for_backward(qkv, qk, out, lse, table)
+    ctx.softmax = softmax
+    ctx.num_registers = 0 if reg_pos_emb is None else reg_pos_emb.shape[-2]
+    ctx.pw_dtype = pos_weight.dtype
+    ctx.rp_dtype = None if reg_pos_emb is None else reg_pos_emb.dtype
+    ctx.set_materialize_grads(False)
+
+
+def _susie_block_backward(ctx, dout, dlse, dqk):
+    # only `out` carries a gradient: L and the saved q', k' are by-products (the reference ignores dL too)
+    qkv, qk, out, lse, table = ctx.saved_tensors
+    if dout is None:
+        return None, None, None, None, None, None
+    dqkv, d_pw, d_rp = torch.ops.rbf_attn_b200.susie_block_bwd(
+        qkv, qk, out, lse, dout, table, ctx.num_registers, ctx.softmax)
+    d_rp = None if ctx.rp_dtype is None else d_rp.to(ctx.rp_dtype)
+    return dqkv, d_pw.to(ctx.pw_dtype), d_rp, None, None, None
+
+
+torch.library.register_autograd(
+    "rbf_attn_b200::susie_block_fwd", _susie_block_backward, setup_context=_susie_block_setup_context
+)
+
+
+def susie_block_attention(qkv, pos_weight, reg_pos_emb, table, num_heads, softmax=True):
+    """Attention of one block from the fused projection output: (B, S, 3 H D) -> (B, S, H D), causal, with the SuSiE
+    position term and the register-position rows added to q and k inside the operator."""
+    return torch.ops.rbf_attn_b200.susie_block_fwd(qkv, pos_weight, reg_pos_emb, table, num_heads, softmax)[0]
+
+
+# ---------------------------------------------------------------------------------------------
 # Wrappers with the reference's names (rbf_attention.py:848-853)
 # ---------------------------------------------------------------------------------------------
 def run_triton_rbf(q, k, v, is_causal=True):

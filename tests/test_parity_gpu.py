@@ -401,6 +401,100 @@ def test_attention_block_matches_its_comparator_branch():
         assert oracle.error_report(pf.grad.cpu().float(), ps.grad)["rel_l2"] <= 5e-2, name
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H,D,R,softmax", [(8, 64, 4, True), (4, 128, 0, True), (4, 64, 2, False)])
+def test_qkv_prep_through_c_abi(H, D, R, softmax, dtype):
+    """rbf_b200_qkv_prep against the torch ops it replaces (rbf_attention.py:1659-1688, evaluated in fp32 and rounded
+    once), the forward that follows it (main kernel only, fed by the workspace the preparation filled) against the
+    regular forward on the same q', k', and rbf_b200_qkv_prep_bwd against fp32 sums."""
+    lib = _lib.load()
+    B, S = 3, 333
+    E = H * D
+    g = torch.Generator().manual_seed(S + D)
+    qkv = (torch.randn(B, S, 3 * E, generator=g) * (1.0 if softmax else 0.5)).to(DEV, dtype)
+    pw = (torch.rand(H, D // 2, generator=g) + 0.2).to(DEV)                     # fp32 parameters (autocast training)
+    rp = (torch.randn(H, R, D, generator=g) * 0.1).to(DEV) if R else None
+    table = attention.get_unrotated_sinusoids(S, D, DEV).contiguous()
+    code = 0 if dtype == torch.bfloat16 else 1
+    stream = torch.cuda.current_stream().cuda_stream
+    qk = torch.empty((2, B, S, H, D), dtype=dtype, device=DEV)
+    q, k = qk[0].permute(0, 2, 1, 3), qk[1].permute(0, 2, 1, 3)
+    v = qkv.view(B, S, 3, H, D)[:, :, 2].permute(0, 2, 1, 3)
+    nbytes = lib.rbf_b200_workspace_bytes(B, H, S, D, int(softmax), 0)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    rc = lib.rbf_b200_qkv_prep(qkv.data_ptr(), pw.data_ptr(), rp.data_ptr() if R else None, 1, table.data_ptr(),
+                               q.data_ptr(), k.data_ptr(), _s3(q), _s3(k), ws.data_ptr(), nbytes, B, S, H, D, R, code,
+                               int(softmax), 1.0 / math.sqrt(D), stream)
+    assert rc == 0, lib.rbf_b200_last_error()
+    # (1) q', k' = round(x + emb) with emb evaluated in fp32
+    emb = table[None, None, : S - R] * pw.repeat(1, 2)[None, :, None, :]
+    if R:
+        emb = torch.cat([rp[None], emb], dim=2)
+    x = qkv.view(B, S, 3, H, D).permute(2, 0, 3, 1, 4).float()
+    for got, want in ((q, x[0] + emb), (k, x[1] + emb)):
+        assert (got.float() - want).abs().max().item() <= 2.0 ** -7 * max(1.0, want.abs().max().item())
+        assert (got != want.to(dtype)).float().mean().item() <= 1e-3        # fused multiply-adds may differ by an ulp
+    # (2) forward main kernel on the prepared workspace == complete forward on q', k'
+    out = torch.empty((B, H, S, D), dtype=dtype, device=DEV)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=DEV)
+    rc = lib.rbf_b200_fwd_phases(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), ws.data_ptr(),
+                                 nbytes, B, H, S, D, _s3(q), _s3(k), _s3(v), _s3(out), code, 1, int(softmax),
+                                 1.0 / math.sqrt(D), stream, 2)
+    assert rc == 0, lib.rbf_b200_last_error()
+    ref_out, ref_lse = cabi_forward(q, k, v, True, softmax)
+    assert torch.equal(out, ref_out)
+    if softmax:
+        assert torch.equal(lse, ref_lse)
+    # (3) parameter gradients from dq', dk'
+    dqk = (torch.randn(2, B, S, H, D, generator=g)).to(DEV, dtype)
+    dq, dk = dqk[0].permute(0, 2, 1, 3), dqk[1].permute(0, 2, 1, 3)
+    d_pw = torch.empty((H, D // 2), dtype=torch.float32, device=DEV)
+    d_rp = torch.empty((H, R, D), dtype=torch.float32, device=DEV)
+    nb2 = lib.rbf_b200_qkv_prep_bwd_workspace_bytes(B, S, H, D, R)
+    ws2 = torch.empty(nb2, dtype=torch.uint8, device=DEV)
+    rc = lib.rbf_b200_qkv_prep_bwd(dq.data_ptr(), dk.data_ptr(), _s3(dq), _s3(dk), table.data_ptr(), d_pw.data_ptr(),
+                                   d_rp.data_ptr() if R else None, ws2.data_ptr(), nb2, B, S, H, D, R, code, stream)
+    assert rc == 0, lib.rbf_b200_last_error()
+    gsum = (dq.double() + dk.double())                                           # (B, H, S, D)
+    want_tab = (gsum[:, :, R:] * table[None, None, : S - R].double()).sum((0, 2))   # (H, D)
+    want_pw = want_tab[:, : D // 2] + want_tab[:, D // 2:]
+    assert (d_pw.double() - want_pw).abs().max().item() <= 1e-4 * want_pw.abs().max().item()
+    if R:
+        want_rp = gsum[:, :, :R].sum(0)
+        assert (d_rp.double() - want_rp).abs().max().item() <= 1e-5 * max(1.0, want_rp.abs().max().item())
+
+
+@pytest.mark.parametrize("kind,H,E,R", [("rbf_triton", 8, 512, 4), ("rbf_triton", 2, 256, 0), ("rbf_non_softmax", 4, 256, 2)])
+def test_fused_block_operator_equals_the_operator_by_operator_path(kind, H, E, R, monkeypatch):
+    """The single block operator (fused preparation, in-place layouts) against the same module taking the generic path
+    (torch ops + run_triton_rbf): outputs, input gradient and every parameter gradient, bf16, ragged length."""
+    torch.manual_seed(2)
+    blk = attention.CustomCausalAttention(H, E, max_seq_len=600, attention_type=kind, num_registers=R).to(DEV, torch.bfloat16)
+    with torch.no_grad():
+        blk.pos_weight.uniform_(0.2, 0.8)
+    scale = 1.0 if kind == "rbf_triton" else 0.3
+    x = (torch.randn(2, 300 + R, E, device=DEV) * scale).bfloat16()
+    gy = torch.randn(2, 300 + R, E, device=DEV).bfloat16()
+    results = []
+    for fused in (True, False):
+        if not fused:
+            monkeypatch.setattr(attention.CustomCausalAttention, "_fused_block", lambda self, qkv: False)
+        else:
+            assert blk._fused_block(blk.qkv_proj(x))
+        xi = x.clone().requires_grad_(True)
+        blk.zero_grad(set_to_none=True)
+        y, w = blk(xi)
+        y.backward(gy)
+        assert w is None
+        results.append((y.detach().float(), xi.grad.float(), {n: p.grad.float().clone() for n, p in blk.named_parameters()}))
+    (y1, gx1, gp1), (y0, gx0, gp0) = results
+    # the generic path rounds the position term and the sum to bf16 separately; the operator rounds once
+    assert oracle.error_report(y1.cpu(), y0.cpu())["rel_l2"] <= 1e-2
+    assert oracle.error_report(gx1.cpu(), gx0.cpu())["rel_l2"] <= 1.5e-2
+    for name in gp0:
+        assert oracle.error_report(gp1[name].cpu(), gp0[name].cpu())["rel_l2"] <= 2e-2, name
+
+
 def test_non_softmax_block_and_compiled_call():
     torch.manual_seed(1)
     blk = attention.CustomCausalAttention(4, 256, max_seq_len=256, attention_type="rbf_non_softmax").to(DEV, torch.bfloat16)
