@@ -152,6 +152,18 @@ int rbf_b200_qkv_prep_bwd(const void* dq, const void* dk, const int64_t* dq_stri
                           const float* susie_table, float* d_pos_weight, float* d_reg_pos_emb, void* workspace,
                           size_t workspace_bytes, int B, int S, int H, int D, int R, int dtype, void* stream);
 
+/* Exclusive self attention, the attention block's apply_xsa option (rbf_attention.py:1757-1759):
+ * out = o - (o . vh) vh per row, with vh = v / max(|v|, 1e-12) the normalised value row of the same position; all
+ * tensors (B, H, N, D) through strides, arithmetic in fp32, one pass over the rows. The backward call returns, from
+ * the gradient g of `out`, d_o = g - (g . vh) vh and the contribution to d_v of this step (the attention backward's
+ * own d_v is added by the caller); it needs o as the attention produced it, which is why this is a separate pass and
+ * not part of the attention kernel's output stage: the attention backward needs that same unprojected o. */
+int rbf_b200_xsa_fwd(const void* o, const void* v, void* out, const int64_t* o_strides, const int64_t* v_strides,
+                     const int64_t* out_strides, int B, int H, int N, int D, int dtype, void* stream);
+int rbf_b200_xsa_bwd(const void* g, const void* o, const void* v, void* d_o, void* d_v, const int64_t* g_strides,
+                     const int64_t* o_strides, const int64_t* v_strides, const int64_t* do_strides,
+                     const int64_t* dv_strides, int B, int H, int N, int D, int dtype, void* stream);
+
 /* Synchronises `stream` and reads the device status word that the last call using `workspace` left:
  * 0 = ok, otherwise (site << 24 | work unit) of the bounded wait that ran out; the work unit is the linear block
  * index of the launch or, for the persistent backward kernel, the (key tile, batch-head) item. Returns

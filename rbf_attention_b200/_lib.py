@@ -71,6 +71,8 @@ SIGNATURES = {
         [ctypes.c_void_p] * 2 + [_c_i64p] * 2 + [ctypes.c_void_p] * 4 + [ctypes.c_size_t] + [ctypes.c_int] * 6
         + [ctypes.c_void_p],
     ),
+    "rbf_b200_xsa_fwd": (ctypes.c_int, [ctypes.c_void_p] * 3 + [_c_i64p] * 3 + [ctypes.c_int] * 5 + [ctypes.c_void_p]),
+    "rbf_b200_xsa_bwd": (ctypes.c_int, [ctypes.c_void_p] * 5 + [_c_i64p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_void_p]),
     "rbf_b200_set_deterministic": (ctypes.c_int, [ctypes.c_int]),
     "rbf_b200_get_deterministic": (ctypes.c_int, []),
     "rbf_b200_selftest_wait_timeout": (

@@ -26,7 +26,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .ops import run_triton_non_softmax_rbf, run_triton_rbf, susie_block_attention
+from .ops import exclusive_self_attention, run_triton_non_softmax_rbf, run_triton_rbf, susie_block_attention
 
 __all__ = [
     "CustomCausalAttention",
@@ -260,8 +260,12 @@ class CustomCausalAttention(nn.Module):
             raise ValueError(f"unknown attention_type {kind!r}")
 
         if self.apply_xsa:
-            v_hat = F.normalize(v, dim=-1)
-            out = out - (out * v_hat).sum(dim=-1, keepdim=True) * v_hat
+            if out.is_cuda and out.dtype in (torch.bfloat16, torch.float16) and self.head_dim in (64, 128) \
+                    and v.dtype == out.dtype:
+                out = exclusive_self_attention(out, v)          # one fused pass (and one for its backward)
+            else:
+                v_hat = F.normalize(v, dim=-1)
+                out = out - (out * v_hat).sum(dim=-1, keepdim=True) * v_hat
 
         out = out.transpose(1, 2).reshape(bsz, seq_len, emb)
         return self.proj(out), attn_weights

@@ -466,6 +466,45 @@ int rbf_b200_qkv_prep_bwd(const void* dq, const void* dk, const int64_t* dq_stri
   return RBF_B200_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Exclusive self attention (projection away from the position's own value row)
+// ---------------------------------------------------------------------------------------------
+int rbf_b200_xsa_fwd(const void* o, const void* v, void* out, const int64_t* o_strides, const int64_t* v_strides,
+                     const int64_t* out_strides, int B, int H, int N, int D, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_common(B, H, N, D, dtype, 1.0f))) return rc;
+  if ((rc = check_tensor("o", o, o_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("v", v, v_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("out", out, out_strides, B, H, N, D))) return rc;
+  rbf::XsaArgs a{};
+  a.o = o; a.v = v; a.out = out; a.B = B; a.H = H; a.N = N;
+  set_strides(a.os, o_strides); set_strides(a.vs, v_strides); set_strides(a.outs, out_strides);
+  const cudaError_t e = rbf::launch_xsa(a, false, dtype == 0, D, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "xsa forward launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+int rbf_b200_xsa_bwd(const void* g, const void* o, const void* v, void* d_o, void* d_v, const int64_t* g_strides,
+                     const int64_t* o_strides, const int64_t* v_strides, const int64_t* do_strides,
+                     const int64_t* dv_strides, int B, int H, int N, int D, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_common(B, H, N, D, dtype, 1.0f))) return rc;
+  if ((rc = check_tensor("g", g, g_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("o", o, o_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("v", v, v_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("d_o", d_o, do_strides, B, H, N, D))) return rc;
+  if ((rc = check_tensor("d_v", d_v, dv_strides, B, H, N, D))) return rc;
+  rbf::XsaArgs a{};
+  a.g = g; a.o = o; a.v = v; a.out = d_o; a.dv = d_v; a.B = B; a.H = H; a.N = N;
+  set_strides(a.gs, g_strides); set_strides(a.os, o_strides); set_strides(a.vs, v_strides);
+  set_strides(a.outs, do_strides); set_strides(a.dvs, dv_strides);
+  const cudaError_t e = rbf::launch_xsa(a, true, dtype == 0, D, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "xsa backward launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
 int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned int* code) {
   g_last_error[0] = 0;
   if (code == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "code is NULL");

@@ -80,6 +80,21 @@ struct QkvPrepBwdArgs {
 int qkv_prep_bwd_chunks(int S, int R);
 cudaError_t launch_qkv_prep_bwd(QkvPrepBwdArgs a, bool bf16, cudaStream_t stream);
 
+// Exclusive self attention (the attention block's `apply_xsa` option, rbf_attention.py:1757-1759): every output row
+// loses its component along the value row of the same position, out = o - (o . vh) vh with vh = v / max(|v|, 1e-12).
+// One pass forward; one pass backward giving d_o = g - (g . vh) vh and d_v = (-(o . vh) g - (g . vh) o +
+// 2 (o . vh)(g . vh) vh) / |v|. All tensors (B, H, N, D) through strides (elements, dims b, h, n).
+struct XsaArgs {
+  const void* o;
+  const void* v;
+  const void* g;           // backward only: gradient of the projected output
+  void* out;               // forward: projected output; backward: d_o
+  void* dv;                // backward only
+  int64_t os[3], vs[3], gs[3], outs[3], dvs[3];
+  int B, H, N;
+};
+cudaError_t launch_xsa(const XsaArgs& a, bool backward, bool bf16, int D, cudaStream_t stream);
+
 // Self-test of the bounded waits: one block waits on a barrier that nothing arms; when the wait runs out after `limit`
 // SM clocks it records site kSiteSelfTest in `status` exactly as the attention kernels do, and the kernel returns.
 static constexpr uint32_t kSiteSelfTest = 250;

@@ -329,6 +329,93 @@ cudaError_t launch_qkv_prep_bwd(QkvPrepBwdArgs a, bool bf16, cudaStream_t stream
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Exclusive self attention: row-wise projection away from the position's own value row (see XsaArgs)
+// ---------------------------------------------------------------------------------------------
+template <bool kBf16>
+__device__ __forceinline__ void unpack8(const uint4& x, float (&f)[8]) {
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack2<kBf16>(w[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack2<kBf16>(f[0], f[1]), pack2<kBf16>(f[2], f[3]), pack2<kBf16>(f[4], f[5]),
+                    pack2<kBf16>(f[6], f[7]));
+}
+
+template <bool kBf16, int D, bool kBackward>
+__global__ void __launch_bounds__(256) xsa_kernel(const XsaArgs a) {
+  constexpr int kLanesPerRow = D / 8;
+  constexpr int kRowsPerBlock = 256 / kLanesPerRow;
+  const int sub = threadIdx.x / kLanesPerRow, part = threadIdx.x % kLanesPerRow;
+  const int bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int row = blockIdx.x * kRowsPerBlock + sub;
+  const bool valid = row < a.N;
+  float o[8] = {}, v[8] = {}, g[8] = {};
+  if (valid) {
+    unpack8<kBf16>(load_chunk(a.o, a.os, b, h, row, part), o);
+    unpack8<kBf16>(load_chunk(a.v, a.vs, b, h, row, part), v);
+    if (kBackward) unpack8<kBf16>(load_chunk(a.g, a.gs, b, h, row, part), g);
+  }
+  float vv = 0.f, ov = 0.f, gv = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    vv = fmaf(v[j], v[j], vv);
+    ov = fmaf(o[j], v[j], ov);
+    if (kBackward) gv = fmaf(g[j], v[j], gv);
+  }
+#pragma unroll
+  for (int m = kLanesPerRow / 2; m > 0; m >>= 1) {
+    vv += __shfl_xor_sync(0xffffffffu, vv, m);
+    ov += __shfl_xor_sync(0xffffffffu, ov, m);
+    if (kBackward) gv += __shfl_xor_sync(0xffffffffu, gv, m);
+  }
+  if (!valid) return;
+  const float nrm = fmaxf(sqrtf(vv), 1e-12f);
+  const float inv = 1.0f / nrm;
+  const float alpha = ov * inv;                 // o . vh
+  uint16_t* out = reinterpret_cast<uint16_t*>(a.out) + b * a.outs[0] + h * a.outs[1] +
+                  static_cast<int64_t>(row) * a.outs[2] + part * 8;
+  float r[8];
+  if (!kBackward) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = fmaf(-alpha * inv, v[j], o[j]);
+    *reinterpret_cast<uint4*>(out) = pack8<kBf16>(r);
+  } else {
+    const float beta = gv * inv;                // g . vh
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = fmaf(-beta * inv, v[j], g[j]);
+    *reinterpret_cast<uint4*>(out) = pack8<kBf16>(r);
+    // below the clamp vh = v / 1e-12 is linear in v: only the first two terms remain
+    const float corr = sqrtf(vv) > 1e-12f ? 2.f * alpha * beta * inv : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = (fmaf(corr, v[j], -alpha * g[j]) - beta * o[j]) * inv;
+    uint16_t* dv = reinterpret_cast<uint16_t*>(a.dv) + b * a.dvs[0] + h * a.dvs[1] +
+                   static_cast<int64_t>(row) * a.dvs[2] + part * 8;
+    *reinterpret_cast<uint4*>(dv) = pack8<kBf16>(r);
+  }
+}
+
+template <bool kBf16, int D>
+static cudaError_t launch_xsa_t(const XsaArgs& a, bool backward, cudaStream_t stream) {
+  constexpr int kRowsPerBlock = 256 / (D / 8);
+  dim3 grid((a.N + kRowsPerBlock - 1) / kRowsPerBlock, a.B * a.H);
+  if (backward) xsa_kernel<kBf16, D, true><<<grid, 256, 0, stream>>>(a);
+  else xsa_kernel<kBf16, D, false><<<grid, 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_xsa(const XsaArgs& a, bool backward, bool bf16, int D, cudaStream_t stream) {
+  if (D == 64) return bf16 ? launch_xsa_t<true, 64>(a, backward, stream) : launch_xsa_t<false, 64>(a, backward, stream);
+  return bf16 ? launch_xsa_t<true, 128>(a, backward, stream) : launch_xsa_t<false, 128>(a, backward, stream);
+}
+
 __global__ void __launch_bounds__(32) wait_selftest_kernel(DeviceStatus* status, long long limit) {
   __shared__ uint64_t bar;
   __shared__ int abort_flag;

@@ -540,6 +540,71 @@ def susie_block_attention(qkv, pos_weight, reg_pos_emb, table, num_heads, softma
 
 
 # ---------------------------------------------------------------------------------------------
+# Exclusive self attention (the block's apply_xsa option, rbf_attention.py:1757-1759) as one fused pass each way
+# ---------------------------------------------------------------------------------------------
+@torch.library.custom_op("rbf_attn_b200::xsa_fwd", mutates_args=())
+def xsa_fwd(o: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """out = o - (o . vh) vh with vh = v / max(|v|, 1e-12), row by row; o, v (B, H, N, D)."""
+    _validate("o", o)
+    _validate("v", v, o)
+    if o.dtype not in _DTYPE_CODE:
+        raise ValueError(f"unsupported dtype {o.dtype} (bfloat16 or float16)")
+    B, H, N, D = o.shape
+    lib = _lib.load()
+    oc, vc = _tma_ready(o), _tma_ready(v)
+    out = torch.empty((B, H, N, D), dtype=o.dtype, device=o.device)
+    with torch.cuda.device(o.device):
+        rc = lib.rbf_b200_xsa_fwd(oc.data_ptr(), vc.data_ptr(), out.data_ptr(), _lib.strides3(oc), _lib.strides3(vc),
+                                  _lib.strides3(out), B, H, N, D, _DTYPE_CODE[o.dtype], _stream_ptr(o.device))
+    _lib.check(rc, "rbf_b200_xsa_fwd")
+    return out
+
+
+@xsa_fwd.register_fake
+def _(o, v):
+    return torch.empty_like(o, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op("rbf_attn_b200::xsa_bwd", mutates_args=())
+def xsa_bwd(g: torch.Tensor, o: torch.Tensor, v: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    B, H, N, D = o.shape
+    lib = _lib.load()
+    gc, oc, vc = _tma_ready(g.to(o.dtype)), _tma_ready(o), _tma_ready(v)
+    d_o = torch.empty((B, H, N, D), dtype=o.dtype, device=o.device)
+    d_v = torch.empty_like(d_o)
+    with torch.cuda.device(o.device):
+        rc = lib.rbf_b200_xsa_bwd(gc.data_ptr(), oc.data_ptr(), vc.data_ptr(), d_o.data_ptr(), d_v.data_ptr(),
+                                  _lib.strides3(gc), _lib.strides3(oc), _lib.strides3(vc), _lib.strides3(d_o),
+                                  _lib.strides3(d_v), B, H, N, D, _DTYPE_CODE[o.dtype], _stream_ptr(o.device))
+    _lib.check(rc, "rbf_b200_xsa_bwd")
+    return d_o, d_v
+
+
+@xsa_bwd.register_fake
+def _(g, o, v):
+    return (torch.empty_like(o, memory_format=torch.contiguous_format),
+            torch.empty_like(o, memory_format=torch.contiguous_format))
+
+
+def _xsa_setup_context(ctx, inputs, output):
+    o, v = inputs
+    ctx.save_for_backward(o, v)
+
+
+def _xsa_backward(ctx, g):
+    o, v = ctx.saved_tensors
+    return torch.ops.rbf_attn_b200.xsa_bwd(g, o, v)
+
+
+torch.library.register_autograd("rbf_attn_b200::xsa_fwd", _xsa_backward, setup_context=_xsa_setup_context)
+
+
+def exclusive_self_attention(o, v):
+    """Removes from every attention output row its component along the value row of the same position."""
+    return torch.ops.rbf_attn_b200.xsa_fwd(o, v)
+
+
+# ---------------------------------------------------------------------------------------------
 # Wrappers with the reference's names (rbf_attention.py:848-853)
 # ---------------------------------------------------------------------------------------------
 def run_triton_rbf(q, k, v, is_causal=True):

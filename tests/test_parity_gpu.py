@@ -495,6 +495,47 @@ def test_fused_block_operator_equals_the_operator_by_operator_path(kind, H, E, R
         assert oracle.error_report(gp1[name].cpu(), gp0[name].cpu())["rel_l2"] <= 2e-2, name
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 64), (torch.float16, 128)])
+def test_exclusive_self_attention_kernels(dtype, D):
+    """rbf_b200_xsa_fwd / _bwd (through their operators) against the reference's expression (rbf_attention.py:
+    1757-1759) and its autograd in fp64, on strided inputs; then the block with apply_xsa=True against its
+    materialised-matrix branch."""
+    g = torch.Generator().manual_seed(D)
+    B, H, N = 2, 3, 333
+    o = torch.randn(B, N, H, D, generator=g).to(DEV, dtype).permute(0, 2, 1, 3)          # strided like the block's tensors
+    v = torch.randn(B, N, H, D, generator=g).to(DEV, dtype).permute(0, 2, 1, 3)
+    gy = torch.randn(B, H, N, D, generator=g).to(DEV, dtype)
+    o64, v64 = o.double().requires_grad_(True), v.double().requires_grad_(True)
+    vh = torch.nn.functional.normalize(v64, dim=-1)
+    ref = o64 - (o64 * vh).sum(-1, keepdim=True) * vh
+    ref.backward(gy.double())
+    oi, vi = o.detach().requires_grad_(True), v.detach().requires_grad_(True)
+    out = ops.exclusive_self_attention(oi, vi)
+    out.backward(gy)
+    tol = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    for name, got, want in (("out", out, ref), ("d_o", oi.grad, o64.grad), ("d_v", vi.grad, v64.grad)):
+        err = (got.double() - want).abs().max().item()
+        assert err <= tol * max(1.0, want.abs().max().item()), (name, err)
+    # the projection is idempotent and leaves nothing along v
+    assert (out.float() * torch.nn.functional.normalize(v.float(), dim=-1)).sum(-1).abs().max().item() <= 5e-2
+    torch.manual_seed(3)
+    slow = attention.CustomCausalAttention(4, 256, max_seq_len=256, attention_type="rbf_slow", apply_xsa=True, num_registers=2)
+    fast = attention.CustomCausalAttention(4, 256, max_seq_len=256, attention_type="rbf_triton", apply_xsa=True, num_registers=2)
+    fast.load_state_dict(slow.state_dict())
+    fast = fast.to(DEV, torch.bfloat16)
+    x, gx = torch.randn(2, 202, 256), torch.randn(2, 202, 256)
+    xs = x.clone().requires_grad_(True)
+    ys, _ = slow(xs)
+    ys.backward(gx)
+    xf = x.to(DEV, torch.bfloat16).requires_grad_(True)
+    yf, _ = fast(xf)
+    yf.backward(gx.to(DEV, torch.bfloat16))
+    assert oracle.error_report(yf.detach().cpu().float(), ys.detach())["rel_l2"] <= 2e-2
+    assert oracle.error_report(xf.grad.cpu().float(), xs.grad)["rel_l2"] <= 3e-2
+    for (name, pf), (_, ps) in zip(fast.named_parameters(), slow.named_parameters()):
+        assert oracle.error_report(pf.grad.cpu().float(), ps.grad)["rel_l2"] <= 5e-2, name
+
+
 def test_non_softmax_block_and_compiled_call():
     torch.manual_seed(1)
     blk = attention.CustomCausalAttention(4, 256, max_seq_len=256, attention_type="rbf_non_softmax").to(DEV, torch.bfloat16)
