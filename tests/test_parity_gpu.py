@@ -225,6 +225,32 @@ def test_second_device_of_one_process():
             check(f"{name} on {dev}", got.detach().cpu().float(), want, REL_L2[torch.bfloat16])
 
 
+@pytest.mark.parametrize("D,causal", [(64, True), (64, False), (128, True)])
+@pytest.mark.parametrize("offset,q_scale", [(2.2, 1.0), (0.0, 6.0), (3.5, 1.0)])
+def test_forward_rows_whose_first_keys_are_far_away(D, causal, offset, q_scale):
+    """The bf16 forward stops computing tile maxima once the applied maximum is within 2^64 of the row's upper bound
+    g |q|^2. Cases: the first key tile far from every query and near keys later (the later logits exceed the applied
+    maximum by up to ~2^60: the stale maximum must neither overflow nor lose the early keys); very long queries (the
+    bound is never close: every tile's maximum is computed); a first tile so far away that the bound is only reached
+    after the maximum has been raised by later tiles."""
+    B, H, N = 1, 2, 640
+    g = torch.Generator().manual_seed(int(offset * 10) + D)
+    q = (torch.randn(B, H, N, D, generator=g) * q_scale).bfloat16()
+    k = torch.randn(B, H, N, D, generator=g)
+    k[:, :, :128] += offset                      # |q - k|^2 grows by about D * offset^2 for the first tile's keys
+    k = k.bfloat16()
+    v = torch.randn(B, H, N, D, generator=g).bfloat16()
+    do = torch.randn(B, H, N, D, generator=g).bfloat16()
+    ref = oracle.torch_forward_backward(q, k, v, do, causal, True, dtype=torch.float32)
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+    out, lse = cabi_forward(qd, kd, vd, causal, True)
+    dq, dk, dv = cabi_backward(qd, kd, vd, out, lse, dod, causal, True)
+    for name, got, want in zip(("O", "dQ", "dK", "dV"), (out, dq, dk, dv), ref):
+        check(name, got.cpu().float(), want, REL_L2[torch.bfloat16])
+    ref_l = oracle.torch_lse2(q, k, causal)
+    assert (lse.cpu() - ref_l).abs().max().item() <= 2e-4 * max(1.0, ref_l.abs().max().item())
+
+
 def test_golden_fixture_small(golden_dir):
     """attn_small.npz holds the reference's fp32 results; the kernel sees the same inputs rounded to bf16."""
     g = np.load(os.path.join(golden_dir, "attn_small.npz"))
