@@ -634,7 +634,7 @@ def lm_step_record(torch, dist, rank, world, local_rank, steps, warmup, compile_
 
     def step(ids):
         logits, _ = net(ids[:, :-1])
-        loss = torch.nn.functional.cross_entropy(logits.view(-1, LM["vocab"]), ids[:, 1:].reshape(-1))
+        loss = torch.nn.functional.cross_entropy(logits.reshape(-1, LM["vocab"]), ids[:, 1:].reshape(-1))
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)

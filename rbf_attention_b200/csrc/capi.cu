@@ -263,7 +263,10 @@ int rbf_b200_bwd_phases(const void* q, const void* k, const void* v, const void*
     r.B = B; r.H = H; r.N = N; r.n_pad = n_pad; r.scale = c; r.status_to_clear = ws.status;
     r.scale2 = 2.f * c; r.slab_w = slab_w(bf16); r.slab_big = slab_big(bf16);
     if (fused) { r.lslab_out = ws.lslab; r.dslab_out = ws.dslab; r.zero_rows = ws.dq_acc; }
-    r.k = k; r.ksq_out = ws.ksq; set_strides(r.ks, k_strides);
+    // The head-dim-128 single kernel takes the key norms from its resident K tile, so K is not read here. (At head
+    // dim 64 the same change slowed the main kernel by as much as the pre-pass gained: its compute warps have no
+    // registers to spare and its other warps are on the critical path of the dQ hand-over.)
+    if (!(fused && D == 128)) { r.k = k; r.ksq_out = ws.ksq; set_strides(r.ks, k_strides); }
     r.delta_out = ws.delta;                     // written as zeros when there is no O (non-softmax variant)
     if (softmax) {
       r.o = out; r.dout = dout; set_strides(r.os, o_strides); set_strides(r.dos, do_strides);

@@ -140,7 +140,7 @@ struct BwdFusedArgs {
   float* dq_acc;          // fp32 (B, H, N, D) contiguous accumulator
   void* dq;               // final dQ in the operand type
   int64_t dq_strides[3];
-  const float* ksq;       // (B*H, n_pad)
+  const float* ksq;       // (B*H, n_pad); head dim 64 only (the head-dim-128 kernel takes the norms from its K tile)
   // non-softmax variant: dQ = 2 gamma (acc - delta * q) with delta = rowsum(O * dO) = rowsum_j dS_ij; null otherwise
   const void* q_rows;
   int64_t q_strides[3];

@@ -84,7 +84,6 @@ enum Site : uint32_t {
 };
 
 struct Params {
-  const float* ksq;      // (B*H, n_pad), +inf on padding rows
   float* dq_acc;         // fp32 (B, H, N, 128), zero-initialised
   DeviceStatus* status;
   int H, N, n_pad, causal;
@@ -368,11 +367,28 @@ rbf_bwd_fused128_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
     const int g = (warp - kComputeWarp0) >> 2;             // 16-column slice of the query step
     const int r = tid & (kTile - 1);
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const float neg_ksq = -p.ksq[static_cast<int64_t>(bh) * p.n_pad + k_row0 + r];
     float ds_rowsum = 0.f;
-    bool ok = true;
+    // c |k_r|^2 of this thread's key row, from the resident K tile; rows past N (zero-filled by the load) get
+    // +infinity, i.e. weight exp2(-inf) = 0
+    float neg_ksq = -INFINITY;
+    bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kSiteKV);
+    if (ok && k_row0 + r < p.N) {
+      float acc = 0.f;
+#pragma unroll 1
+      for (int c16 = 0; c16 < D / 8; ++c16) {      // once per key tile: kept rolled, registers are scarce here
+        const uint4 kv = *reinterpret_cast<const uint4*>(s_k + (c16 >> 3) * kBoxBytes + sw128_offset(r, c16 & 7));
+        const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 x = unpack2<kBf16>(w[i]);
+          acc = fmaf(x.x, x.x, acc);
+          acc = fmaf(x.y, x.y, acc);
+        }
+      }
+      neg_ksq = -acc * (0.5f * p.scale2);
+    }
 
-    for (int n = 0; n < cnt; ++n) {
+    for (int n = 0; n < cnt && ok; ++n) {
       ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull);
       if (!ok) break;
       tc_fence_after_sync();
@@ -567,7 +583,7 @@ static cudaError_t launch_t(const BwdFusedArgs& a, cudaStream_t stream) {
   // the pre-pass has cleared the dQ accumulator
   cudaError_t e = cudaSuccess;
   Params p{};
-  p.ksq = a.ksq; p.dq_acc = a.dq_acc; p.status = a.status;
+  p.dq_acc = a.dq_acc; p.status = a.status;
   p.H = a.H; p.N = a.N; p.n_pad = a.n_pad; p.causal = a.causal;
   p.scale2 = a.scale2; p.grad_scale = a.grad_scale; p.slab_w = a.slab_w;
   dim3 grid((a.N + kTile - 1) / kTile, a.B * a.H);

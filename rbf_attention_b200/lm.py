@@ -8,8 +8,24 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .attention import CustomCausalAttention
+
+
+def vocab_projection(linear: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    """``linear(x)`` for an output width (the vocabulary) whose rows are not 16-byte aligned in 16-bit types. With the
+    reference's vocabulary of 50257 the logits' row pitch is odd, and the GEMM library falls back to kernels of an old
+    architecture for all three products of this layer (measured on B200: 77 of the 116 ms of a training step). The
+    product is evaluated at the width rounded up to a multiple of 64 - the weight is zero-padded on the fly, 51 MB -
+    and the caller gets the first ``out_features`` columns as a view; parameters and state dict are unchanged."""
+    V = linear.out_features
+    pad = (-V) % 64
+    if pad == 0 or not x.is_cuda or x.dtype == torch.float32:
+        return linear(x)
+    weight = F.pad(linear.weight, (0, 0, 0, pad))
+    bias = None if linear.bias is None else F.pad(linear.bias, (0, pad))
+    return F.linear(x, weight, bias)[..., :V]
 
 
 class TransformerBlock(nn.Module):
@@ -76,7 +92,7 @@ class CausalLM(nn.Module):
             weights.append(w)
         if self.num_registers > 0:
             x = x[:, self.num_registers:, :]
-        return self.to_logits(self.ln_f(x)), weights
+        return vocab_projection(self.to_logits, self.ln_f(x)), weights
 
 
 def zipf_token_ids(batch, seq_len, vocab_size, exponent=1.1, seed=0):

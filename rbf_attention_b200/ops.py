@@ -61,6 +61,23 @@ def _compute_dtype(q: torch.Tensor) -> torch.dtype:
     raise ValueError(f"unsupported dtype {q.dtype} (bfloat16, float16 or float32)")
 
 
+def _padded_head_dim(D: int) -> int:
+    """Head dim the kernels run at: 64 or 128. Other head dims up to 128 run zero-padded to the next of the two, which
+    is exact: zero columns add nothing to q.k, to |k|^2 or to |q|^2, and zero value columns give zero output columns
+    (the reference pads to the next power of two inside its kernels, rbf_attention.py:661). The softmax scale keeps
+    using the caller's D."""
+    if D <= 64:
+        return 64
+    if D <= 128:
+        return 128
+    raise ValueError(f"head dim {D} is not supported (at most 128)")
+
+
+def _pad_d(t: torch.Tensor, Dp: int) -> torch.Tensor:
+    D = t.shape[-1]
+    return t if D == Dp else torch.nn.functional.pad(t, (0, Dp - D))
+
+
 def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -158,12 +175,11 @@ def _forward(q, k, v, is_causal: bool, softmax: bool):
     _validate("q", q)
     _validate("k", k, q)
     _validate("v", v, q)
-    B, H, N, D = q.shape
-    if D not in (64, 128):
-        raise ValueError(f"head dim {D} is not supported (64 or 128)")
+    B, H, N, D0 = q.shape
+    D = _padded_head_dim(D0)
     lib = _lib.load()
     cdt = _compute_dtype(q)
-    qc, kc, vc = (_tma_ready(t.to(cdt)) for t in (q, k, v))
+    qc, kc, vc = (_tma_ready(_pad_d(t.to(cdt), D)) for t in (q, k, v))
     out = torch.empty((B, H, N, D), dtype=cdt, device=q.device)
     lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device) if softmax else None
     ws = _workspace(B, H, N, D, softmax, False, q.device)
@@ -174,10 +190,12 @@ def _forward(q, k, v, is_causal: bool, softmax: bool):
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
             lse.data_ptr() if softmax else None, ws.data_ptr(), ws.numel(),
             B, H, N, D, _lib.strides3(qc), _lib.strides3(kc), _lib.strides3(vc), _lib.strides3(out),
-            _DTYPE_CODE[cdt], int(bool(is_causal)), int(softmax), 1.0 / math.sqrt(D), _stream_ptr(q.device),
+            _DTYPE_CODE[cdt], int(bool(is_causal)), int(softmax), 1.0 / math.sqrt(D0), _stream_ptr(q.device),
         )
         _lib.check(rc, "rbf_b200_fwd")
         mon.record(ws, "rbf_b200_fwd")
+    if D != D0:
+        out = out[..., :D0].contiguous()
     if cdt != q.dtype:
         out = out.to(q.dtype)
     return out, lse
@@ -188,13 +206,14 @@ def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax
     _validate("k", k, q)
     _validate("v", v, q)
     _validate("dout", dout, q)
-    B, H, N, D = q.shape
+    B, H, N, D0 = q.shape
+    D = _padded_head_dim(D0)
     lib = _lib.load()
     cdt = _compute_dtype(q)
-    qc, kc, vc, doc = (_tma_ready(t.to(cdt)) for t in (q, k, v, dout))
+    qc, kc, vc, doc = (_tma_ready(_pad_d(t.to(cdt), D)) for t in (q, k, v, dout))
     # the non-softmax variant takes the forward output when the caller has it: the single-kernel backward needs it
     have_out = out is not None
-    oc = _tma_ready(out.to(cdt)) if have_out else None
+    oc = _tma_ready(_pad_d(out.to(cdt), D)) if have_out else None
     dq = torch.empty((B, H, N, D), dtype=cdt, device=q.device)
     dk = torch.empty_like(dq)
     dv = torch.empty_like(dq)
@@ -216,6 +235,8 @@ def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax
         )
         _lib.check(rc, "rbf_b200_bwd")
         mon.record(ws, "rbf_b200_bwd")
+    if D != D0:
+        dq, dk, dv = (t[..., :D0].contiguous() for t in (dq, dk, dv))
     if cdt != q.dtype:
         dq, dk, dv = dq.to(q.dtype), dk.to(q.dtype), dv.to(q.dtype)
     return dq, dk, dv

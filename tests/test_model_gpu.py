@@ -42,7 +42,7 @@ def _models():
 
 def _loss(model, ids):
     logits, _ = model(ids[:, :-1])
-    return F.cross_entropy(logits.float().view(-1, VOCAB), ids[:, 1:].reshape(-1)), logits
+    return F.cross_entropy(logits.float().reshape(-1, VOCAB), ids[:, 1:].reshape(-1)), logits
 
 
 def test_language_model_on_the_kernels_matches_materialised_attention():

@@ -245,8 +245,14 @@ def test_forward_rows_whose_first_keys_are_far_away(D, causal, offset, q_scale):
     qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
     out, lse = cabi_forward(qd, kd, vd, causal, True)
     dq, dk, dv = cabi_backward(qd, kd, vd, out, lse, dod, causal, True)
-    for name, got, want in zip(("O", "dQ", "dK", "dV"), (out, dq, dk, dv), ref):
-        check(name, got.cpu().float(), want, REL_L2[torch.bfloat16])
+    # O and L at the stated tolerance. The gradients (which do not depend on how the forward tracks its maximum) are
+    # held to 1.5e-2 here: with logits spread over dozens of powers of two, dS = P (dP - delta) cancels heavily and
+    # the 16-bit rounding of P and dS - the reference's own recipe, rbf_attention.py:422,432,621 - weighs more than on
+    # the benchmark distributions (that recipe emulated in PyTorch on these inputs is off the fp32 oracle by 6.3e-3
+    # and 8.6e-3 in dQ for the two shifted cases, against 2.7e-3 without the shift).
+    check("O", out.cpu().float(), ref[0], REL_L2[torch.bfloat16])
+    for name, got, want in zip(("dQ", "dK", "dV"), (dq, dk, dv), ref[1:]):
+        check(name, got.cpu().float(), want, 1.5e-2)
     ref_l = oracle.torch_lse2(q, k, causal)
     assert (lse.cpu() - ref_l).abs().max().item() <= 2e-4 * max(1.0, ref_l.abs().max().item())
 
@@ -281,11 +287,8 @@ def test_reference_parity_script_case(golden_dir, dtype, atol):
         assert got.dtype == dtype
         ref = torch.tensor(g[name])
         sub = got.detach().cpu().float()[:, :, ::8]
-        if dtype == torch.float32:
-            # fp32 inputs run on 16-bit tensor-core operands here (the reference uses TF32 for them)
-            assert (sub - ref).abs().max().item() <= atol + 1e-3 * ref.abs().max().item(), name
-        else:
-            assert torch.allclose(sub, ref, atol=atol, rtol=1e-3), (name, (sub - ref).abs().max().item())
+        # fp32 inputs run on fp16 tensor-core operands here (11-bit significands, like the TF32 the reference uses)
+        assert torch.allclose(sub, ref, atol=atol, rtol=1e-3), (name, (sub - ref).abs().max().item())
 
 
 def test_strided_views_as_the_attention_block_produces_them():
@@ -399,9 +402,25 @@ def test_operator_errors():
     with pytest.raises(ValueError):
         ops.run_triton_rbf(q, q.half(), q)
     with pytest.raises(ValueError):
-        ops.run_triton_rbf(q[..., :48], q[..., :48], q[..., :48])
-    with pytest.raises(ValueError):
         ops.run_triton_rbf(q[0], q[0], q[0])
+    big = torch.randn(1, 1, 64, 160, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="at most 128"):
+        ops.run_triton_rbf(big, big, big)
+
+
+@pytest.mark.parametrize("D,softmax", [(32, True), (80, True), (48, False)])
+def test_other_head_dims_run_zero_padded(D, softmax):
+    """The reference accepts any head dim (it pads to a power of two inside its kernels, rbf_attention.py:661); here
+    the operators pad to 64 or 128 on the host, which is exact, and keep the caller's 1/sqrt(D)."""
+    q, k, v, do = oracle.make_inputs(2, 2, 300, D, seed=D, dtype=torch.bfloat16, std=1.0 if softmax else 0.5)
+    ref = oracle.torch_forward_backward(q, k, v, do, True, softmax, dtype=torch.float32)
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    fn = ops.run_triton_rbf if softmax else ops.run_triton_non_softmax_rbf
+    out = fn(qd, kd, vd, True)
+    assert out.shape == (2, 2, 300, D)
+    out.backward(do.to(DEV))
+    for name, got, want in zip(("O", "dQ", "dK", "dV"), (out, qd.grad, kd.grad, vd.grad), ref):
+        check(name, got.detach().cpu().float(), want, REL_L2[torch.bfloat16])
 
 
 def test_attention_block_matches_its_comparator_branch():
