@@ -633,8 +633,9 @@ def lm_step_record(torch, dist, rank, world, local_rank, steps, warmup, compile_
     loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
 
     def step(ids):
-        logits, _ = net(ids[:, :-1])
-        loss = torch.nn.functional.cross_entropy(logits.reshape(-1, LM["vocab"]), ids[:, 1:].reshape(-1))
+        # the logits keep the vocabulary's padding to a multiple of 64 (-inf columns: same loss, no strided copies)
+        logits, _ = net(ids[:, :-1], padded_logits=True)
+        loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), ids[:, 1:].reshape(-1))
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)

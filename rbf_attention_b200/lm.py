@@ -13,17 +13,23 @@ import torch.nn.functional as F
 from .attention import CustomCausalAttention
 
 
-def vocab_projection(linear: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+def vocab_projection(linear: nn.Linear, x: torch.Tensor, keep_padding: bool = False) -> torch.Tensor:
     """``linear(x)`` for an output width (the vocabulary) whose rows are not 16-byte aligned in 16-bit types. With the
     reference's vocabulary of 50257 the logits' row pitch is odd, and the GEMM library falls back to kernels of an old
     architecture for all three products of this layer (measured on B200: 77 of the 116 ms of a training step). The
     product is evaluated at the width rounded up to a multiple of 64 - the weight is zero-padded on the fly, 51 MB -
-    and the caller gets the first ``out_features`` columns as a view; parameters and state dict are unchanged."""
+    and the caller gets the first ``out_features`` columns as a view; parameters and state dict are unchanged.
+    With ``keep_padding`` the padded width is returned as it is, the extra columns holding -inf (probability zero,
+    gradient zero): a loss evaluated on it equals the loss on the sliced logits and saves the copies a strided view of
+    6.6 GB of logits costs on its way through log-softmax and back."""
     V = linear.out_features
     pad = (-V) % 64
     if pad == 0 or not x.is_cuda or x.dtype == torch.float32:
         return linear(x)
     weight = F.pad(linear.weight, (0, 0, 0, pad))
+    if keep_padding:
+        bias = torch.zeros(V, dtype=x.dtype, device=x.device) if linear.bias is None else linear.bias
+        return F.linear(x, weight, F.pad(bias, (0, pad), value=float("-inf")))
     bias = None if linear.bias is None else F.pad(linear.bias, (0, pad))
     return F.linear(x, weight, bias)[..., :V]
 
@@ -79,7 +85,9 @@ class CausalLM(nn.Module):
         self.ln_f = nn.LayerNorm(d_model)
         self.to_logits = nn.Linear(d_model, vocab_size)
 
-    def forward(self, idx):
+    def forward(self, idx, padded_logits: bool = False):
+        """Returns (logits, attention weights per block). ``padded_logits`` (not in the reference): the logits keep the
+        vocabulary rounded up to a multiple of 64 with -inf in the extra columns, see ``vocab_projection``."""
         bsz, seq = idx.shape
         x = self.token_emb(idx)
         if self.pos_emb_type == "learned":
@@ -92,7 +100,7 @@ class CausalLM(nn.Module):
             weights.append(w)
         if self.num_registers > 0:
             x = x[:, self.num_registers:, :]
-        return vocab_projection(self.to_logits, self.ln_f(x)), weights
+        return vocab_projection(self.to_logits, self.ln_f(x), keep_padding=padded_logits), weights
 
 
 def zipf_token_ids(batch, seq_len, vocab_size, exponent=1.1, seed=0):

@@ -65,6 +65,26 @@ def test_language_model_on_the_kernels_matches_materialised_attention():
         assert rep["rel_l2"] <= 8e-2, (name, rep)
 
 
+def test_padded_logits_give_the_same_loss_and_gradients():
+    """``padded_logits=True`` (what the benchmark's training step uses) against the sliced logits of the reference's
+    interface: same loss, same gradients."""
+    _, a = _models()
+    _, b = _models()
+    ids = lm.zipf_token_ids(2, 1025, VOCAB, seed=9).to(DEV)
+    la, logits_a = _loss(a, ids)
+    la.backward()
+    logits_b, _ = b(ids[:, :-1], padded_logits=True)
+    assert logits_b.shape[-1] == 1024 and logits_a.shape[-1] == VOCAB
+    assert torch.isinf(logits_b[..., VOCAB:]).all() and torch.equal(logits_b[..., :VOCAB], logits_a)
+    lb = F.cross_entropy(logits_b.float().view(-1, 1024), ids[:, 1:].reshape(-1))
+    lb.backward()
+    assert abs(la.item() - lb.item()) <= 1e-6
+    for (name, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
+        assert torch.isfinite(pb.grad).all(), name
+        rep = oracle.error_report(pb.grad.float().cpu(), pa.grad.float().cpu())
+        assert rep["rel_l2"] <= 2e-3 or rep["max_abs"] <= 1e-6, (name, rep)      # dQ summation order differs run to run
+
+
 def test_compiled_training_step_equals_the_eager_one():
     _, eager = _models()
     _, compiled_src = _models()
