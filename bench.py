@@ -60,11 +60,17 @@ def config_of(name, w, world):
             "parallelism": f"bh-shard x{world}, no collective"}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the named kernel, from ncu captures of a reduced batch
-# scaled to the full batch (traffic grows in proportion to B): (read, write) bytes, batch divisor of the capture.
+# DRAM bytes (read, write) of ONE launch of the named kernel from ncu captures of a reduced batch, and the factor that
+# scales the capture to the full batch (traffic grows in proportion to B). Configuration 2: dram__bytes_read.sum and
+# dram__bytes_write.sum of a --set full capture; configurations 3 and 4: dram__bytes.sum.per_second x
+# gpu__time_duration.sum of a sections capture (read + write together).
 NCU_DRAM_BYTES = {
-    ("config2", "bwd_fused"): (109.726720e6, 30.068992e6, 4),
-    ("config2", "fwd"): (54.800640e6, 2.691584e6, 4),
+    ("config2", "bwd_fused"): (109.639680e6, 29.786880e6, 4),
+    ("config2", "fwd"): (54.870528e6, 3.142912e6, 4),
+    ("config3", "bwd_fused"): (0.256082e12 * 5.218400e-3, 0.0, 2),
+    ("config3", "fwd"): (1.167834e12 * 2.020160e-3, 0.0, 2),
+    ("config4", "bwd_fused"): (311.094650e9 * 451.008e-6, 0.0, 4),
+    ("config4", "fwd"): (327.947988e9 * 182.112e-6, 0.0, 4),
 }
 
 
