@@ -15,7 +15,9 @@
  *     for the dims (b, h, n), exactly what the reference passes to its kernels
  *     (rbf_attention.py:671-682). D must be 64 or 128. Base addresses must be 16-byte aligned and the
  *     strides multiples of 8 elements (TMA addressing).
- *   - dtype: 0 = bfloat16, 1 = float16. Accumulation is fp32. `lse` and the workspace are fp32.
+ *   - dtype: 0 = bfloat16, 1 = float16. Accumulation is fp32. `lse` and the workspace are fp32. The forward
+ *     also takes dtype 2 = float32 tensors at D = 64: TF32 tensor-core operands like the reference's Triton path for
+ *     fp32 inputs (rbf_attention.py:183), strides counted in fp32 elements (multiples of 4), fp32 output.
  *   - The library never allocates device memory: the caller passes a workspace of at least
  *     rbf_b200_workspace_bytes() bytes, 256-byte aligned, which the call may overwrite entirely.
  *   - Launches go to `stream` (a cudaStream_t passed as void*; NULL = legacy default stream) on the

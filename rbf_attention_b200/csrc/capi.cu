@@ -155,12 +155,73 @@ size_t rbf_b200_workspace_bytes(int B, int H, int N, int D, int softmax, int bac
   return carve(nullptr, B, H, N, D, softmax, backward).bytes;
 }
 
+// Forward for fp32 tensors on TF32 operands (dtype 2, head dim 64): the tensors' strides count fp32 elements.
+static int fwd_tf32(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
+                    size_t workspace_bytes, int B, int H, int N, int D, const int64_t* q_strides,
+                    const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides, int causal,
+                    int softmax, float sm_scale, void* stream_v, int phases) {
+  int rc;
+  if ((rc = check_common(B, H, N, 64, 0, sm_scale))) return rc;
+  if (D != 64) return fail(RBF_B200_ERR_BAD_ARGUMENT, "fp32 tensors (TF32 operands) are supported at head dim 64, got %d", D);
+  const void* ptrs[4] = {q, k, v, out};
+  const int64_t* strs[4] = {q_strides, k_strides, v_strides, o_strides};
+  const char* names[4] = {"q", "k", "v", "out"};
+  for (int t = 0; t < 4; ++t) {
+    if (ptrs[t] == nullptr || strs[t] == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "%s or its strides are NULL", names[t]);
+    if (reinterpret_cast<uintptr_t>(ptrs[t]) % 16 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "%s base address is not 16-byte aligned", names[t]);
+    const int ext[3] = {B, H, N};
+    for (int i = 0; i < 3; ++i)
+      if (ext[i] > 1 && (strs[t][i] <= 0 || strs[t][i] % 4 != 0))
+        return fail(RBF_B200_ERR_BAD_LAYOUT, "%s stride[%d] = %lld must be a positive multiple of 4 fp32 elements", names[t], i,
+                    static_cast<long long>(strs[t][i]));
+    if (N > 1 && strs[t][2] < D) return fail(RBF_B200_ERR_BAD_LAYOUT, "%s row stride is smaller than D", names[t]);
+  }
+  if (softmax && lse == nullptr) return fail(RBF_B200_ERR_BAD_ARGUMENT, "lse is NULL");
+  if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace is NULL or not 256-byte aligned");
+  const Workspace ws = carve(workspace, B, H, N, D, softmax, 0);       // same sizes: 32 bytes of slab per padded row
+  if (workspace_bytes < ws.bytes)
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, ws.bytes);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int n_pad = rbf::padded_rows(N);
+  const float c = sm_scale * rbf::kLog2e;
+  cudaError_t e = cudaSuccess;
+  if (phases & RBF_B200_PHASE_PREPASS) {
+    rbf::RowStatsF32Args r{};
+    r.k = static_cast<const float*>(k); set_strides(r.ks, k_strides);
+    if (!softmax) { r.q = static_cast<const float*>(q); set_strides(r.qs, q_strides); r.qsq_out = ws.row_bias; }
+    r.kslab_out = static_cast<float*>(ws.kslab); r.status_to_clear = ws.status;
+    r.B = B; r.H = H; r.N = N; r.n_pad = n_pad; r.scale = c; r.scale2 = 2.f * c;
+    e = rbf::launch_row_stats_f32(r, stream);
+    if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "pre-pass launch failed: %s", cudaGetErrorString(e));
+  }
+  if (!(phases & RBF_B200_PHASE_MAIN)) return RBF_B200_OK;
+  rbf::FwdArgs a{};
+  const void* bases[4] = {q, k, v, out};
+  CUtensorMap* maps[4] = {&a.tm_q, &a.tm_k, &a.tm_v, &a.tm_o};
+  const int rows[4] = {rbf::kTile, 64, 64, rbf::kTile};
+  for (int t = 0; t < 4; ++t) {
+    const int r = rbf::make_tmap_bhnd_f32(maps[t], bases[t], B, H, N, D, strs[t][0], strs[t][1], strs[t][2], rows[t]);
+    if (r != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for %s (code %d)", names[t], r);
+  }
+  const int sr = rbf::make_tmap_slab8_f32(&a.tm_kslab, ws.kslab, B * H, n_pad, 64);
+  if (sr != 0) return fail(RBF_B200_ERR_TENSOR_MAP, "cuTensorMapEncodeTiled failed for the key-norm slabs (code %d)", sr);
+  a.qsq = ws.row_bias; a.lse = lse; a.status = ws.status;
+  a.B = B; a.H = H; a.N = N; a.n_pad = n_pad; a.causal = causal ? 1 : 0; a.scale2 = 2.f * c; a.slab_w = 1.0f;
+  e = rbf::launch_fwd_tf32(a, softmax != 0, stream);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "forward launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
 int rbf_b200_fwd_phases(const void* q, const void* k, const void* v, void* out, float* lse, void* workspace,
                         size_t workspace_bytes, int B, int H, int N, int D, const int64_t* q_strides,
                         const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides, int dtype,
                         int causal, int softmax, float sm_scale, void* stream_v, int phases) {
   g_last_error[0] = 0;
   int rc;
+  if (dtype == 2)
+    return fwd_tf32(q, k, v, out, lse, workspace, workspace_bytes, B, H, N, D, q_strides, k_strides, v_strides,
+                    o_strides, causal, softmax, sm_scale, stream_v, phases);
   if ((rc = check_common(B, H, N, D, dtype, sm_scale))) return rc;
   if ((rc = check_tensor("q", q, q_strides, B, H, N, D))) return rc;
   if ((rc = check_tensor("k", k, k_strides, B, H, N, D))) return rc;

@@ -113,6 +113,22 @@ struct FwdArgs {
   float scale2;           // 2 * gamma * log2(e)
 };
 cudaError_t launch_fwd(const FwdArgs& a, bool bf16, int D, bool softmax, cudaStream_t stream);
+// fp32 tensors on TF32 operands, head dim 64 (tensor maps of fp32 tiles, slabs of 8 floats per row; slab_w unused)
+cudaError_t launch_fwd_tf32(const FwdArgs& a, bool softmax, cudaStream_t stream);
+
+// Pre-pass of the TF32 forward over fp32 K (and Q): key-norm bias slabs of 8 floats per row (three TF32 parts of
+// -c|k|^2 / scale2, -1e30 on padding rows) and, for the non-softmax variant, c|q|^2 per row (0 on padding rows).
+struct RowStatsF32Args {
+  const float* k;
+  const float* q;           // optional
+  int64_t ks[3], qs[3];
+  float* kslab_out;
+  float* qsq_out;           // optional
+  DeviceStatus* status_to_clear;
+  int B, H, N, n_pad;
+  float scale, scale2;
+};
+cudaError_t launch_row_stats_f32(const RowStatsF32Args& a, cudaStream_t stream);
 
 // Backward pass (two kernels: key-stationary dK/dV, query-stationary dQ).
 struct BwdArgs {

@@ -126,6 +126,58 @@ static cudaError_t launch_row_stats_t(RowStatsArgs a, cudaStream_t stream) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// Pre-pass of the TF32 forward (fp32 tensors, head dim 64)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float tf32_part(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+
+__global__ void __launch_bounds__(256) row_stats_f32_kernel(const RowStatsF32Args a) {
+  constexpr int D = 64;
+  constexpr int kLanesPerRow = D / 4;                 // 16 lanes x 16 bytes
+  constexpr int kRowsPerWarp = 32 / kLanesPerRow;     // 2
+  if (a.status_to_clear != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 64)
+    reinterpret_cast<unsigned int*>(a.status_to_clear)[threadIdx.x] = 0u;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / kLanesPerRow, part = lane % kLanesPerRow;
+  const int bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int row = (blockIdx.x * 8 + warp) * kRowsPerWarp + sub;
+  const bool valid = row < a.N;
+  float ksq = 0.f, qsq = 0.f;
+  if (valid) {
+    const float4 kv = *reinterpret_cast<const float4*>(a.k + b * a.ks[0] + h * a.ks[1] +
+                                                       static_cast<int64_t>(row) * a.ks[2] + part * 4);
+    ksq = kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w;
+    if (a.q != nullptr) {
+      const float4 qv = *reinterpret_cast<const float4*>(a.q + b * a.qs[0] + h * a.qs[1] +
+                                                         static_cast<int64_t>(row) * a.qs[2] + part * 4);
+      qsq = qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w;
+    }
+  }
+#pragma unroll
+  for (int o = kLanesPerRow / 2; o > 0; o >>= 1) {
+    ksq += __shfl_xor_sync(0xffffffffu, ksq, o);
+    qsq += __shfl_xor_sync(0xffffffffu, qsq, o);
+  }
+  if (part == 0 && row < a.n_pad) {
+    const int64_t out_row = static_cast<int64_t>(bh) * a.n_pad + row;
+    // three parts that the tensor core reads exactly (it keeps the upper 19 bits of an operand) and that add up to
+    // the fp32 value
+    const float x = valid ? -ksq * a.scale / a.scale2 : -1e30f;
+    const float hi = tf32_part(x), mid = tf32_part(x - hi), lo = tf32_part(x - hi - mid);
+    float4* dst = reinterpret_cast<float4*>(a.kslab_out + out_row * 8);
+    dst[0] = make_float4(hi, mid, lo, 0.f);
+    dst[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (a.qsq_out != nullptr) a.qsq_out[out_row] = valid ? qsq * a.scale : 0.f;
+  }
+}
+
+cudaError_t launch_row_stats_f32(const RowStatsF32Args& a, cudaStream_t stream) {
+  dim3 grid((a.n_pad + 15) / 16, a.B * a.H);
+  row_stats_f32_kernel<<<grid, 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
 // Fused q/k preparation of the attention block (see QkvPrepArgs)
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float load_param(const void* base, int64_t index, bool fp32, bool bf16) {

@@ -18,6 +18,7 @@ import torch
 from . import _lib
 
 _DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1}
+_F32_CODE = 2          # forward only: fp32 tensors on TF32 operands, head dim 64
 
 
 def _validate(name: str, t: torch.Tensor, like: torch.Tensor | None = None) -> None:
@@ -38,12 +39,13 @@ def _validate(name: str, t: torch.Tensor, like: torch.Tensor | None = None) -> N
 
 def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     """Returns ``t`` if the TMA engine can address it in place (unit stride on D, 16-byte aligned base,
-    strides of dims b, h, n multiples of 8 elements), else a contiguous copy. The reference assumes
+    strides of dims b, h, n multiples of 16 bytes), else a contiguous copy. The reference assumes
     ``stride(-1) == 1`` without checking (rbf_attention.py:111-138)."""
     B, H, N, D = t.shape
+    per16 = 16 // t.element_size()
     ok = t.stride(3) == 1 and t.data_ptr() % 16 == 0
     for ext, s in zip((B, H, N), t.stride()[:3]):
-        if ext > 1 and (s <= 0 or s % 8 != 0):
+        if ext > 1 and (s <= 0 or s % per16 != 0):
             ok = False
     if N > 1 and t.stride(2) < D:
         ok = False
@@ -54,9 +56,10 @@ def _compute_dtype(q: torch.Tensor) -> torch.dtype:
     if q.dtype in _DTYPE_CODE:
         return q.dtype
     if q.dtype == torch.float32:
-        # fp32 inputs run with fp16 tensor-core operands (11-bit significand, like the TF32 the reference's
-        # Triton path uses for them, rbf_attention.py:183) and fp32 accumulation. fp16's range limit applies:
-        # |x| must stay below 65504, which attention activations do by orders of magnitude.
+        # fp32 inputs: the forward at head dims up to 64 runs on TF32 operands (see _forward); everything else - the
+        # backward, head dims above 64 - runs with fp16 tensor-core operands (11-bit significand, like the TF32 the
+        # reference's Triton path uses for them, rbf_attention.py:183) and fp32 accumulation. There fp16's range
+        # limit applies: |x| must stay below 65504, which attention activations do by orders of magnitude.
         return torch.float16
     raise ValueError(f"unsupported dtype {q.dtype} (bfloat16, float16 or float32)")
 
@@ -178,7 +181,10 @@ def _forward(q, k, v, is_causal: bool, softmax: bool):
     B, H, N, D0 = q.shape
     D = _padded_head_dim(D0)
     lib = _lib.load()
-    cdt = _compute_dtype(q)
+    # fp32 tensors at head dim <= 64: TF32 operands, as the reference's Triton path uses for them (fp32's exponent range)
+    tf32 = q.dtype == torch.float32 and D == 64
+    cdt = torch.float32 if tf32 else _compute_dtype(q)
+    code = _F32_CODE if tf32 else _DTYPE_CODE[cdt]
     qc, kc, vc = (_tma_ready(_pad_d(t.to(cdt), D)) for t in (q, k, v))
     out = torch.empty((B, H, N, D), dtype=cdt, device=q.device)
     lse = torch.empty((B, H, N), dtype=torch.float32, device=q.device) if softmax else None
@@ -190,7 +196,7 @@ def _forward(q, k, v, is_causal: bool, softmax: bool):
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
             lse.data_ptr() if softmax else None, ws.data_ptr(), ws.numel(),
             B, H, N, D, _lib.strides3(qc), _lib.strides3(kc), _lib.strides3(vc), _lib.strides3(out),
-            _DTYPE_CODE[cdt], int(bool(is_causal)), int(softmax), 1.0 / math.sqrt(D0), _stream_ptr(q.device),
+            code, int(bool(is_causal)), int(softmax), 1.0 / math.sqrt(D0), _stream_ptr(q.device),
         )
         _lib.check(rc, "rbf_b200_fwd")
         mon.record(ws, "rbf_b200_fwd")

@@ -257,6 +257,45 @@ def test_forward_rows_whose_first_keys_are_far_away(D, causal, offset, q_scale):
     assert (lse.cpu() - ref_l).abs().max().item() <= 2e-4 * max(1.0, ref_l.abs().max().item())
 
 
+@pytest.mark.parametrize("B,H,N,causal,softmax", [(2, 3, 333, True, True), (1, 2, 1000, False, True), (1, 2, 640, True, False),
+                                                   (1, 1, 1, True, True), (1, 2, 1028, True, True)])
+def test_fp32_forward_on_tf32_operands(B, H, N, causal, softmax):
+    """dtype 2 of rbf_b200_fwd: fp32 tensors, TF32 operands, D = 64 (the reference's path for fp32 inputs,
+    rbf_attention.py:183). Tolerance: TF32 has fp16's 10-bit significand, and the tensor core truncates Q and K to it
+    instead of rounding: relative L2 <= 3e-3 against the fp32 oracle (measured 0.8e-3 to 1.5e-3), L to 3e-3 of its range;
+    values beyond fp16's range (V scaled by 1e6) must work, which the fp16 operand path cannot do."""
+    lib = _lib.load()
+    D = 64
+    std = 1.0 if softmax else 0.5
+    q, k, v, _ = oracle.make_inputs(B, H, N, D, seed=N, dtype=torch.float32, std=std, key_norm_sigma=0.3 if softmax else 0.0)
+    for scale in ((1.0, 1e6) if N == 333 else (1.0,)):
+        qs, ks, vs = q, k, v * scale
+        ref_o = oracle.torch_forward(qs, ks, vs, causal, softmax)
+        qd, kd, vd = (t.to(DEV) for t in (qs, ks, vs))
+        out = torch.empty((B, H, N, D), dtype=torch.float32, device=DEV)
+        lse = torch.empty((B, H, N), dtype=torch.float32, device=DEV)
+        nbytes = lib.rbf_b200_workspace_bytes(B, H, N, D, int(softmax), 0)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.rbf_b200_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), lse.data_ptr(), ws.data_ptr(),
+                              nbytes, B, H, N, D, _s3(qd), _s3(kd), _s3(vd), _s3(out), 2, int(causal), int(softmax),
+                              1.0 / math.sqrt(D), stream)
+        assert rc == 0, lib.rbf_b200_last_error()
+        code = ctypes.c_uint(0)
+        assert lib.rbf_b200_read_device_status(ws.data_ptr(), stream, ctypes.byref(code)) == 0, lib.rbf_b200_last_error()
+        rep = oracle.error_report(out.cpu(), ref_o)
+        assert torch.isfinite(out).all()
+        assert rep["rel_l2"] <= 3e-3 or rep["max_abs"] <= 1e-6 * scale, (scale, rep)
+        if softmax:
+            ref_l = oracle.torch_lse2(qs, ks, causal)
+            assert (lse.cpu() - ref_l).abs().max().item() <= 3e-3 * max(1.0, ref_l.abs().max().item())
+    # the operator takes this path for fp32 tensors and returns fp32
+    if softmax:
+        o2 = ops.run_triton_rbf(q.to(DEV), k.to(DEV), v.to(DEV), causal)
+        assert o2.dtype == torch.float32
+        assert oracle.error_report(o2.cpu(), oracle.torch_forward(q, k, v, causal, softmax))["rel_l2"] <= 3e-3
+
+
 def test_golden_fixture_small(golden_dir):
     """attn_small.npz holds the reference's fp32 results; the kernel sees the same inputs rounded to bf16."""
     g = np.load(os.path.join(golden_dir, "attn_small.npz"))
