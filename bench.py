@@ -286,15 +286,30 @@ GEMMS = {"fwd": 2, "bwd_fused": 5}
 
 
 def timed_workload(torch, runner, w, steps, warmup, local_rank):
-    """Warm-up, then the whole step and its phases with CUDA events. Returns (ms per step, phase times, clocks)."""
+    """Warm-up, then the whole step with CUDA events (the headline), then - directly afterwards, in the same clock
+    and power state - the same number of steps once more with events between the kernels of each step, which gives the
+    average duration of every phase over steps like the timed ones (a loop over one phase alone, run after a long
+    sequence of others, lands in a different power state: on a 1 kW part the clocks drop after about 100 ms of load and
+    the same kernel then measures up to 14 % slower). Returns (ms per step, phase times, clocks)."""
     for _ in range(max(warmup, 3)):
         runner.step()
     runner.check_status()
     with ClockSampler(local_rank) as clocks:
         ms = time_loop(torch, runner.step, steps)
-        phase_ms = {"fwd": time_loop(torch, lambda: runner.fwd(2), steps),
-                    "bwd_fused": time_loop(torch, lambda: runner.bwd(2), steps),
-                    "prepass": time_loop(torch, lambda: (runner.fwd(1), runner.bwd(1)), steps)}
+        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(steps)]
+        for ev in marks:
+            ev[0].record()
+            runner.fwd(1)
+            ev[1].record()
+            runner.fwd(2)
+            ev[2].record()
+            runner.bwd(1)
+            ev[3].record()
+            runner.bwd(6)
+            ev[4].record()
+        torch.cuda.synchronize()
+    seg = [sum(ev[i].elapsed_time(ev[i + 1]) for ev in marks) / steps for i in range(4)]
+    phase_ms = {"fwd": seg[1], "bwd_fused": seg[3], "prepass": seg[0] + seg[2]}
     runner.check_status()
     return ms, phase_ms, clocks.summary()
 
