@@ -122,6 +122,11 @@ class _StatusMonitor:
         code = int(self.host[i]) & 0xFFFFFFFF
         if code != 0:
             self.host[i] = 0
+            if self.what[i].startswith("range:"):
+                raise RuntimeError(
+                    f"{self.what[i][6:]}: float32 inputs exceed float16's range (|x| >= 65504) on a path that runs on "
+                    "float16 tensor-core operands; its results contain inf / nan. Scale the inputs or use bfloat16"
+                )
             raise RuntimeError(
                 f"{self.what[i]}: a device-side wait ran out (site {code >> 24}, work unit {code & 0xFFFFFF}); "
                 "the results of that call are incomplete"
@@ -136,6 +141,16 @@ class _StatusMonitor:
             elif not ev.query():
                 break
             self._retire_oldest()
+
+    def record_range_check(self, tensors, what):
+        """fp32 tensors narrowed to fp16 operands: records (asynchronously, like the status word) whether the
+        conversion overflowed, so that a later call raises instead of inf / nan passing silently."""
+        flag = torch.zeros(4, dtype=torch.uint8, device=tensors[0].device)
+        bad = tensors[0].new_zeros((), dtype=torch.bool)
+        for t in tensors:
+            bad = bad | torch.isinf(t).any()
+        flag[0] = bad
+        self.record(flag, "range:" + what)
 
     def record(self, ws, what):
         if torch.cuda.is_current_stream_capturing():
@@ -200,6 +215,8 @@ def _forward(q, k, v, is_causal: bool, softmax: bool):
         )
         _lib.check(rc, "rbf_b200_fwd")
         mon.record(ws, "rbf_b200_fwd")
+        if q.dtype == torch.float32 and not tf32:
+            mon.record_range_check((qc, kc, vc), "rbf_b200_fwd")
     if D != D0:
         out = out[..., :D0].contiguous()
     if cdt != q.dtype:
@@ -241,6 +258,8 @@ def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax
         )
         _lib.check(rc, "rbf_b200_bwd")
         mon.record(ws, "rbf_b200_bwd")
+        if q.dtype == torch.float32:
+            mon.record_range_check((qc, kc, vc, doc), "rbf_b200_bwd")
     if D != D0:
         dq, dk, dv = (t[..., :D0].contiguous() for t in (dq, dk, dv))
     if cdt != q.dtype:

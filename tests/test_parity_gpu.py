@@ -296,6 +296,26 @@ def test_fp32_forward_on_tf32_operands(B, H, N, causal, softmax):
         assert oracle.error_report(o2.cpu(), oracle.torch_forward(q, k, v, causal, softmax))["rel_l2"] <= 3e-3
 
 
+def test_fp32_inputs_beyond_fp16_range_are_reported():
+    """fp32 tensors run their backward (and head dims above 64 their forward) on fp16 operands. Values at or beyond
+    65504 overflow there; the operators record that and raise from a later call or from check_device_status()
+    instead of letting inf / nan pass silently. The TF32 forward itself takes such values."""
+    q, k, v, do = (t.to(DEV) for t in oracle.make_inputs(1, 2, 200, 64, seed=8, dtype=torch.float32))
+    v_big = (v * 1e6).requires_grad_(True)
+    qa, ka = q.clone().requires_grad_(True), k.clone().requires_grad_(True)
+    out = ops.run_triton_rbf(qa, ka, v_big, True)
+    assert torch.isfinite(out).all()                     # TF32 forward: fp32 range
+    ops.check_device_status()
+    out.backward(do)                                     # backward on fp16 operands: v overflows
+    with pytest.raises(RuntimeError, match="float16's range"):
+        ops.check_device_status()
+    ops.check_device_status()                            # reported once
+    # in range: nothing is reported
+    qa, ka, va = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ops.run_triton_rbf(qa, ka, va, True).backward(do)
+    ops.check_device_status()
+
+
 def test_golden_fixture_small(golden_dir):
     """attn_small.npz holds the reference's fp32 results; the kernel sees the same inputs rounded to bf16."""
     g = np.load(os.path.join(golden_dir, "attn_small.npz"))
