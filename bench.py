@@ -376,6 +376,106 @@ def also_attention(torch, device, local_rank, peak, peak_src, steps):
     return out
 
 
+def also_layer(torch, device):
+    """The reference's layer benchmark (its rbf_attention.py run_layer_benchmarks: CustomCausalAttention with 8 heads
+    x 64, fp16, batch 4, "RBF Triton + SuSiE" with and without XSA; forward under no_grad, backward = forward+backward
+    - forward) on the block operator, and on the operator-by-operator path for comparison; plus the streaming
+    kernels of the block (q/k preparation, its parameter gradients, XSA) alone against the HBM roofline."""
+    import ctypes as ct
+
+    from rbf_attention_b200 import _lib, attention
+
+    out = {"dtype": "fp16", "batch": 4, "heads": 8, "head_dim": 64, "by_N": {}}
+    fused_flag = attention.CustomCausalAttention._fused_block
+    try:
+        for n in (1024, 2048, 4096, 8192):
+            x = torch.randn(4, n, 512, device=device, dtype=torch.float16, requires_grad=True)
+            dout = torch.randn_like(x)
+            rec = {}
+            for label, xsa, fused in (("block_operator", False, True), ("operator_by_operator", False, False),
+                                      ("block_with_xsa", True, True)):
+                torch.manual_seed(0)
+                layer = attention.CustomCausalAttention(8, 512, max_seq_len=8192, use_rope=True, attention_type="rbf_triton",
+                                                        apply_xsa=xsa).to(device, torch.float16)
+                attention.CustomCausalAttention._fused_block = fused_flag if fused else (lambda self, qkv: False)
+
+                def fwd_bwd():
+                    x.grad = None
+                    y, _ = layer(x)
+                    y.backward(dout)
+
+                for _ in range(3):
+                    fwd_bwd()
+                with torch.no_grad():
+                    fwd = time_loop(torch, lambda: layer(x)[0], 20)
+                both = time_loop(torch, fwd_bwd, 20)
+                rec[label] = {"fwd_ms": fwd, "bwd_ms": both - fwd}
+            out["by_N"][str(n)] = rec
+    except Exception as exc:
+        out["error"] = repr(exc)[:300]
+    finally:
+        attention.CustomCausalAttention._fused_block = fused_flag
+    # the block's streaming kernels at the language model's shape (B64 S1028 H8 D64, bf16): achieved HBM bandwidth
+    try:
+        lib = _lib.load()
+        B, S, H, D, R = 64, 1028, 8, 64, 4
+        E = H * D
+        qkv = torch.randn(B, S, 3 * E, device=device, dtype=torch.bfloat16)
+        pw = torch.rand(H, D // 2, device=device) + 0.2
+        rp = torch.randn(H, R, D, device=device) * 0.1
+        table = attention.get_unrotated_sinusoids(S, D, device).contiguous()
+        qk = torch.empty(2, B, S, H, D, device=device, dtype=torch.bfloat16)
+        q, k = qk[0].permute(0, 2, 1, 3), qk[1].permute(0, 2, 1, 3)
+        nb = lib.rbf_b200_workspace_bytes(B, H, S, D, 1, 0)
+        ws = torch.empty(nb, dtype=torch.uint8, device=device)
+        nb2 = lib.rbf_b200_qkv_prep_bwd_workspace_bytes(B, S, H, D, R)
+        ws2 = torch.empty(nb2, dtype=torch.uint8, device=device)
+        d_pw = torch.empty(H, D // 2, device=device)
+        d_rp = torch.empty(H, R, D, device=device)
+        o2 = torch.empty(B, H, S, D, device=device, dtype=torch.bfloat16)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        s3 = _lib.strides3
+        n_pad = (S + 127) // 128 * 128
+        tensor = B * S * E * 2
+
+        def prep():
+            _lib.check(lib.rbf_b200_qkv_prep(qkv.data_ptr(), pw.data_ptr(), rp.data_ptr(), 1, table.data_ptr(), q.data_ptr(),
+                                             k.data_ptr(), s3(q), s3(k), ws.data_ptr(), nb, B, S, H, D, R, 0, 1, 0.125, stream), "prep")
+
+        def prep_bwd():
+            _lib.check(lib.rbf_b200_qkv_prep_bwd(q.data_ptr(), k.data_ptr(), s3(q), s3(k), table.data_ptr(), d_pw.data_ptr(),
+                                                 d_rp.data_ptr(), ws2.data_ptr(), nb2, B, S, H, D, R, 0, stream), "prep_bwd")
+
+        def xsa():
+            _lib.check(lib.rbf_b200_xsa_fwd(q.data_ptr(), k.data_ptr(), o2.data_ptr(), s3(q), s3(k), s3(o2), B, H, S, D, 0, stream), "xsa")
+
+        def xsa_bwd():
+            _lib.check(lib.rbf_b200_xsa_bwd(o2.data_ptr(), q.data_ptr(), k.data_ptr(), qk[0].permute(0, 2, 1, 3).data_ptr(),
+                                            o2.data_ptr(), s3(o2), s3(q), s3(k), s3(q), s3(o2), B, H, S, D, 0, stream), "xsa_bwd")
+
+        hbm = None
+        path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(path):
+            with open(path) as fh:
+                hbm = float(json.load(fh).get("hbm_gbs", 0.0)) or None
+        kernels = {}
+        for name, fn, nbytes in (("qkv_prep", prep, 4 * tensor + B * H * n_pad * 32),        # read q, k; write q', k', slabs
+                                 ("qkv_prep_bwd", prep_bwd, 2 * tensor),                     # read dq', dk'
+                                 ("xsa_fwd", xsa, 3 * tensor), ("xsa_bwd", xsa_bwd, 5 * tensor)):
+            for _ in range(3):
+                fn()
+            ms = time_loop(torch, fn, 20)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            kernels[name] = {"ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs,
+                             "frac_of_hbm_peak": None if hbm is None else gbs / hbm}
+        out["streaming_kernels"] = {"shape": "B64 S1028 H8 D64 bf16 (one layer of configuration 5)", "hbm_peak_gbs": hbm,
+                                    "kernels": kernels}
+    except Exception as exc:
+        out["streaming_kernels"] = {"error": repr(exc)[:300]}
+    torch.cuda.empty_cache()
+    return out
+
+
 def gpu_baselines(torch, w, runner, steps=10):
     """The reference project's own GPU implementations on this GPU and workload, for comparison only: its Triton
     operators (JIT-compiled and autotuned here by the installed Triton) and its SDPA formulation on an augmented
@@ -544,6 +644,7 @@ def run_ours(args, w, rank, world, local_rank):
         torch.cuda.empty_cache()
         if world == 1:
             also.update(also_attention(torch, device, local_rank, peak, peak_src, max(10, min(args.steps, 20))))
+            also["reference_layer_benchmark"] = also_layer(torch, device)
         barrier()
         try:
             also["config5_lm"] = lm_step_record(torch, dist, rank, world, local_rank, steps=8, warmup=3, compile_model=False)

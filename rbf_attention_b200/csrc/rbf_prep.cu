@@ -281,26 +281,27 @@ int qkv_prep_bwd_chunks(int S, int R) { return (S - R + kPrepBwdRows - 1) / kPre
 
 template <bool kBf16>
 __global__ void __launch_bounds__(256) qkv_prep_bwd_partial_kernel(const QkvPrepBwdArgs a) {
-  extern __shared__ float s_cols[];              // H * D column sums of this block
+  extern __shared__ float s_cols[];              // groups x (H * D) column sums of this block
   const int D = a.D;
   const int lanes = D / 8;
-  const int cols = a.H * lanes;
+  const int cols = a.H * lanes;                  // 16-byte columns of one text row over all heads
+  const int groups = cols >= 256 ? 1 : 256 / cols;   // row groups: few columns leave threads for a split over the rows
   const int b = blockIdx.y;
   const int t0 = blockIdx.x * kPrepBwdRows;
   const int t1 = min(t0 + kPrepBwdRows, a.S - a.R);
-  float acc[kPrepBwdMaxSlots][8];
-#pragma unroll
-  for (int u = 0; u < kPrepBwdMaxSlots; ++u)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
 #pragma unroll
   for (int u = 0; u < kPrepBwdMaxSlots; ++u) {
-    const int c = threadIdx.x + u * 256;
-    if (c >= cols) break;
+    const int idx = threadIdx.x + u * 256;
+    if (idx >= cols * groups) break;
+    const int c = idx % cols, rg = idx / cols;
     const int h = c / lanes, part = c % lanes;
     const uint16_t* pq = reinterpret_cast<const uint16_t*>(a.dq) + b * a.dqs[0] + h * a.dqs[1] + part * 8;
     const uint16_t* pk = reinterpret_cast<const uint16_t*>(a.dk) + b * a.dks[0] + h * a.dks[1] + part * 8;
-    for (int t = t0; t < t1; ++t) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 4                                   // independent rows: keep several 16-byte loads in flight
+    for (int t = t0 + rg; t < t1; t += groups) {
       const uint4 x = *reinterpret_cast<const uint4*>(pq + static_cast<int64_t>(a.R + t) * a.dqs[2]);
       const uint4 y = *reinterpret_cast<const uint4*>(pk + static_cast<int64_t>(a.R + t) * a.dks[2]);
       const float4 w0 = *reinterpret_cast<const float4*>(a.table + static_cast<int64_t>(t) * D + part * 8);
@@ -310,48 +311,64 @@ __global__ void __launch_bounds__(256) qkv_prep_bwd_partial_kernel(const QkvPrep
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 f = unpack2<kBf16>(xw[i]), g = unpack2<kBf16>(yw[i]);
-        acc[u][2 * i] = fmaf(f.x + g.x, w[2 * i], acc[u][2 * i]);
-        acc[u][2 * i + 1] = fmaf(f.y + g.y, w[2 * i + 1], acc[u][2 * i + 1]);
+        acc[2 * i] = fmaf(f.x + g.x, w[2 * i], acc[2 * i]);
+        acc[2 * i + 1] = fmaf(f.y + g.y, w[2 * i + 1], acc[2 * i + 1]);
       }
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) s_cols[c * 8 + j] = acc[u][j];
+    float* mine = s_cols + (rg * cols + c) * 8;
+    *reinterpret_cast<float4*>(mine) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(mine + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
   __syncthreads();
-  // fold the sine half and the cosine half of every head onto the head's D/2 weights
+  // fold the row groups (fixed order), then the sine half and the cosine half of every head onto its D/2 weights
   const int half = D / 2;
   float* dst = a.partials + (static_cast<int64_t>(b) * gridDim.x + blockIdx.x) * a.H * half;
   for (int o = threadIdx.x; o < a.H * half; o += 256) {
     const int h = o / half, i = o % half;
-    dst[o] = s_cols[h * D + i] + s_cols[h * D + half + i];
+    float sum = 0.f;
+    for (int g = 0; g < groups; ++g) {
+      const float* src = s_cols + g * cols * 8;
+      sum += src[h * D + i] + src[h * D + half + i];
+    }
+    dst[o] = sum;
   }
 }
 
 template <bool kBf16>
-__global__ void __launch_bounds__(256) qkv_prep_bwd_final_kernel(const QkvPrepBwdArgs a) {
-  // blocks [0, nw): 32 weight gradients each, 8 lanes per output striding over the block partials;
-  // the remaining blocks: register-position gradients, one thread per element, summed over the batch
+__global__ void __launch_bounds__(1024) qkv_prep_bwd_final_kernel(const QkvPrepBwdArgs a) {
+  // blocks [0, nw): 32 weight gradients each; 32 partial-lanes per output stride over the block partials with four
+  // independent sums (the loads of a lane are independent: several stay in flight), then a fixed-order tree in shared
+  // memory. The remaining blocks: register-position gradients, one thread per element, summed over the batch.
   const int half = a.D / 2;
   const int n_out = a.H * half;
   const int nw = (n_out + 31) / 32;
   if (static_cast<int>(blockIdx.x) < nw) {
-    __shared__ float s_part[8][32];
-    const int o = blockIdx.x * 32 + (threadIdx.x & 31);
-    const int lane8 = threadIdx.x >> 5;
+    __shared__ float s_part[32][33];
+    const int col = threadIdx.x & 31, lane_p = threadIdx.x >> 5;
+    const int o = blockIdx.x * 32 + col;
     const int n_blocks = a.B * a.chunks;
-    float sum = 0.f;
-    if (o < n_out)
-      for (int p = lane8; p < n_blocks; p += 8) sum += a.partials[static_cast<int64_t>(p) * n_out + o];
-    s_part[lane8][threadIdx.x & 31] = sum;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    if (o < n_out) {
+      const float* src = a.partials + o;
+      int p = lane_p;
+      for (; p + 96 < n_blocks; p += 128) {
+        s0 += src[static_cast<int64_t>(p) * n_out];
+        s1 += src[static_cast<int64_t>(p + 32) * n_out];
+        s2 += src[static_cast<int64_t>(p + 64) * n_out];
+        s3 += src[static_cast<int64_t>(p + 96) * n_out];
+      }
+      for (; p < n_blocks; p += 32) s0 += src[static_cast<int64_t>(p) * n_out];
+    }
+    s_part[lane_p][col] = (s0 + s1) + (s2 + s3);
     __syncthreads();
     if (threadIdx.x < 32 && o < n_out) {
       float total = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) total += s_part[i][threadIdx.x];
+      for (int i = 0; i < 32; ++i) total += s_part[i][threadIdx.x];
       a.d_pos_weight[o] = total;
     }
   } else {
-    const int e = (blockIdx.x - nw) * 256 + threadIdx.x;
+    const int e = (blockIdx.x - nw) * 1024 + threadIdx.x;
     if (e >= a.H * a.R * a.D) return;
     const int d = e % a.D, r = (e / a.D) % a.R, h = e / (a.D * a.R);
     float sum = 0.f;
@@ -368,16 +385,17 @@ __global__ void __launch_bounds__(256) qkv_prep_bwd_final_kernel(const QkvPrepBw
 cudaError_t launch_qkv_prep_bwd(QkvPrepBwdArgs a, bool bf16, cudaStream_t stream) {
   if (a.H * (a.D / 8) > 256 * kPrepBwdMaxSlots) return cudaErrorInvalidValue;
   a.chunks = qkv_prep_bwd_chunks(a.S, a.R);
-  const int smem = a.H * a.D * sizeof(float);
+  const int cols = a.H * (a.D / 8);
+  const int smem = (cols >= 256 ? 1 : 256 / cols) * a.H * a.D * sizeof(float);
   dim3 grid(a.chunks, a.B);
   if (bf16) qkv_prep_bwd_partial_kernel<true><<<grid, 256, smem, stream>>>(a);
   else qkv_prep_bwd_partial_kernel<false><<<grid, 256, smem, stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int nw = (a.H * (a.D / 2) + 31) / 32;
-  const int nr = (a.H * a.R * a.D + 255) / 256;
-  if (bf16) qkv_prep_bwd_final_kernel<true><<<nw + nr, 256, 0, stream>>>(a);
-  else qkv_prep_bwd_final_kernel<false><<<nw + nr, 256, 0, stream>>>(a);
+  const int nr = (a.H * a.R * a.D + 1023) / 1024;
+  if (bf16) qkv_prep_bwd_final_kernel<true><<<nw + nr, 1024, 0, stream>>>(a);
+  else qkv_prep_bwd_final_kernel<false><<<nw + nr, 1024, 0, stream>>>(a);
   return cudaGetLastError();
 }
 
