@@ -526,7 +526,8 @@ def e2e_leg(torch, dist, runner, w, device, world, steps):
     """End to end through the public operator with host buffers. Three streams, double-buffered device inputs: the
     host->device copy of step s+1, the kernels of step s and the device->host copy of step s-1 overlap (PCIe is full
     duplex). Every step moves all of its inputs and all of its results across the bus inside the timed region.
-    Returns (ms per step, ms per step of the same loop with the kernels left out = the copy floor)."""
+    Returns (ms per step, ms per step of the same loop with the kernels left out = the copy floor, ms of one step's
+    transfers in the slower single direction with the bus otherwise idle)."""
     from rbf_attention_b200 import ops
 
     fn = ops.run_triton_rbf if w["softmax"] else ops.run_triton_non_softmax_rbf
@@ -590,7 +591,18 @@ def e2e_leg(torch, dist, runner, w, device, world, steps):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / steps
 
-    return timed(True), timed(False)
+    def one_way(to_device):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(4):
+            for d, h in zip(dev_in[0], (hq, hk, hv, hdo)):
+                (d if to_device else h).copy_(h if to_device else d, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 4
+
+    return timed(True), timed(False), max(one_way(True), one_way(False))
 
 
 def run_ours(args, w, rank, world, local_rank):
@@ -631,7 +643,7 @@ def run_ours(args, w, rank, world, local_rank):
 
     # ---- end to end through the public operator with host buffers -----------------------------
     e2e_steps = max(2, min(args.steps, 10))
-    e2e_ms, floor_ms = max_over_ranks(list(e2e_leg(torch, dist, runner, w, device, world, e2e_steps)))
+    e2e_ms, floor_ms, one_way_ms = max_over_ranks(list(e2e_leg(torch, dist, runner, w, device, world, e2e_steps)))
     tensor_bytes = runner.q.numel() * runner.q.element_size()
 
     # ---- the other configurations ---------------------------------------------------------------
@@ -671,7 +683,9 @@ def run_ours(args, w, rank, world, local_rank):
                     "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     # the same three-stream loop with the kernels left out: what the host link alone costs per step
-                    "copy_floor_ms": floor_ms},
+                    "copy_floor_ms": floor_ms,
+                    # one step's transfers in the slower direction with the bus otherwise idle (the hard lower bound)
+                    "copy_one_direction_ms": one_way_ms},
             "gpu_launches": LAUNCHES_PER_STEP * args.steps,
             "clocks": clocks,
         }

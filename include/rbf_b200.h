@@ -174,6 +174,13 @@ int rbf_b200_xsa_bwd(const void* g, const void* o, const void* v, void* d_o, voi
  * no device-side waits). */
 int rbf_b200_read_device_status(const void* workspace, void* stream, unsigned int* code);
 
+/* Asynchronous form of the status read: enqueues on `stream` a one-thread kernel that stores the status word at the
+ * start of `workspace` into `*host_slot`, a 4-byte slot in page-locked host memory that is mapped into the device's
+ * address space (cudaHostAlloc / cudaHostRegister; the function resolves the device-side address itself). Nothing
+ * synchronises and no copy engine is used, so the word is not queued behind the caller's own bulk transfers; the host
+ * reads the slot once an event recorded after this call has completed. No counterpart in the reference. */
+int rbf_b200_post_device_status(const void* workspace, unsigned int* host_slot, void* stream);
+
 /* Process-wide switch for run-to-run bitwise reproducible gradients. Off (default): the backward runs as one kernel
  * per call whose dQ partials are added in fp32 in arrival order (dQ then differs by rounding between runs; O, L, dK,
  * dV never do). On: the backward runs as the reference's two kernels (key-stationary dK/dV, rbf_attention.py:279-477,

@@ -60,6 +60,7 @@ SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint)],
     ),
+    "rbf_b200_post_device_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "rbf_b200_qkv_prep": (
         ctypes.c_int,
         [ctypes.c_void_p] * 3 + [ctypes.c_int] + [ctypes.c_void_p] * 3 + [_c_i64p] * 2 + [ctypes.c_void_p, ctypes.c_size_t]

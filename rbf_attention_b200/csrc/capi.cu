@@ -591,6 +591,22 @@ int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned 
   return RBF_B200_OK;
 }
 
+int rbf_b200_post_device_status(const void* workspace, unsigned int* host_slot, void* stream_v) {
+  g_last_error[0] = 0;
+  if (workspace == nullptr || host_slot == nullptr)
+    return fail(RBF_B200_ERR_BAD_ARGUMENT, "workspace and host_slot must not be NULL");
+  void* dev_ptr = nullptr;
+  cudaError_t e = cudaHostGetDevicePointer(&dev_ptr, host_slot, 0);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RBF_B200_ERR_BAD_ARGUMENT, "host_slot is not mapped page-locked host memory: %s", cudaGetErrorString(e));
+  }
+  e = rbf::launch_post_status(static_cast<const rbf::DeviceStatus*>(workspace), static_cast<unsigned int*>(dev_ptr),
+                              static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "status post failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
 int rbf_b200_set_deterministic(int on) { return g_deterministic.exchange(on ? 1 : 0); }
 
 int rbf_b200_get_deterministic(void) { return g_deterministic.load(); }

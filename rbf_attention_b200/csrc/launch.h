@@ -99,6 +99,8 @@ cudaError_t launch_xsa(const XsaArgs& a, bool backward, bool bf16, int D, cudaSt
 // SM clocks it records site kSiteSelfTest in `status` exactly as the attention kernels do, and the kernel returns.
 static constexpr uint32_t kSiteSelfTest = 250;
 cudaError_t launch_wait_selftest(DeviceStatus* status, long long limit, cudaStream_t stream);
+// One thread stores the status word into mapped page-locked host memory (device-side address of the slot).
+cudaError_t launch_post_status(const DeviceStatus* status, unsigned int* host_slot_device_ptr, cudaStream_t stream);
 
 // Forward pass. Tensor maps use a 64-element x 128-row box with the 128-byte swizzle.
 struct FwdArgs {

@@ -502,6 +502,20 @@ __global__ void __launch_bounds__(32) wait_selftest_kernel(DeviceStatus* status,
   if (threadIdx.x == 0) mbar_inval(&bar);
 }
 
+__global__ void __launch_bounds__(32) post_status_kernel(const DeviceStatus* status, unsigned int* host_slot) {
+  // a plain store into page-locked host memory mapped into the device's address space: no copy engine takes part,
+  // so the word arrives even while the engines are busy with the caller's own bulk transfers
+  if (threadIdx.x == 0) {
+    *reinterpret_cast<volatile unsigned int*>(host_slot) = status->code;
+    __threadfence_system();
+  }
+}
+
+cudaError_t launch_post_status(const DeviceStatus* status, unsigned int* host_slot_device_ptr, cudaStream_t stream) {
+  post_status_kernel<<<1, 32, 0, stream>>>(status, host_slot_device_ptr);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_wait_selftest(DeviceStatus* status, long long limit, cudaStream_t stream) {
   wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit);
   return cudaGetLastError();

@@ -96,9 +96,11 @@ class _StatusMonitor:
     """Surfaces device-side wait timeouts of the operator path without synchronising.
 
     Every kernel bounds its waits; one that runs out leaves a non-zero status word at the start of the call's
-    workspace and the kernels return with incomplete results. After each launch the word is copied (asynchronously,
-    on the launch stream) into a ring of pinned host slots; later calls look at the slots whose copy has completed
-    and raise ``RuntimeError`` for a non-zero one. A timeout is therefore reported by a later operator call or by
+    workspace and the kernels return with incomplete results. After each launch a one-thread kernel on the launch
+    stream stores the word into a ring of pinned host slots (a store through the mapped host address: a copy would
+    queue on the copy engine behind the caller's own device-to-host transfers and hold the launch stream up for
+    their duration); later calls look at the slots whose store has completed and raise ``RuntimeError`` for a
+    non-zero one. A timeout is therefore reported by a later operator call or by
     ``check_device_status()``, not by the call that suffered it. ``RBF_B200_SYNC_STATUS=1`` makes every call
     synchronise and check its own status (for debugging). Nothing is recorded while a CUDA graph is being captured.
     """
@@ -159,7 +161,8 @@ class _StatusMonitor:
             self.events[self.oldest].synchronize()
             self._retire_oldest()
         i = self.next
-        self.host[i : i + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
+        _lib.check(_lib.load().rbf_b200_post_device_status(
+            ws.data_ptr(), self.host.data_ptr() + 4 * i, _stream_ptr(ws.device)), "rbf_b200_post_device_status")
         ev = torch.cuda.Event()
         ev.record()
         self.events[i], self.what[i] = ev, what

@@ -186,6 +186,13 @@ def test_bounded_wait_runs_out_and_the_workspace_recovers():
     rc = lib.rbf_b200_read_device_status(ws.data_ptr(), stream, ctypes.byref(code))     # synchronises: the kernel is back
     assert rc == 6 and code.value >> 24 == 250 and code.value & 0xFFFFFF == 0
     assert b"wait ran out" in lib.rbf_b200_last_error()
+    # the asynchronous form: a kernel stores the word into mapped pinned host memory; pageable memory is refused
+    slot = torch.zeros(1, dtype=torch.int32).pin_memory()
+    assert lib.rbf_b200_post_device_status(ws.data_ptr(), slot.data_ptr(), stream) == 0, lib.rbf_b200_last_error()
+    torch.cuda.synchronize()
+    assert (int(slot[0]) & 0xFFFFFFFF) == code.value
+    pageable = torch.zeros(1, dtype=torch.int32)
+    assert lib.rbf_b200_post_device_status(ws.data_ptr(), pageable.data_ptr(), stream) == 1
     # main kernel only (no pre-pass, which would clear the word): every block sees the word and leaves
     out = torch.full((B, H, N, D), 7.0, dtype=torch.bfloat16, device=DEV)
     lse = torch.full((B, H, N), 7.0, dtype=torch.float32, device=DEV)
