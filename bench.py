@@ -786,7 +786,7 @@ def lm_step_record(torch, dist, rank, world, local_rank, steps, warmup, compile_
     def step(ids):
         # the logits keep the vocabulary's padding to a multiple of 64 (-inf columns: same loss, no strided copies)
         logits, _ = net(ids[:, :-1], padded_logits=True)
-        loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), ids[:, 1:].reshape(-1))
+        loss = lm.cross_entropy(logits, ids[:, 1:])         # loss and d(loss)/d(logits) from one kernel
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)

@@ -166,6 +166,22 @@ int rbf_b200_xsa_bwd(const void* g, const void* o, const void* v, void* d_o, voi
                      const int64_t* o_strides, const int64_t* v_strides, const int64_t* do_strides,
                      const int64_t* dv_strides, int B, int H, int N, int D, int dtype, void* stream);
 
+/* Cross entropy of the language-model training step: replaces torch.nn.CrossEntropyLoss(ignore_index=-100) and its
+ * backward (train_rbf_transformer.py:282, 335-345). One kernel reads the logits (rows x cols, row pitch `ld` elements,
+ * dtype 0 = bfloat16, 1 = float16, 2 = float32), writes loss_rows[r] = logsumexp(logits[r]) - logits[r, targets[r]] and
+ * dlogits[r, :] = (softmax(logits[r]) - onehot(targets[r])) * (*grad_scale), in the dtype of the logits with row pitch
+ * `ld_out`. `grad_scale` is a device scalar (the caller's 1 / number of counted rows), so that the mean loss's
+ * gradient needs no second pass. A row whose target equals `ignore_index` or lies outside [0, cols) gets loss 0 and a
+ * zero gradient. Columns holding -inf have probability and gradient zero. 16-byte aligned bases and pitches that are
+ * multiples of 16 bytes take the vector path; anything else runs element by element. */
+int rbf_b200_cross_entropy(const void* logits, const int64_t* targets, const float* grad_scale, float* loss_rows,
+                           void* dlogits, int rows, int cols, int64_t ld, int64_t ld_out, int64_t ignore_index,
+                           int dtype, void* stream);
+
+/* x[0..n) *= *factor, decided on the device: when *factor == 1 (the gradient of a loss that is the graph's output)
+ * the kernel returns without touching x. Used by the backward of the cross entropy above. */
+int rbf_b200_scale_unless_one(void* x, const float* factor, int64_t n, int dtype, void* stream);
+
 /* Synchronises `stream` and reads the device status word that the last call using `workspace` left:
  * 0 = ok, otherwise (site << 24 | work unit) of the bounded wait that ran out; the work unit is the linear block
  * index of the launch or, for the persistent backward kernel, the (key tile, batch-head) item. Returns

@@ -60,6 +60,13 @@ SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint)],
     ),
+    "rbf_b200_cross_entropy": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                 ctypes.c_void_p],
+    ),
+    "rbf_b200_scale_unless_one": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
+                                                 ctypes.c_void_p]),
     "rbf_b200_post_device_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "rbf_b200_qkv_prep": (
         ctypes.c_int,

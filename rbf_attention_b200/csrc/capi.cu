@@ -591,6 +591,42 @@ int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned 
   return RBF_B200_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Cross entropy of the language-model training step
+// ---------------------------------------------------------------------------------------------
+int rbf_b200_cross_entropy(const void* logits, const int64_t* targets, const float* grad_scale, float* loss_rows,
+                           void* dlogits, int rows, int cols, int64_t ld, int64_t ld_out, int64_t ignore_index,
+                           int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  if (rows < 0 || cols <= 0) return fail(RBF_B200_ERR_BAD_ARGUMENT, "rows must be >= 0 and cols > 0");
+  if (dtype < 0 || dtype > 2) return fail(RBF_B200_ERR_BAD_ARGUMENT, "dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
+  if (ld < cols || ld_out < cols) return fail(RBF_B200_ERR_BAD_ARGUMENT, "row pitches must be at least cols");
+  if (rows == 0) return RBF_B200_OK;
+  if (!logits || !targets || !grad_scale || !loss_rows || !dlogits)
+    return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL tensor pointer");
+  const int sms = sm_count();
+  if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
+  rbf::CrossEntropyArgs a{};
+  a.logits = logits; a.ld = ld; a.targets = targets; a.dlogits = dlogits; a.ld_out = ld_out;
+  a.loss_rows = loss_rows; a.grad_scale = grad_scale; a.rows = rows; a.cols = cols; a.ignore_index = ignore_index;
+  const cudaError_t e = rbf::launch_cross_entropy(a, dtype, sms, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "cross entropy launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+int rbf_b200_scale_unless_one(void* x, const float* factor, int64_t n, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  if (n < 0) return fail(RBF_B200_ERR_BAD_ARGUMENT, "n must be >= 0");
+  if (dtype < 0 || dtype > 2) return fail(RBF_B200_ERR_BAD_ARGUMENT, "dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
+  if (n == 0) return RBF_B200_OK;
+  if (!x || !factor) return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL pointer");
+  const int sms = sm_count();
+  if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
+  const cudaError_t e = rbf::launch_scale_unless_one(x, factor, n, dtype, sms, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "scale launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
 int rbf_b200_post_device_status(const void* workspace, unsigned int* host_slot, void* stream_v) {
   g_last_error[0] = 0;
   if (workspace == nullptr || host_slot == nullptr)

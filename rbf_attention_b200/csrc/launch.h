@@ -98,6 +98,22 @@ cudaError_t launch_xsa(const XsaArgs& a, bool backward, bool bf16, int D, cudaSt
 // Self-test of the bounded waits: one block waits on a barrier that nothing arms; when the wait runs out after `limit`
 // SM clocks it records site kSiteSelfTest in `status` exactly as the attention kernels do, and the kernel returns.
 static constexpr uint32_t kSiteSelfTest = 250;
+// Cross entropy of the language-model step (ce_loss.cu): per-row losses and d(mean loss)/d(logits) in one kernel.
+struct CrossEntropyArgs {
+  const void* logits;        // (rows, cols), row pitch ld elements
+  int64_t ld;
+  const int64_t* targets;    // (rows); ignore_index or out-of-range: the row has no loss and a zero gradient
+  void* dlogits;             // (rows, cols), row pitch ld_out elements, dtype of the logits
+  int64_t ld_out;
+  float* loss_rows;          // (rows)
+  const float* grad_scale;   // device scalar multiplied into every gradient (1 / number of rows that count)
+  int rows, cols;
+  int64_t ignore_index;
+};
+cudaError_t launch_cross_entropy(const CrossEntropyArgs& a, int dtype, int sms, cudaStream_t stream);
+// x *= *factor unless *factor == 1 (decided on the device: nothing synchronises).
+cudaError_t launch_scale_unless_one(void* x, const float* factor, int64_t n, int dtype, int sms, cudaStream_t stream);
+
 cudaError_t launch_wait_selftest(DeviceStatus* status, long long limit, cudaStream_t stream);
 // One thread stores the status word into mapped page-locked host memory (device-side address of the slot).
 cudaError_t launch_post_status(const DeviceStatus* status, unsigned int* host_slot_device_ptr, cudaStream_t stream);

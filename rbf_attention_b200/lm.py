@@ -34,6 +34,20 @@ def vocab_projection(linear: nn.Linear, x: torch.Tensor, keep_padding: bool = Fa
     return F.linear(x, weight, bias)[..., :V]
 
 
+def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """The training loss of the reference (``torch.nn.CrossEntropyLoss(ignore_index=-100)`` on flattened logits,
+    train_rbf_transformer.py:282, 340-345). CUDA logits go through the library's single-kernel loss + gradient
+    (``ops.cross_entropy``: one read and one write of the logits instead of four passes and an fp32 copy); anything
+    else (the CPU oracle runs of the tests) is PyTorch's."""
+    logits = logits.reshape(-1, logits.shape[-1])
+    targets = targets.reshape(-1)
+    if logits.is_cuda:
+        from . import ops
+
+        return ops.cross_entropy(logits, targets, ignore_index)
+    return F.cross_entropy(logits, targets, ignore_index=ignore_index)
+
+
 class TransformerBlock(nn.Module):
     def __init__(self, emb_dim, num_heads, max_seq_len, use_rope, attention_type, use_qk_norm=False, use_xsa=False,
                  num_registers=0):

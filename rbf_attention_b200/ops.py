@@ -654,6 +654,82 @@ def exclusive_self_attention(o, v):
 
 
 # ---------------------------------------------------------------------------------------------
+# Cross entropy of the language-model step (torch.nn.CrossEntropyLoss(ignore_index=-100),
+# train_rbf_transformer.py:282): loss and d(loss)/d(logits) from one kernel
+# ---------------------------------------------------------------------------------------------
+_CE_DTYPE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+@torch.library.custom_op("rbf_attn_b200::cross_entropy_fwd", mutates_args=())
+def cross_entropy_fwd(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Mean cross entropy over the rows whose target is not ``ignore_index`` (fp32 scalar) and its gradient with
+    respect to ``logits`` (same shape and dtype), from one pass: logits (rows, cols) with unit column stride,
+    targets (rows,) int64."""
+    if logits.dim() != 2 or targets.dim() != 1 or targets.shape[0] != logits.shape[0]:
+        raise ValueError(f"logits must be (rows, cols) and targets (rows,), got {tuple(logits.shape)}, {tuple(targets.shape)}")
+    if not logits.is_cuda or targets.device != logits.device:
+        raise RuntimeError("logits and targets must be CUDA tensors on one device: rbf_attention_b200 has no CPU path")
+    if logits.dtype not in _CE_DTYPE:
+        raise ValueError(f"unsupported dtype {logits.dtype} (bfloat16, float16 or float32)")
+    if targets.dtype != torch.int64:
+        raise ValueError(f"targets must be int64, got {targets.dtype}")
+    rows, cols = logits.shape
+    x = logits if logits.stride(1) == 1 and (rows <= 1 or logits.stride(0) >= cols) else logits.contiguous()
+    t = targets.contiguous()
+    counted = ((t != ignore_index) & (t >= 0) & (t < cols)).sum()
+    grad_scale = 1.0 / counted.to(torch.float32)          # no counted row: inf * 0 = nan, as torch's mean of nothing
+    loss_rows = torch.empty(rows, dtype=torch.float32, device=x.device)
+    dlogits = torch.empty((rows, cols), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().rbf_b200_cross_entropy(
+            x.data_ptr(), t.data_ptr(), grad_scale.data_ptr(), loss_rows.data_ptr(), dlogits.data_ptr(), rows, cols,
+            x.stride(0) if rows > 1 else cols, cols, int(ignore_index), _CE_DTYPE[x.dtype], _stream_ptr(x.device))
+    _lib.check(rc, "rbf_b200_cross_entropy")
+    return loss_rows.sum() * grad_scale, dlogits
+
+
+@cross_entropy_fwd.register_fake
+def _(logits, targets, ignore_index):
+    return logits.new_empty((), dtype=torch.float32), torch.empty_like(logits, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op("rbf_attn_b200::scale_unless_one_", mutates_args=("x",))
+def scale_unless_one_(x: torch.Tensor, factor: torch.Tensor) -> None:
+    """x *= factor (a one-element tensor) unless factor == 1, decided on the device."""
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    f = factor.reshape(1).to(device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().rbf_b200_scale_unless_one(x.data_ptr(), f.data_ptr(), x.numel(), _CE_DTYPE[x.dtype],
+                                                   _stream_ptr(x.device))
+    _lib.check(rc, "rbf_b200_scale_unless_one")
+
+
+def _ce_setup_context(ctx, inputs, output):
+    ctx.save_for_backward(output[1])
+    ctx.set_materialize_grads(False)        # no zero tensor of the logits' size for the unused second output
+
+
+def _ce_backward(ctx, g_loss, _g_dlogits):
+    # the gradient was formed by the forward; it is scaled in place (a no-op for the usual g_loss = 1), so a graph
+    # retained for a second backward pass with g_loss != 1 would see it scaled twice
+    if g_loss is None:
+        return None, None, None
+    (dlogits,) = ctx.saved_tensors
+    torch.ops.rbf_attn_b200.scale_unless_one_(dlogits, g_loss)
+    return dlogits, None, None
+
+
+torch.library.register_autograd("rbf_attn_b200::cross_entropy_fwd", _ce_backward, setup_context=_ce_setup_context)
+
+
+def cross_entropy(logits, targets, ignore_index: int = -100):
+    """``F.cross_entropy(logits, targets, ignore_index=ignore_index)`` (mean reduction) for 2-D CUDA logits, with the
+    gradient produced by the forward kernel."""
+    return torch.ops.rbf_attn_b200.cross_entropy_fwd(logits, targets, ignore_index)[0]
+
+
+# ---------------------------------------------------------------------------------------------
 # Wrappers with the reference's names (rbf_attention.py:848-853)
 # ---------------------------------------------------------------------------------------------
 def run_triton_rbf(q, k, v, is_causal=True):

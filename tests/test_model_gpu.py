@@ -45,6 +45,23 @@ def _loss(model, ids):
     return F.cross_entropy(logits.float().reshape(-1, VOCAB), ids[:, 1:].reshape(-1)), logits
 
 
+def test_training_loss_from_the_fused_kernel_equals_torchs():
+    """``lm.cross_entropy`` on the padded bf16 logits (what the benchmark's step uses) against ``F.cross_entropy`` on
+    the same logits in fp32: same loss (1e-5), same parameter gradients (relative L2 <= 5e-3: the logit gradients are rounded
+    to bf16 once in both, at slightly different points)."""
+    _, a = _models()
+    _, b = _models()
+    ids = lm.zipf_token_ids(2, 1025, VOCAB, seed=11).to(DEV)
+    la = F.cross_entropy(a(ids[:, :-1], padded_logits=True)[0].float().view(-1, 1024), ids[:, 1:].reshape(-1))
+    la.backward()
+    lb = lm.cross_entropy(b(ids[:, :-1], padded_logits=True)[0], ids[:, 1:])
+    lb.backward()
+    assert abs(la.item() - lb.item()) <= 1e-5 * max(1.0, abs(la.item())), (la.item(), lb.item())
+    for (name, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
+        rep = oracle.error_report(pb.grad.float().cpu(), pa.grad.float().cpu())
+        assert rep["rel_l2"] <= 5e-3 or rep["max_abs"] <= 1e-6, (name, rep)
+
+
 def test_language_model_on_the_kernels_matches_materialised_attention():
     slow, fast = _models()
     ids = lm.zipf_token_ids(2, 1025, VOCAB, seed=3)
@@ -105,6 +122,77 @@ def test_compiled_training_step_equals_the_eager_one():
     for name in g0:
         rep = oracle.error_report(g1[name].cpu(), g0[name].cpu())
         assert rep["rel_l2"] <= 2e-2, (name, rep)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,cols", [(64, 1024), (37, 1000), (5, 50257), (3, 17)])
+def test_cross_entropy_kernel_matches_torch(dtype, rows, cols):
+    """Loss and gradient of ``ops.cross_entropy`` against ``F.cross_entropy(ignore_index=-100)`` evaluated in fp64 on
+    the same (rounded) logits: vector path (aligned widths), element path (odd widths), ignored rows, -inf columns,
+    a non-unit upstream gradient. Tolerances: loss |diff| <= 2e-6 * max(1, loss); gradient within one rounding of
+    the output dtype per pass (bf16 8e-3, fp16 2e-3, fp32 5e-6 - a few ulps of an exponent of magnitude 16 -, relative to
+    the row's largest gradient)."""
+    from rbf_attention_b200 import ops
+
+    g = torch.Generator().manual_seed(rows * 100003 + cols)
+    logits = (torch.randn(rows, cols, generator=g) * 3.0).to(dtype)
+    if cols > 20:
+        logits[:, -3:] = float("-inf")                      # padded vocabulary columns
+    targets = torch.randint(0, cols - 3 if cols > 20 else cols, (rows,), generator=g)
+    targets[1] = -100
+    ref_in = logits.double().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, targets, ignore_index=-100)
+    (ref * 1.7).backward()
+    x = logits.to(DEV).requires_grad_(True)
+    loss = ops.cross_entropy(x, targets.to(DEV))
+    assert loss.dtype == torch.float32 and loss.dim() == 0
+    (loss * 1.7).backward()
+    ops.check_device_status()
+    assert abs(loss.item() - ref.item()) <= 2e-6 * max(1.0, abs(ref.item())) + 1e-6, (loss.item(), ref.item())
+    tol = {torch.bfloat16: 8e-3, torch.float16: 2e-3, torch.float32: 5e-6}[dtype]
+    got, want = x.grad.double().cpu(), ref_in.grad
+    assert torch.isfinite(got).all()
+    assert (got[1] == 0).all()                              # the ignored row
+    scale = want.abs().amax(dim=1, keepdim=True).clamp_min(1e-30)
+    assert ((got - want).abs() / scale).max().item() <= tol
+    # the usual case: the loss is the graph's output (upstream gradient exactly 1: the scaling pass is skipped)
+    x2 = logits.to(DEV).requires_grad_(True)
+    ops.cross_entropy(x2, targets.to(DEV)).backward()
+    assert ((x2.grad.double().cpu() * 1.7 - want).abs() / scale).max().item() <= 2 * tol
+
+
+def test_cross_entropy_through_the_c_abi_with_a_row_pitch():
+    """Raw pointers, a logits view with a row pitch larger than its width, every row ignored but two."""
+    from rbf_attention_b200 import _lib
+
+    lib = _lib.load()
+    rows, cols, ld = 16, 512, 640
+    torch.manual_seed(4)
+    store = torch.randn(rows, ld, device=DEV).to(torch.bfloat16)
+    targets = torch.full((rows,), -100, dtype=torch.int64, device=DEV)
+    targets[3], targets[9] = 7, 511
+    scale = torch.tensor([0.5], dtype=torch.float32, device=DEV)
+    loss_rows = torch.full((rows,), 9.0, dtype=torch.float32, device=DEV)
+    dl = torch.full((rows, cols), 9.0, dtype=torch.bfloat16, device=DEV)
+    rc = lib.rbf_b200_cross_entropy(store.data_ptr(), targets.data_ptr(), scale.data_ptr(), loss_rows.data_ptr(),
+                                    dl.data_ptr(), rows, cols, ld, cols, -100, 0,
+                                    torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.rbf_b200_last_error()
+    torch.cuda.synchronize()
+    x = store[:, :cols].double().cpu()
+    want_rows = torch.zeros(rows, dtype=torch.float64)
+    for r in (3, 9):
+        want_rows[r] = torch.logsumexp(x[r], 0) - x[r, targets[r].item()]
+    assert (loss_rows.double().cpu() - want_rows).abs().max().item() <= 2e-6 * 10
+    p = torch.softmax(x, 1)
+    for r in range(rows):
+        if r in (3, 9):
+            p[r, targets[r].item()] -= 1.0
+            assert (dl[r].double().cpu() - 0.5 * p[r]).abs().max().item() <= 4e-3 * 0.5
+        else:
+            assert (dl[r] == 0).all()
+    assert lib.rbf_b200_cross_entropy(store.data_ptr(), targets.data_ptr(), scale.data_ptr(), loss_rows.data_ptr(),
+                                      dl.data_ptr(), rows, cols, cols - 8, cols, -100, 0, None) == 1   # pitch < width
 
 
 def test_reference_parity_script_runs_unmodified():
