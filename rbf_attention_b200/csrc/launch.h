@@ -208,4 +208,20 @@ inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, PerDeviceFlags&
   return e;
 }
 
+// SM count of the current device (-1 on error), cached per device.
+inline int device_sm_count() {
+  static std::atomic<int> cached[PerDeviceFlags::kMaxDevices];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return -1;
+  const bool slot = dev < PerDeviceFlags::kMaxDevices;
+  if (slot) {
+    const int c = cached[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return -1;
+  if (slot) cached[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
 }  // namespace rbf
