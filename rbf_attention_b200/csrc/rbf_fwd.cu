@@ -190,7 +190,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int total = heads * blocks;
   // Items of this CTA: its first one is its block index (the launch never has more CTAs than items); in the
   // persistent launch the producer thread then takes further items from a launch-wide counter (work[0], zero at
-  // launch), one ahead of what it is loading, and hands each number to the other roles through a small ring in
+  // launch) once it has issued the current item's loads, and hands each number to the other roles through a small ring in
   // shared memory. Causal items come sorted by length, so the CTAs finish within one of the shortest items of each
   // other (a fixed assignment - items w, w + G, ... - left the first CTAs 7 % above the average at B4 H16 N8192).
   // -1 ends the sequence.
@@ -312,7 +312,6 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       uint32_t G = 0, qn[2] = {0, 0};
       bool ok = true;
       int w = static_cast<int>(blockIdx.x);
-      int w_next = take_item();                      // in flight while this item's tiles are loaded
       for (uint32_t n = 0; w >= 0 && ok && (kPersistent || n == 0); ++n) {
         const Item it = (n == 0) ? first_item : get_item<kKeys>(w, heads, blocks, H, N, causal);
         if (n != 0) {
@@ -338,17 +337,19 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
           load_values(it, j, st);
         }
+        if (!ok) break;
         G += it.nkt_max;
         for (int t = 0; t < 2; ++t) qn[t] += it.nkt[t] > 0 ? 1 : 0;
-        // publish the next item number (or the end of the sequence) and take the one after it
-        w = w_next;
+        // Take and publish the next item number (or the end of the sequence) only now: all loads of this item are
+        // issued, the other roles still have up to kStages key tiles of it ahead of them, which hides the counter's
+        // round trip; taking items earlier leaves the launch's last items reserved by CTAs that are still busy.
+        w = take_item();
         const int slot = (n + 1) % kItemSlots;
         if (n + 1 >= kItemSlots &&
             !mbar_wait(&item_empty[slot], (((n + 1) / kItemSlots) - 1) & 1, abort_flag, status, kSiteItemEmpty))
           break;
         s_items[slot] = w;
         mbar_arrive(&item_full[slot]);
-        if (w >= 0) w_next = take_item();
       }
     }
   } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
