@@ -166,6 +166,18 @@ int rbf_b200_xsa_bwd(const void* g, const void* o, const void* v, void* d_o, voi
                      const int64_t* o_strides, const int64_t* v_strides, const int64_t* do_strides,
                      const int64_t* dv_strides, int B, int H, int N, int D, int dtype, void* stream);
 
+/* LayerNorm of the language model's blocks (nn.LayerNorm(emb_dim), train_rbf_transformer.py:139-150, 217) for 16-bit
+ * activations: x, y (rows, cols) contiguous, gamma and beta (cols) in the dtype of x (0 = bfloat16, 1 = float16), cols
+ * 256, 512, 768 or 1024, all 16-byte aligned. Statistics in fp32; `mean` and `rstd` (rows, fp32) are saved for the
+ * backward, which returns dx in the dtype of x and dgamma, dbeta in fp32, summed in a fixed order (bitwise
+ * reproducible). The backward's workspace holds one fp32 partial row per thread block. */
+int rbf_b200_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                            int64_t rows, int cols, float eps, int dtype, void* stream);
+size_t rbf_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int cols);
+int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                            void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
+                            int64_t rows, int cols, int dtype, void* stream);
+
 /* Cross entropy of the language-model training step: replaces torch.nn.CrossEntropyLoss(ignore_index=-100) and its
  * backward (train_rbf_transformer.py:282, 335-345). One kernel reads the logits (rows x cols, row pitch `ld` elements,
  * dtype 0 = bfloat16, 1 = float16, 2 = float32), writes loss_rows[r] = logsumexp(logits[r]) - logits[r, targets[r]] and

@@ -60,6 +60,15 @@ SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint)],
     ),
+    "rbf_b200_layer_norm_fwd": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 6 + [ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p],
+    ),
+    "rbf_b200_layer_norm_bwd_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int64, ctypes.c_int]),
+    "rbf_b200_layer_norm_bwd": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 9 + [ctypes.c_size_t, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p],
+    ),
     "rbf_b200_cross_entropy": (
         ctypes.c_int,
         [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,

@@ -592,6 +592,64 @@ int rbf_b200_read_device_status(const void* workspace, void* stream_v, unsigned 
 }
 
 // ---------------------------------------------------------------------------------------------
+// LayerNorm of the language model's blocks
+// ---------------------------------------------------------------------------------------------
+static int check_layer_norm(int64_t rows, int cols, int dtype) {
+  if (rows < 0) return fail(RBF_B200_ERR_BAD_ARGUMENT, "rows must be >= 0");
+  if (!rbf::layer_norm_supported(cols))
+    return fail(RBF_B200_ERR_BAD_ARGUMENT, "cols must be 256, 512, 768 or 1024, got %d", cols);
+  if (dtype != 0 && dtype != 1) return fail(RBF_B200_ERR_BAD_ARGUMENT, "dtype must be 0 (bf16) or 1 (fp16)");
+  return RBF_B200_OK;
+}
+
+int rbf_b200_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                            int64_t rows, int cols, float eps, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_layer_norm(rows, cols, dtype))) return rc;
+  if (rows == 0) return RBF_B200_OK;
+  if (!x || !gamma || !beta || !y || !mean || !rstd) return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL tensor pointer");
+  for (const void* ptr : {x, gamma, beta, static_cast<const void*>(y)})
+    if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "tensors must be 16-byte aligned");
+  const int sms = sm_count();
+  if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
+  rbf::LayerNormArgs a{};
+  a.x = x; a.gamma = gamma; a.beta = beta; a.y = y; a.mean = mean; a.rstd = rstd; a.rows = rows; a.eps = eps;
+  const cudaError_t e = rbf::launch_layer_norm_fwd(a, cols, dtype == 0, sms, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "layer norm launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+size_t rbf_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int cols) {
+  const int sms = sm_count();
+  if (sms <= 0 || rows < 0 || !rbf::layer_norm_supported(cols)) return 0;
+  return static_cast<size_t>(rbf::layer_norm_bwd_blocks(rows, sms)) * 2 * cols * sizeof(float);
+}
+
+int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                            void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
+                            int64_t rows, int cols, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  int rc;
+  if ((rc = check_layer_norm(rows, cols, dtype))) return rc;
+  if (!dgamma || !dbeta || !workspace) return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL output pointer");
+  if (rows > 0 && (!x || !dy || !gamma || !mean || !rstd || !dx))
+    return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL tensor pointer");
+  for (const void* ptr : {x, dy, gamma, static_cast<const void*>(dx)})
+    if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "tensors must be 16-byte aligned");
+  if (workspace_bytes < rbf_b200_layer_norm_bwd_workspace_bytes(rows, cols))
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace too small: %zu bytes", workspace_bytes);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
+  rbf::LayerNormBwdArgs a{};
+  a.x = x; a.dy = dy; a.gamma = gamma; a.mean = mean; a.rstd = rstd; a.dx = dx; a.dgamma = dgamma; a.dbeta = dbeta;
+  a.partials = static_cast<float*>(workspace); a.rows = rows;
+  const cudaError_t e = rbf::launch_layer_norm_bwd(a, cols, dtype == 0, sms, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "layer norm backward launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Cross entropy of the language-model training step
 // ---------------------------------------------------------------------------------------------
 int rbf_b200_cross_entropy(const void* logits, const int64_t* targets, const float* grad_scale, float* loss_rows,

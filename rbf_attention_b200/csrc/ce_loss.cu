@@ -5,7 +5,9 @@
 // one read and one write. Roofline: HBM. A block owns a row: pass 1 reads it from DRAM with an online maximum / sum
 // and keeps it in shared memory (100 KB per row at the benchmark's vocabulary, two blocks per SM), pass 2 writes
 // softmax - onehot, scaled by 1 / (rows that count), from there. Rows too long for that are read a second time
-// (with two blocks per SM in flight they are L2 hits).
+// (with two blocks per SM in flight they are L2 hits). Measured at 65536 x 50304 bf16: 3.16 ms, 4.2 TB/s = 64 % of the
+// copy bandwidth; a variant with one block of 1024 threads per SM that streams the next row into a second buffer with
+// cp.async while the current one is reduced was slower (3.82 ms) and is not kept.
 #include <cstdint>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>

@@ -98,6 +98,34 @@ cudaError_t launch_xsa(const XsaArgs& a, bool backward, bool bf16, int D, cudaSt
 // Self-test of the bounded waits: one block waits on a barrier that nothing arms; when the wait runs out after `limit`
 // SM clocks it records site kSiteSelfTest in `status` exactly as the attention kernels do, and the kernel returns.
 static constexpr uint32_t kSiteSelfTest = 250;
+// LayerNorm of the language model's blocks (layer_norm.cu): 16-bit rows of 256, 512, 768 or 1024 columns.
+struct LayerNormArgs {
+  const void* x;             // (rows, cols) contiguous
+  const void* gamma;         // (cols), dtype of x
+  const void* beta;          // (cols)
+  void* y;                   // (rows, cols)
+  float* mean;               // (rows) saved for the backward
+  float* rstd;               // (rows)
+  int64_t rows;
+  float eps;
+};
+struct LayerNormBwdArgs {
+  const void* x;
+  const void* dy;
+  const void* gamma;
+  const float* mean;
+  const float* rstd;
+  void* dx;                  // (rows, cols), dtype of x
+  float* dgamma;             // (cols) fp32
+  float* dbeta;              // (cols) fp32
+  float* partials;           // layer_norm_bwd_blocks() x 2 x cols floats
+  int64_t rows;
+};
+bool layer_norm_supported(int cols);
+int layer_norm_bwd_blocks(int64_t rows, int sms);
+cudaError_t launch_layer_norm_fwd(const LayerNormArgs& a, int cols, bool bf16, int sms, cudaStream_t stream);
+cudaError_t launch_layer_norm_bwd(const LayerNormBwdArgs& a, int cols, bool bf16, int sms, cudaStream_t stream);
+
 // Cross entropy of the language-model step (ce_loss.cu): per-row losses and d(mean loss)/d(logits) in one kernel.
 struct CrossEntropyArgs {
   const void* logits;        // (rows, cols), row pitch ld elements

@@ -654,6 +654,92 @@ def exclusive_self_attention(o, v):
 
 
 # ---------------------------------------------------------------------------------------------
+# LayerNorm of the language model's blocks (nn.LayerNorm, train_rbf_transformer.py:139-150, 217)
+# ---------------------------------------------------------------------------------------------
+def layer_norm_supported(x: torch.Tensor, weight, bias) -> bool:
+    """16-bit CUDA activations with an affine LayerNorm over 256, 512, 768 or 1024 columns."""
+    return (x.is_cuda and x.dtype in _DTYPE_CODE and weight is not None and bias is not None
+            and weight.dtype == x.dtype and bias.dtype == x.dtype
+            and x.shape[-1] % 256 == 0 and 0 < x.shape[-1] <= 1024)
+
+
+@torch.library.custom_op("rbf_attn_b200::layer_norm_fwd", mutates_args=())
+def layer_norm_fwd(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                   eps: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """y = (x - mean) * rstd * weight + bias over the last dim; returns (y, mean, rstd), the statistics in fp32."""
+    if not layer_norm_supported(x, weight, bias):
+        raise ValueError("layer_norm_fwd: 16-bit CUDA tensors with 256, 512, 768 or 1024 columns")
+    cols = x.shape[-1]
+    xc = x.contiguous()
+    rows = xc.numel() // cols
+    y = torch.empty_like(xc)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    wc, bc = weight.contiguous(), bias.contiguous()
+    with torch.cuda.device(x.device):
+        rc = _lib.load().rbf_b200_layer_norm_fwd(xc.data_ptr(), wc.data_ptr(), bc.data_ptr(), y.data_ptr(),
+                                                 mean.data_ptr(), rstd.data_ptr(), rows, cols, float(eps),
+                                                 _DTYPE_CODE[x.dtype], _stream_ptr(x.device))
+    _lib.check(rc, "rbf_b200_layer_norm_fwd")
+    return y, mean, rstd
+
+
+@layer_norm_fwd.register_fake
+def _(x, weight, bias, eps):
+    rows = x.numel() // x.shape[-1]
+    return (torch.empty_like(x, memory_format=torch.contiguous_format), x.new_empty(rows, dtype=torch.float32),
+            x.new_empty(rows, dtype=torch.float32))
+
+
+@torch.library.custom_op("rbf_attn_b200::layer_norm_bwd", mutates_args=())
+def layer_norm_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor, mean: torch.Tensor,
+                   rstd: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    cols = x.shape[-1]
+    xc, dyc, wc = x.contiguous(), dy.to(x.dtype).contiguous(), weight.contiguous()
+    rows = xc.numel() // cols
+    lib = _lib.load()
+    dx = torch.empty_like(xc)
+    dgamma = torch.empty(cols, dtype=torch.float32, device=x.device)
+    dbeta = torch.empty(cols, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.rbf_b200_layer_norm_bwd_workspace_bytes(rows, cols)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+        rc = lib.rbf_b200_layer_norm_bwd(xc.data_ptr(), dyc.data_ptr(), wc.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                         dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), ws.data_ptr(), ws.numel(),
+                                         rows, cols, _DTYPE_CODE[x.dtype], _stream_ptr(x.device))
+    _lib.check(rc, "rbf_b200_layer_norm_bwd")
+    return dx, dgamma.to(weight.dtype), dbeta.to(weight.dtype)
+
+
+@layer_norm_bwd.register_fake
+def _(x, dy, weight, mean, rstd):
+    return (torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(weight),
+            torch.empty_like(weight))
+
+
+def _ln_setup_context(ctx, inputs, output):
+    x, weight, _bias, _eps = inputs
+    ctx.save_for_backward(x, weight, output[1], output[2])
+    ctx.set_materialize_grads(False)
+
+
+def _ln_backward(ctx, g_y, _g_mean, _g_rstd):
+    if g_y is None:
+        return None, None, None, None
+    x, weight, mean, rstd = ctx.saved_tensors
+    dx, dgamma, dbeta = torch.ops.rbf_attn_b200.layer_norm_bwd(x, g_y, weight, mean, rstd)
+    return dx, dgamma, dbeta, None
+
+
+torch.library.register_autograd("rbf_attn_b200::layer_norm_fwd", _ln_backward, setup_context=_ln_setup_context)
+
+
+def layer_norm(x, weight, bias, eps: float = 1e-5):
+    """``F.layer_norm(x, (x.shape[-1],), weight, bias, eps)`` on the library's kernels (see layer_norm_supported)."""
+    return torch.ops.rbf_attn_b200.layer_norm_fwd(x, weight, bias, eps)[0]
+
+
+# ---------------------------------------------------------------------------------------------
 # Cross entropy of the language-model step (torch.nn.CrossEntropyLoss(ignore_index=-100),
 # train_rbf_transformer.py:282): loss and d(loss)/d(logits) from one kernel
 # ---------------------------------------------------------------------------------------------

@@ -125,10 +125,11 @@ def test_compiled_training_step_equals_the_eager_one():
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("rows,cols", [(64, 1024), (37, 1000), (5, 50257), (3, 17)])
+@pytest.mark.parametrize("rows,cols", [(64, 1024), (37, 1000), (5, 50257), (3, 17), (700, 4096), (600, 50304)])
 def test_cross_entropy_kernel_matches_torch(dtype, rows, cols):
     """Loss and gradient of ``ops.cross_entropy`` against ``F.cross_entropy(ignore_index=-100)`` evaluated in fp64 on
-    the same (rounded) logits: vector path (aligned widths), element path (odd widths), ignored rows, -inf columns,
+    the same (rounded) logits: vector path (aligned widths), element path (odd widths), more rows than
+    resident blocks, ignored rows, -inf columns,
     a non-unit upstream gradient. Tolerances: loss |diff| <= 2e-6 * max(1, loss); gradient within one rounding of
     the output dtype per pass (bf16 8e-3, fp16 2e-3, fp32 5e-6 - a few ulps of an exponent of magnitude 16 -, relative to
     the row's largest gradient)."""
@@ -159,6 +160,38 @@ def test_cross_entropy_kernel_matches_torch(dtype, rows, cols):
     x2 = logits.to(DEV).requires_grad_(True)
     ops.cross_entropy(x2, targets.to(DEV)).backward()
     assert ((x2.grad.double().cpu() * 1.7 - want).abs() / scale).max().item() <= 2 * tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols", [(4113, 512), (77, 256), (1, 1024), (300, 768)])
+def test_layer_norm_kernels_match_torch(dtype, rows, cols):
+    """``ops.layer_norm`` and its backward against ``F.layer_norm`` in fp64 on the same 16-bit values (rows not a
+    multiple of the 8 rows a block walks at a time, a non-zero mean, a non-trivial affine part). Tolerances: y and dx
+    within one rounding of the output dtype relative to the tensor's largest value (bf16 8e-3, fp16 1e-3); d(gamma),
+    d(beta) - fp32 sums over the rows, rounded once - relative L2 <= 5e-3 / 1e-3."""
+    from rbf_attention_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=g) * 1.5 + 0.7).to(dtype)
+    w = (1.0 + 0.3 * torch.randn(cols, generator=g)).to(dtype)
+    b = (0.2 * torch.randn(cols, generator=g)).to(dtype)
+    dy = torch.randn(rows, cols, generator=g).to(dtype)
+    xr, wr, br = (t.double().requires_grad_(True) for t in (x, w, b))
+    ref = F.layer_norm(xr, (cols,), wr, br, 1e-5)
+    ref.backward(dy.double())
+    xd, wd, bd = (t.to(DEV).requires_grad_(True) for t in (x, w, b))
+    y = ops.layer_norm(xd, wd, bd, 1e-5)
+    y.backward(dy.to(DEV))
+    tol = 8e-3 if dtype == torch.bfloat16 else 1e-3
+    assert (y.double().cpu() - ref).abs().max().item() <= tol * ref.abs().max().item()
+    assert (xd.grad.double().cpu() - xr.grad).abs().max().item() <= tol * xr.grad.abs().max().item()
+    ptol = 5e-3 if dtype == torch.bfloat16 else 1e-3
+    for got, want in ((wd.grad, wr.grad), (bd.grad, br.grad)):
+        rep = oracle.error_report(got.float().cpu(), want.float())
+        assert rep["rel_l2"] <= ptol, rep
+    # a 3-D activation (batch, sequence, width) as the model passes it; bitwise reproducible
+    x3 = xd.detach().reshape(1, rows, cols)
+    assert torch.equal(ops.layer_norm(x3, wd.detach(), bd.detach(), 1e-5).reshape(rows, cols), y.detach())
 
 
 def test_cross_entropy_through_the_c_abi_with_a_row_pitch():

@@ -139,6 +139,46 @@ def test_persistent_backward_with_ragged_tiles_and_many_items(causal, softmax, d
             check(f"{name}[{b},{h}]", got[sl].cpu().float(), want, REL_L2[dtype])
 
 
+@pytest.mark.parametrize("causal,softmax", [(True, True), (False, True), (True, False)])
+def test_persistent_forward_queue_and_workspace_reuse(causal, softmax):
+    """B6 H10 N1000 D64: 60 pairs x 4 query blocks = 240 work items for at most 148 resident blocks, so the forward's
+    blocks take further items from the launch's work counter, whose last block puts it back to zero: the main kernel
+    alone (phase 2, no pre-pass in between) is launched twice more on the same workspace and must reproduce output
+    and log-sum-exp bit for bit. Three pairs are compared with the oracle."""
+    lib = _lib.load()
+    B, H, N, D = 6, 10, 1000, 64
+    std = 1.0 if softmax else 0.5
+    q, k, v, _ = oracle.make_inputs(B, H, N, D, seed=23, dtype=torch.bfloat16, std=std,
+                                    key_norm_sigma=0.3 if softmax else 0.0)
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    stream = torch.cuda.current_stream().cuda_stream
+    nbytes = lib.rbf_b200_workspace_bytes(B, H, N, D, int(softmax), 0)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    code = ctypes.c_uint(0)
+    results = []
+    for phases in (3, 2, 2):
+        out = torch.zeros((B, H, N, D), dtype=torch.bfloat16, device=DEV)
+        lse = torch.zeros((B, H, N), dtype=torch.float32, device=DEV)
+        rc = lib.rbf_b200_fwd_phases(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                     ws.data_ptr(), nbytes, B, H, N, D, _s3(qd), _s3(kd), _s3(vd), _s3(out), 0,
+                                     int(causal), int(softmax), 1.0 / math.sqrt(D), stream, phases)
+        assert rc == 0, lib.rbf_b200_last_error()
+        assert lib.rbf_b200_read_device_status(ws.data_ptr(), stream, ctypes.byref(code)) == 0
+        results.append((out, lse))
+    for out, lse in results[1:]:
+        assert torch.equal(out, results[0][0]) and torch.equal(lse, results[0][1])
+    out, lse = results[0]
+    assert torch.isfinite(out).all()
+    for (b, h) in [(0, 0), (3, 4), (5, 9)]:
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        ref = oracle.torch_forward_backward(q[sl], k[sl], v[sl], torch.zeros_like(q[sl]), causal, softmax,
+                                            dtype=torch.float32)
+        check(f"O[{b},{h}]", out[sl].cpu().float(), ref[0], REL_L2[torch.bfloat16])
+        if softmax:
+            ref_l = oracle.torch_lse2(q[sl], k[sl], causal)
+            assert (lse[sl].cpu() - ref_l).abs().max().item() <= 2e-4 * max(1.0, ref_l.abs().max().item())
+
+
 @pytest.mark.parametrize("D", [64, 128])
 def test_deterministic_switch_gives_bitwise_reproducible_gradients(D):
     """rbf_b200_set_deterministic(1): the softmax backward runs as two kernels with a fixed summation order; dQ is
