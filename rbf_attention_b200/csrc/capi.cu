@@ -689,11 +689,28 @@ int rbf_b200_post_device_status(const void* workspace, unsigned int* host_slot, 
   g_last_error[0] = 0;
   if (workspace == nullptr || host_slot == nullptr)
     return fail(RBF_B200_ERR_BAD_ARGUMENT, "workspace and host_slot must not be NULL");
+  // device-side address of the slot: resolved by the driver once per 256-byte block and thread (callers post into a
+  // small ring of slots, and the driver call costs more than the launch)
+  thread_local uintptr_t cached_page = 0;
+  thread_local intptr_t cached_delta = 0;
+  thread_local int cached_device = -1;
+  const uintptr_t host_addr = reinterpret_cast<uintptr_t>(host_slot);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "cudaGetDevice failed: %s", cudaGetErrorString(e));
   void* dev_ptr = nullptr;
-  cudaError_t e = cudaHostGetDevicePointer(&dev_ptr, host_slot, 0);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return fail(RBF_B200_ERR_BAD_ARGUMENT, "host_slot is not mapped page-locked host memory: %s", cudaGetErrorString(e));
+  if (cached_page != 0 && cached_page == (host_addr & ~uintptr_t(255)) && cached_device == device) {
+    dev_ptr = reinterpret_cast<void*>(host_addr + cached_delta);
+  } else {
+    e = cudaHostGetDevicePointer(&dev_ptr, host_slot, 0);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(RBF_B200_ERR_BAD_ARGUMENT, "host_slot is not mapped page-locked host memory: %s",
+                  cudaGetErrorString(e));
+    }
+    cached_page = host_addr & ~uintptr_t(255);
+    cached_delta = static_cast<intptr_t>(reinterpret_cast<uintptr_t>(dev_ptr) - host_addr);
+    cached_device = device;
   }
   e = rbf::launch_post_status(static_cast<const rbf::DeviceStatus*>(workspace), static_cast<unsigned int*>(dev_ptr),
                               static_cast<cudaStream_t>(stream_v));

@@ -75,7 +75,7 @@ static constexpr int kColS = 0, kColDP = 128, kColPT = 256, kColDV = 320, kColDK
 
 enum Site : uint32_t {
   kSiteKV = 64, kSiteQFull, kSiteDoFull, kSiteQEmpty, kSiteDoEmpty, kSiteSFull, kSiteDPFull, kSitePFull, kSiteDSFull,
-  kSiteDQFull, kSiteDQDrained, kSiteAccDone, kSiteGroup, kSiteSConsumed, kSiteDPConsumed, kSiteDVDone, kSiteDsFree
+  kSiteDQFull, kSiteDQDrained, kSiteAccDone, kSiteGroup, kSiteSConsumed, kSiteDPConsumed, kSiteDVDone, kSiteDsFree, kSiteStageFree
 };
 
 struct Params {
@@ -128,6 +128,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   uint64_t* dq_drained = dq_full + 1;        // drain warps have read dQ_partial(n) out of TMEM
   uint64_t* acc_done = dq_drained + 1;       // two arrivals: all MMAs of both issuers complete
   uint64_t* grp_sync = acc_done + 1;         // compute warps (16 arrivals)
+  uint64_t* stage_free = grp_sync + 1;       // the previous item's dK and dV stores have read their staging tiles
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + Smem::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 4);
 
@@ -166,32 +167,45 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     tma_load_4d(s_do + st * kTileBytes, &tm_do, &do_full[st], 0, row0, h, b);
     tma_load_3d(s_dslab + st * kSlabBytes, &tm_dslab, &do_full[st], 0, row0, bh);
   };
-  // Executed by the producer thread before every item's opening synchronisation (nothing of the previous item is in
-  // flight any more): takes the next item, re-initialises the barriers and issues the item's first loads.
+  // Executed by the producer warp before every item's opening synchronisation (nothing of the previous item is in
+  // flight any more): lane 0 takes the next item and reads the launch's status word, and while those two round trips
+  // to L2 are under way the warp re-initialises the barriers, one per lane (one thread doing all 25 in turn took
+  // about 1500 clocks per item); then lane 0 issues the item's first loads.
   auto prepare_item = [&](bool first_time) {
-    const int item = static_cast<int>(atomicAdd(&p.work[0], 1u));
-    const unsigned int earlier = *reinterpret_cast<volatile unsigned int*>(&p.status->code);
-    if (!first_time)
-      for (int i = 0; i < Smem::kNumBars; ++i) mbar_inval(&bars[i]);
-    mbar_init(kv_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&q_full[s], 1);
-      mbar_init(&q_empty[s], 2);
-      mbar_init(&do_full[s], 1);
-      mbar_init(&do_empty[s], 2);
+    int item = 0;
+    unsigned int earlier = 0u;
+    if (lane == 0) {
+      item = static_cast<int>(atomicAdd(&p.work[0], 1u));
+      earlier = *reinterpret_cast<volatile unsigned int*>(&p.status->code);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_consumed, kNumComputeWarps);   // one arrival per warp
-    mbar_init(dp_full, 1);
-    mbar_init(dp_consumed, kNumComputeWarps);
-    mbar_init(p_full, kNumComputeWarps);
-    mbar_init(dv_done, 1);
-    mbar_init(ds_full, kNumComputeWarps);
-    mbar_init(dq_full, 2);                    // dK (issuer B) and dQ_partial (issuer C) of the step
-    mbar_init(dq_drained, 4);
-    mbar_init(acc_done, 3);
-    mbar_init(grp_sync, kNumComputeWarps);
+    if (lane < Smem::kNumBars) {
+      // arrival counts in the order of the barrier block: kv_full; q_full, q_empty, do_full, do_empty (kStages
+      // each); s_full, s_consumed, dp_full, dp_consumed, p_full, dv_done, ds_full, dq_full, dq_drained, acc_done,
+      // grp_sync, stage_free
+      uint32_t count;
+      if (lane == 0) {
+        count = 1;
+      } else if (lane < 1 + 4 * kStages) {
+        const int ring = (lane - 1) / kStages;               // 0 q_full, 1 q_empty, 2 do_full, 3 do_empty
+        count = (ring & 1) ? 2 : 1;
+      } else {
+        constexpr uint32_t tail[12] = {1, kNumComputeWarps, 1, kNumComputeWarps, kNumComputeWarps, 1,
+                                       kNumComputeWarps, 2, 4, 3, kNumComputeWarps, 2};
+        count = tail[lane - (1 + 4 * kStages)];
+      }
+      if (!first_time) mbar_inval(&bars[lane]);
+      mbar_init(&bars[lane], count);
+    }
     fence_mbar_init();
+    __syncwarp();
+    if (lane != 0) return;
+    // The loads below complete on barriers that other lanes have just initialised: besides the warp-level
+    // synchronisation, order those generic-proxy writes before this thread's async-proxy operations. (The counter's
+    // round trip, which the fence above waits for, also puts about 2000 clocks between the two. A variant that
+    // fetched the item number under the previous item's last steps, so that the loads followed the initialisation
+    // within about 100 clocks, ended with an unspecified launch failure and a bounded wait that ran out, and was
+    // withdrawn.)
+    fence_proxy_async_smem();
     *s_item = item;
     if (first_time) *abort_flag = 0;
     if (earlier != 0u) *abort_flag = 1;
@@ -213,13 +227,15 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     set_item(item);
     return true;
   };
-  if (tid == kLoadWarp * 32) {
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
-    tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_do);
-    tma_prefetch_desc(&tm_lslab);
-    tma_prefetch_desc(&tm_dslab);
+  if (warp == kLoadWarp) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_lslab);
+      tma_prefetch_desc(&tm_dslab);
+    }
     prepare_item(true);
   }
   if (warp == kMmaWarpA) {
@@ -252,7 +268,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
       }
       __syncthreads();                       // closing synchronisation: every role is done with the item
-      if (lane == 0) prepare_item(false);
+      prepare_item(false);
     }
   } else if (warp == kMmaWarpA || warp == kMmaWarpB || warp == kMmaWarpC) {
     // ------------------------------------------------------------------ MMA issuers
@@ -422,11 +438,21 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const int g = (warp - kComputeWarp0) >> 2;             // 32-column slice of the query tile
     const int r = tid & (kTile - 1);
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const bool storer = r == 0 && (g & 1) == 0;   // issues the item's dK (g = 0) or dV (g = 2) store
+    bool store_pending = false;
     while (open_item()) {
     tmem = *tmem_base_s;
     const float neg_ksq = -p.ksq[static_cast<int64_t>(bh) * p.n_pad + k_row0 + r];
     float ds_rowsum = 0.f;
     bool ok = true;
+    if (storer) {
+      // dK and dV leave through the dS^T tile, which the previous item's stores may still be reading: they were
+      // issued a set-up and a load latency ago, so this wait is over at once; the compute warps check `stage_free`
+      // before the item's first dS^T store
+      if (store_pending) tma_store_wait_read();
+      store_pending = false;
+      mbar_arrive(stage_free);
+    }
 
     for (int n = 0; n < cnt; ++n) {
       ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull, s_item);
@@ -491,11 +517,11 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
         ds_rowsum += rs0 + rs1;
       }
-      // the dS^T tile is free once dK and dQ_partial of the previous step have completed
-      if (n > 0) {
-        ok = mbar_wait(dq_full, (n - 1) & 1, abort_flag, p.status, kSiteDsFree, s_item);
-        if (!ok) break;
-      }
+      // the dS^T tile is free once dK and dQ_partial of the previous step have completed (first step: once the
+      // previous item's output stores have read it)
+      ok = n > 0 ? mbar_wait(dq_full, (n - 1) & 1, abort_flag, p.status, kSiteDsFree, s_item)
+                 : mbar_wait(stage_free, 0, abort_flag, p.status, kSiteStageFree, s_item);
+      if (!ok) break;
       // row r of the [key][query] tile, box g/2, 16-byte chunks 4(g%2) .. +3
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch)
@@ -519,9 +545,10 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       ok = group_sync();
     }
     if (ok) {
-      // groups 0, 1 finish dK (columns [32(g%2), +32)), groups 2, 3 store dV; the Q ring is dead by now
+      // groups 0, 1 finish dK (columns [32(g%2), +32)), groups 2, 3 store dV; the dS^T tile is dead by now (all MMAs
+      // have completed) and is not written again before the next item's first step
       const bool is_dk = g < 2;
-      uint8_t* stage = s_q + (is_dk ? 0 : kTileBytes);
+      uint8_t* stage = s_ds + (is_dk ? 0 : kTileBytes);
       const float w = is_dk ? (s_rowsum[r] + s_rowsum[kTile + r]) + (s_rowsum[2 * kTile + r] + s_rowsum[3 * kTile + r])
                             : 0.f;
       const float out_scale = is_dk ? p.grad_scale : 1.0f;
@@ -545,14 +572,15 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       }
       fence_proxy_async_smem();
       ok = group_sync();
-      if (ok && r == 0 && (g & 1) == 0) {
+      if (ok && storer) {
         tma_store_4d(is_dk ? &tm_dk : &tm_dv, stage, 0, k_row0, h, b);
         tma_store_commit();
-        tma_store_wait_read();   // the staging tile may be reused once it has been read
+        store_pending = true;    // read-wait deferred to the next item (or to the end of the kernel)
       }
     }
     __syncthreads();                         // closing synchronisation
     }
+    if (storer && store_pending) tma_store_wait_read();
   }
 
   // ------------------------------------------------------------------ teardown
