@@ -81,8 +81,36 @@ def _pad_d(t: torch.Tensor, Dp: int) -> torch.Tensor:
     return t if D == Dp else torch.nn.functional.pad(t, (0, Dp - D))
 
 
+def _device_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch._C._cuda_getDevice()
+
+
 def _stream_ptr(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """Raw handle of the current stream of ``device`` (the binding's own call: building a ``torch.cuda.Stream`` object
+    for it costs 10 us, a tenth of what a whole operator call takes on the host)."""
+    return torch._C._cuda_getCurrentRawStream(_device_index(device))
+
+
+class _OnDevice:
+    """``torch.cuda.device(device)`` that does nothing when ``device`` is already the current one."""
+
+    __slots__ = ("index", "prev")
+
+    def __init__(self, device: torch.device):
+        self.index = _device_index(device)
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch._C._cuda_getDevice()
+        if cur != self.index:
+            self.prev = cur
+            torch._C._cuda_setDevice(self.index)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch._C._cuda_setDevice(self.prev)
+        return False
 
 
 def _workspace(B, H, N, D, softmax, backward, device) -> torch.Tensor:
@@ -99,18 +127,20 @@ class _StatusMonitor:
     workspace and the kernels return with incomplete results. After each launch a one-thread kernel on the launch
     stream stores the word into a ring of pinned host slots (a store through the mapped host address: a copy would
     queue on the copy engine behind the caller's own device-to-host transfers and hold the launch stream up for
-    their duration); later calls look at the slots whose store has completed and raise ``RuntimeError`` for a
-    non-zero one. A timeout is therefore reported by a later operator call or by
+    their duration); a slot holds -1 until its word has arrived, so no event is needed to see that it has. Later
+    calls look at the slots that have been written and raise ``RuntimeError`` for a non-zero one. A timeout is therefore reported by a later operator call or by
     ``check_device_status()``, not by the call that suffered it. ``RBF_B200_SYNC_STATUS=1`` makes every call
     synchronise and check its own status (for debugging). Nothing is recorded while a CUDA graph is being captured.
     """
 
     SLOTS = 64
+    _NOT_YET = -1          # slot value until the posting kernel has run (no status word is 0xffffffff: sites end at 250)
 
     def __init__(self, device):
         self.device = device
         self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
-        self.events = [None] * self.SLOTS
+        self.slots = self.host.numpy()          # same memory: reading a slot costs 0.1 us instead of 3
+        self.base = self.host.data_ptr()
         self.what = [""] * self.SLOTS
         self.oldest = 0        # the pending entries are the slots oldest, oldest + 1, ..., next - 1 (mod SLOTS)
         self.next = 0
@@ -118,12 +148,11 @@ class _StatusMonitor:
 
     def _retire_oldest(self):
         i = self.oldest
-        self.events[i] = None
         self.oldest = (i + 1) % self.SLOTS
         self.pending -= 1
-        code = int(self.host[i]) & 0xFFFFFFFF
+        code = int(self.slots[i]) & 0xFFFFFFFF
         if code != 0:
-            self.host[i] = 0
+            self.slots[i] = 0
             if self.what[i].startswith("range:"):
                 raise RuntimeError(
                     f"{self.what[i][6:]}: float32 inputs exceed float16's range (|x| >= 65504) on a path that runs on "
@@ -135,12 +164,14 @@ class _StatusMonitor:
             )
 
     def poll(self, wait=False):
-        """Checks the entries whose copy has completed, oldest first (all of them after waiting when ``wait``)."""
+        """Checks the entries whose status word has arrived, oldest first (all of them, after waiting for the device,
+        when ``wait``)."""
+        if wait and self.pending:
+            torch.cuda.synchronize(self.device)
         while self.pending:
-            ev = self.events[self.oldest]
-            if wait:
-                ev.synchronize()
-            elif not ev.query():
+            if self.slots[self.oldest] == self._NOT_YET:
+                if wait:
+                    raise RuntimeError(f"{self.what[self.oldest]}: the status word did not arrive")
                 break
             self._retire_oldest()
 
@@ -158,14 +189,15 @@ class _StatusMonitor:
         if torch.cuda.is_current_stream_capturing():
             return
         if self.pending == self.SLOTS:          # the ring is full: wait for its oldest entry
-            self.events[self.oldest].synchronize()
-            self._retire_oldest()
+            self.poll()
+            if self.pending == self.SLOTS:
+                torch.cuda.synchronize(self.device)
+                self._retire_oldest()
         i = self.next
-        _lib.check(_lib.load().rbf_b200_post_device_status(
-            ws.data_ptr(), self.host.data_ptr() + 4 * i, _stream_ptr(ws.device)), "rbf_b200_post_device_status")
-        ev = torch.cuda.Event()
-        ev.record()
-        self.events[i], self.what[i] = ev, what
+        self.slots[i] = self._NOT_YET
+        _lib.check(_lib.load().rbf_b200_post_device_status(ws.data_ptr(), self.base + 4 * i, _stream_ptr(ws.device)),
+                   "rbf_b200_post_device_status")
+        self.what[i] = what
         self.next = (i + 1) % self.SLOTS
         self.pending += 1
         if _SYNC_STATUS:
@@ -209,7 +241,7 @@ def _forward(q, k, v, is_causal: bool, softmax: bool):
     ws = _workspace(B, H, N, D, softmax, False, q.device)
     mon = _monitor(q.device)
     mon.poll()
-    with torch.cuda.device(q.device):
+    with _OnDevice(q.device):
         rc = lib.rbf_b200_fwd(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
             lse.data_ptr() if softmax else None, ws.data_ptr(), ws.numel(),
@@ -249,7 +281,7 @@ def _backward(q, k, v, out, lse, dout, is_causal: bool, sm_scale: float, softmax
     mon.poll()
     # torch.use_deterministic_algorithms(True) selects the backward whose summation order is fixed
     lib.rbf_b200_set_deterministic(int(torch.are_deterministic_algorithms_enabled()))
-    with torch.cuda.device(q.device):
+    with _OnDevice(q.device):
         rc = lib.rbf_b200_bwd(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(),
             oc.data_ptr() if have_out else None, lse.data_ptr() if softmax else None, doc.data_ptr(),
@@ -466,7 +498,7 @@ def susie_block_fwd(
     scale = 1.0 / math.sqrt(D)
     mon = _monitor(dev)
     mon.poll()
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         stream = _stream_ptr(dev)
         rc = lib.rbf_b200_qkv_prep(
             qkv.data_ptr(), pw.data_ptr(), None if rp is None else rp.data_ptr(), int(params_fp32), table.data_ptr(),
@@ -529,7 +561,7 @@ def susie_block_bwd(
     mon = _monitor(dev)
     mon.poll()
     lib.rbf_b200_set_deterministic(int(torch.are_deterministic_algorithms_enabled()))
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         stream = _stream_ptr(dev)
         rc = lib.rbf_b200_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr() if softmax else None,
@@ -602,7 +634,7 @@ def xsa_fwd(o: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     lib = _lib.load()
     oc, vc = _tma_ready(o), _tma_ready(v)
     out = torch.empty((B, H, N, D), dtype=o.dtype, device=o.device)
-    with torch.cuda.device(o.device):
+    with _OnDevice(o.device):
         rc = lib.rbf_b200_xsa_fwd(oc.data_ptr(), vc.data_ptr(), out.data_ptr(), _lib.strides3(oc), _lib.strides3(vc),
                                   _lib.strides3(out), B, H, N, D, _DTYPE_CODE[o.dtype], _stream_ptr(o.device))
     _lib.check(rc, "rbf_b200_xsa_fwd")
@@ -621,7 +653,7 @@ def xsa_bwd(g: torch.Tensor, o: torch.Tensor, v: torch.Tensor) -> tuple[torch.Te
     gc, oc, vc = _tma_ready(g.to(o.dtype)), _tma_ready(o), _tma_ready(v)
     d_o = torch.empty((B, H, N, D), dtype=o.dtype, device=o.device)
     d_v = torch.empty_like(d_o)
-    with torch.cuda.device(o.device):
+    with _OnDevice(o.device):
         rc = lib.rbf_b200_xsa_bwd(gc.data_ptr(), oc.data_ptr(), vc.data_ptr(), d_o.data_ptr(), d_v.data_ptr(),
                                   _lib.strides3(gc), _lib.strides3(oc), _lib.strides3(vc), _lib.strides3(d_o),
                                   _lib.strides3(d_v), B, H, N, D, _DTYPE_CODE[o.dtype], _stream_ptr(o.device))
@@ -676,7 +708,7 @@ def layer_norm_fwd(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
     mean = torch.empty(rows, dtype=torch.float32, device=x.device)
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
     wc, bc = weight.contiguous(), bias.contiguous()
-    with torch.cuda.device(x.device):
+    with _OnDevice(x.device):
         rc = _lib.load().rbf_b200_layer_norm_fwd(xc.data_ptr(), wc.data_ptr(), bc.data_ptr(), y.data_ptr(),
                                                  mean.data_ptr(), rstd.data_ptr(), rows, cols, float(eps),
                                                  _DTYPE_CODE[x.dtype], _stream_ptr(x.device))
@@ -701,7 +733,7 @@ def layer_norm_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor, mean
     dx = torch.empty_like(xc)
     dgamma = torch.empty(cols, dtype=torch.float32, device=x.device)
     dbeta = torch.empty(cols, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _OnDevice(x.device):
         nbytes = lib.rbf_b200_layer_norm_bwd_workspace_bytes(rows, cols)
         ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
         rc = lib.rbf_b200_layer_norm_bwd(xc.data_ptr(), dyc.data_ptr(), wc.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
@@ -766,7 +798,7 @@ def cross_entropy_fwd(logits: torch.Tensor, targets: torch.Tensor, ignore_index:
     grad_scale = 1.0 / counted.to(torch.float32)          # no counted row: inf * 0 = nan, as torch's mean of nothing
     loss_rows = torch.empty(rows, dtype=torch.float32, device=x.device)
     dlogits = torch.empty((rows, cols), dtype=x.dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with _OnDevice(x.device):
         rc = _lib.load().rbf_b200_cross_entropy(
             x.data_ptr(), t.data_ptr(), grad_scale.data_ptr(), loss_rows.data_ptr(), dlogits.data_ptr(), rows, cols,
             x.stride(0) if rows > 1 else cols, cols, int(ignore_index), _CE_DTYPE[x.dtype], _stream_ptr(x.device))
@@ -785,7 +817,7 @@ def scale_unless_one_(x: torch.Tensor, factor: torch.Tensor) -> None:
     if not x.is_contiguous():
         raise ValueError("x must be contiguous")
     f = factor.reshape(1).to(device=x.device, dtype=torch.float32)
-    with torch.cuda.device(x.device):
+    with _OnDevice(x.device):
         rc = _lib.load().rbf_b200_scale_unless_one(x.data_ptr(), f.data_ptr(), x.numel(), _CE_DTYPE[x.dtype],
                                                    _stream_ptr(x.device))
     _lib.check(rc, "rbf_b200_scale_unless_one")
