@@ -178,6 +178,14 @@ int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, co
                             void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
                             int64_t rows, int cols, int dtype, void* stream);
 
+/* out[c] = sum over r of x[r, c] in fp32 for a 16-bit matrix (rows x cols, row pitch `ld` elements, cols and ld
+ * multiples of 8, 16-byte aligned base; dtype 0 = bfloat16, 1 = float16): the bias gradient of a linear layer
+ * (`nn.Linear` in train_rbf_transformer.py:143, 216 and rbf_attention.py:1625-1626), which PyTorch computes with a
+ * generic reduction. Summed in a fixed order. The workspace holds one fp32 partial row per band of rows. */
+size_t rbf_b200_column_sums_workspace_bytes(int64_t rows, int cols);
+int rbf_b200_column_sums(const void* x, float* out, void* workspace, size_t workspace_bytes, int64_t rows, int cols,
+                         int64_t ld, int dtype, void* stream);
+
 /* Cross entropy of the language-model training step: replaces torch.nn.CrossEntropyLoss(ignore_index=-100) and its
  * backward (train_rbf_transformer.py:282, 335-345). One kernel reads the logits (rows x cols, row pitch `ld` elements,
  * dtype 0 = bfloat16, 1 = float16, 2 = float32), writes loss_rows[r] = logsumexp(logits[r]) - logits[r, targets[r]] and

@@ -69,6 +69,12 @@ SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p] * 9 + [ctypes.c_size_t, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p],
     ),
+    "rbf_b200_column_sums_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int64, ctypes.c_int]),
+    "rbf_b200_column_sums": (
+        ctypes.c_int,
+        [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int64, ctypes.c_int, ctypes.c_int64,
+         ctypes.c_int, ctypes.c_void_p],
+    ),
     "rbf_b200_cross_entropy": (
         ctypes.c_int,
         [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,

@@ -26,7 +26,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .ops import exclusive_self_attention, run_triton_non_softmax_rbf, run_triton_rbf, susie_block_attention
+from .ops import exclusive_self_attention, linear, run_triton_non_softmax_rbf, run_triton_rbf, susie_block_attention
 
 __all__ = [
     "CustomCausalAttention",
@@ -220,12 +220,12 @@ class CustomCausalAttention(nn.Module):
 
     def forward(self, x):
         bsz, seq_len, emb = x.shape
-        qkv = self.qkv_proj(x)
+        qkv = linear(self.qkv_proj, x)         # the module's forward; on CUDA its bias gradient is the library's
         if self._fused_block(qkv):
             reg = self.reg_pos_emb.squeeze(0) if self.num_registers > 0 else None
             out = susie_block_attention(qkv, self.pos_weight.view(self.num_heads, -1), reg, self._susie_table_f32(),
                                         self.num_heads, softmax=self.attention_type != "rbf_non_softmax")
-            return self.proj(out), None
+            return linear(self.proj, out), None
         qkv = qkv.view(bsz, seq_len, 3, self.num_heads, self.head_dim)
         q, k, v = qkv.permute(2, 0, 3, 1, 4).unbind(0)      # each (B, H, S, D), views of the fused buffer
 
@@ -268,4 +268,4 @@ class CustomCausalAttention(nn.Module):
                 out = out - (out * v_hat).sum(dim=-1, keepdim=True) * v_hat
 
         out = out.transpose(1, 2).reshape(bsz, seq_len, emb)
-        return self.proj(out), attn_weights
+        return linear(self.proj, out), attn_weights

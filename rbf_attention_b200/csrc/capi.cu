@@ -650,6 +650,33 @@ int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, co
 }
 
 // ---------------------------------------------------------------------------------------------
+// Column sums (bias gradients of the model's linear layers)
+// ---------------------------------------------------------------------------------------------
+size_t rbf_b200_column_sums_workspace_bytes(int64_t rows, int cols) {
+  const int sms = sm_count();
+  if (sms <= 0 || rows < 0 || cols <= 0) return 0;
+  return static_cast<size_t>(rbf::col_sums_bands(rows, cols, sms)) * cols * sizeof(float);
+}
+
+int rbf_b200_column_sums(const void* x, float* out, void* workspace, size_t workspace_bytes, int64_t rows, int cols,
+                         int64_t ld, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  if (rows < 0 || cols <= 0 || cols % 8 != 0) return fail(RBF_B200_ERR_BAD_ARGUMENT, "cols must be a positive multiple of 8");
+  if (dtype != 0 && dtype != 1) return fail(RBF_B200_ERR_BAD_ARGUMENT, "dtype must be 0 (bf16) or 1 (fp16)");
+  if (ld < cols || ld % 8 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "row pitch must be a multiple of 8 elements and >= cols");
+  if (!out || !workspace || (rows > 0 && !x)) return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL pointer");
+  if (reinterpret_cast<uintptr_t>(x) % 16 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "x must be 16-byte aligned");
+  if (workspace_bytes < rbf_b200_column_sums_workspace_bytes(rows, cols))
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace too small: %zu bytes", workspace_bytes);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
+  const cudaError_t e = rbf::launch_col_sums(x, ld, rows, cols, dtype == 0, static_cast<float*>(workspace), out, sms,
+                                             static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "column sums launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Cross entropy of the language-model training step
 // ---------------------------------------------------------------------------------------------
 int rbf_b200_cross_entropy(const void* logits, const int64_t* targets, const float* grad_scale, float* loss_rows,

@@ -126,6 +126,12 @@ int layer_norm_bwd_blocks(int64_t rows, int sms);
 cudaError_t launch_layer_norm_fwd(const LayerNormArgs& a, int cols, bool bf16, int sms, cudaStream_t stream);
 cudaError_t launch_layer_norm_bwd(const LayerNormBwdArgs& a, int cols, bool bf16, int sms, cudaStream_t stream);
 
+// Column sums of a 16-bit (rows x cols) matrix, row pitch ld elements, into out (cols, fp32): col_sums.cu.
+// `partials` holds col_sums_bands() x cols floats.
+int col_sums_bands(int64_t rows, int cols, int sms);
+cudaError_t launch_col_sums(const void* x, int64_t ld, int64_t rows, int cols, bool bf16, float* partials, float* out,
+                            int sms, cudaStream_t stream);
+
 // Cross entropy of the language-model step (ce_loss.cu): per-row losses and d(mean loss)/d(logits) in one kernel.
 struct CrossEntropyArgs {
   const void* logits;        // (rows, cols), row pitch ld elements

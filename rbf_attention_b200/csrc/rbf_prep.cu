@@ -371,12 +371,21 @@ __global__ void __launch_bounds__(1024) qkv_prep_bwd_final_kernel(const QkvPrepB
     const int e = (blockIdx.x - nw) * 1024 + threadIdx.x;
     if (e >= a.H * a.R * a.D) return;
     const int d = e % a.D, r = (e / a.D) % a.R, h = e / (a.D * a.R);
+    const uint16_t* pq = reinterpret_cast<const uint16_t*>(a.dq) + h * a.dqs[1] + r * a.dqs[2] + d;
+    const uint16_t* pk = reinterpret_cast<const uint16_t*>(a.dk) + h * a.dks[1] + r * a.dks[2] + d;
     float sum = 0.f;
-    for (int b = 0; b < a.B; ++b) {
-      const uint16_t x = reinterpret_cast<const uint16_t*>(a.dq)[b * a.dqs[0] + h * a.dqs[1] + r * a.dqs[2] + d];
-      const uint16_t y = reinterpret_cast<const uint16_t*>(a.dk)[b * a.dks[0] + h * a.dks[1] + r * a.dks[2] + d];
-      sum += kBf16 ? __uint_as_float(static_cast<uint32_t>(x) << 16) + __uint_as_float(static_cast<uint32_t>(y) << 16)
-                   : __half2float(__ushort_as_half(x)) + __half2float(__ushort_as_half(y));
+    for (int b0 = 0; b0 < a.B; b0 += 8) {            // eight batches' loads in flight (each one a DRAM round trip)
+      uint16_t x[8], y[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = b0 + j < a.B;
+        x[j] = in ? pq[(b0 + j) * a.dqs[0]] : uint16_t(0);
+        y[j] = in ? pk[(b0 + j) * a.dks[0]] : uint16_t(0);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        sum += kBf16 ? __uint_as_float(static_cast<uint32_t>(x[j]) << 16) + __uint_as_float(static_cast<uint32_t>(y[j]) << 16)
+                     : __half2float(__ushort_as_half(x[j])) + __half2float(__ushort_as_half(y[j]));
     }
     a.d_reg_pos[e] = sum;
   }

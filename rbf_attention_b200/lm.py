@@ -76,7 +76,15 @@ class TransformerBlock(nn.Module):
     def forward(self, x):
         attn_out, attn_weights = self.attn(apply_layer_norm(self.ln1, x))
         x = x + attn_out
-        return x + self.ff(apply_layer_norm(self.ln2, x)), attn_weights
+        return x + self._mlp(apply_layer_norm(self.ln2, x)), attn_weights
+
+    def _mlp(self, x):
+        """``self.ff(x)`` (Linear, GELU, Linear) with the bias gradients of both projections from the library."""
+        if x.is_cuda:
+            from . import ops
+
+            return ops.linear(self.ff[2], self.ff[1](ops.linear(self.ff[0], x)))
+        return self.ff(x)
 
 
 class CausalLM(nn.Module):

@@ -686,6 +686,65 @@ def exclusive_self_attention(o, v):
 
 
 # ---------------------------------------------------------------------------------------------
+# Linear layers whose bias gradient is the library's column sum (nn.Linear in train_rbf_transformer.py:143, 216 and
+# rbf_attention.py:1625-1626)
+# ---------------------------------------------------------------------------------------------
+@torch.library.custom_op("rbf_attn_b200::column_sums", mutates_args=())
+def column_sums(x: torch.Tensor) -> torch.Tensor:
+    """fp32 sums over the rows of a 16-bit CUDA matrix (rows, cols), cols a multiple of 8."""
+    if x.dim() != 2 or not x.is_cuda or x.dtype not in _DTYPE_CODE or x.shape[1] % 8 != 0:
+        raise ValueError("column_sums: a 16-bit CUDA matrix whose width is a multiple of 8")
+    ok = x.stride(1) == 1 and x.stride(0) >= x.shape[1] and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+    xc = x if ok else x.contiguous()
+    rows, cols = xc.shape
+    lib = _lib.load()
+    out = torch.empty(cols, dtype=torch.float32, device=x.device)
+    with _OnDevice(x.device):
+        nbytes = lib.rbf_b200_column_sums_workspace_bytes(rows, cols)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+        rc = lib.rbf_b200_column_sums(xc.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), rows, cols,
+                                      xc.stride(0) if rows > 1 else cols, _DTYPE_CODE[x.dtype], _stream_ptr(x.device))
+    _lib.check(rc, "rbf_b200_column_sums")
+    return out
+
+
+@column_sums.register_fake
+def _(x):
+    return x.new_empty(x.shape[1], dtype=torch.float32)
+
+
+class _LinearBiasSum(torch.autograd.Function):
+    """``F.linear`` whose backward takes the bias gradient from ``column_sums`` (the two GEMMs are PyTorch's)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        return torch.nn.functional.linear(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight = ctx.saved_tensors
+        g2 = g.reshape(-1, g.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = g.matmul(weight)
+        if ctx.needs_input_grad[1]:
+            dw = g2.t().mm(x.reshape(-1, x.shape[-1]))
+        if ctx.needs_input_grad[2]:
+            db = torch.ops.rbf_attn_b200.column_sums(g2).to(g.dtype)
+        return dx, dw, db
+
+
+def linear(module: torch.nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    """``module(x)``; for 16-bit CUDA activations and a bias, the bias gradient comes from the library's column-sum
+    kernel instead of PyTorch's generic reduction."""
+    if (x.is_cuda and x.dtype in _DTYPE_CODE and module.bias is not None and module.weight.dtype == x.dtype
+            and module.out_features % 8 == 0 and torch.is_grad_enabled() and module.bias.requires_grad):
+        return _LinearBiasSum.apply(x, module.weight, module.bias)
+    return module(x)
+
+
+# ---------------------------------------------------------------------------------------------
 # LayerNorm of the language model's blocks (nn.LayerNorm, train_rbf_transformer.py:139-150, 217)
 # ---------------------------------------------------------------------------------------------
 def layer_norm_supported(x: torch.Tensor, weight, bias) -> bool:

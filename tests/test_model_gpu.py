@@ -194,6 +194,40 @@ def test_layer_norm_kernels_match_torch(dtype, rows, cols):
     assert torch.equal(ops.layer_norm(x3, wd.detach(), bd.detach(), 1e-5).reshape(rows, cols), y.detach())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols,ld", [(4113, 512, 512), (65, 1536, 1536), (1000, 2048, 2048), (7, 8, 8), (300, 264, 320)])
+def test_column_sums_and_the_linear_layer_built_on_them(dtype, rows, cols, ld):
+    """``ops.column_sums`` against an fp64 sum of the same 16-bit values (fp32 accumulation: relative 1e-5 of the
+    column's absolute sum), with a row pitch; ``ops.linear`` against ``nn.Linear``: same output bit for bit, same
+    weight and input gradients bit for bit (the same GEMMs), bias gradient within one rounding of the dtype."""
+    from rbf_attention_b200 import ops
+
+    g = torch.Generator().manual_seed(rows * 7 + cols)
+    store = torch.randn(rows, ld, generator=g).to(dtype).to(DEV)
+    x = store[:, :cols]
+    got = ops.column_sums(x).double().cpu()
+    want = x.double().sum(0).cpu()
+    bound = x.double().abs().sum(0).cpu() * 1e-5 + 1e-6
+    assert ((got - want).abs() <= bound).all()
+    if cols >= 64:
+        torch.manual_seed(1)
+        lin = torch.nn.Linear(cols // 2, cols).to(DEV, dtype)
+        inp = torch.randn(3, rows // 3 + 1, cols // 2, device=DEV, dtype=dtype)
+        gy = torch.randn(3, rows // 3 + 1, cols, device=DEV, dtype=dtype)
+        a = inp.clone().requires_grad_(True)
+        ya = lin(a)
+        ya.backward(gy)
+        ref = (a.grad.clone(), lin.weight.grad.clone(), lin.bias.grad.clone())
+        lin.zero_grad()
+        b = inp.clone().requires_grad_(True)
+        yb = ops.linear(lin, b)
+        yb.backward(gy)
+        assert torch.equal(ya, yb) and torch.equal(b.grad, ref[0]) and torch.equal(lin.weight.grad, ref[1])
+        exact = gy.double().reshape(-1, cols).sum(0)
+        tol = (8e-3 if dtype == torch.bfloat16 else 1e-3) * exact.abs().max().item() + 1e-3
+        assert (lin.bias.grad.double() - exact).abs().max().item() <= tol
+
+
 def test_cross_entropy_through_the_c_abi_with_a_row_pitch():
     """Raw pointers, a logits view with a row pitch larger than its width, every row ignored but two."""
     from rbf_attention_b200 import _lib
