@@ -90,7 +90,7 @@ struct Smem {
   static constexpr int kItemSlots = 4;                     // ring of work item numbers, producer -> all other roles
   static constexpr int kNumBars = 2 + 4 * kStages + 10 + 4 + 2 * kItemSlots;
   static constexpr int kMisc = kBars + kNumBars * 8;        // tmem base, abort flag
-  static constexpr int kTotal = kMisc + 16 + 4 * kItemSlots;
+  static constexpr int kTotal = kMisc + 16 + 16 * kItemSlots;
   static constexpr int kDynamic = kTotal + 1024;            // slack for 1024-byte alignment
 };
 
@@ -104,9 +104,20 @@ enum Site : uint32_t {
 // launches run a head's query blocks one after the other, which keeps its K/V hot in L2 (measured 20 % faster).
 struct Item {
   int bh, b, h, m0;
-  int nkt[2];      // key tiles of the two query tiles (0: the tile lies past N)
+  int nkt0, nkt1;  // key tiles of the two query tiles (0: the tile lies past N); scalars: no indexed local array
   int nkt_max;
+  __device__ __forceinline__ int nkt(int t) const { return t == 0 ? nkt0 : nkt1; }
 };
+// key tiles of the item's two query tiles from its first row (shifts only: the producer thread decodes an item number -
+// four integer divisions - once and hands bh, b, h, m0 to the other roles)
+template <int kKeys>
+__device__ __forceinline__ void count_key_tiles(Item& it, int N, int causal) {
+  const int all = (N + kKeys - 1) / kKeys;
+  const int r1 = it.m0 + kTile;
+  it.nkt0 = (it.m0 >= N) ? 0 : (causal ? min(all, (it.m0 + kTile) / kKeys) : all);
+  it.nkt1 = (r1 >= N) ? 0 : (causal ? min(all, (r1 + kTile) / kKeys) : all);
+  it.nkt_max = max(it.nkt0, it.nkt1);
+}
 template <int kKeys>
 __device__ __forceinline__ Item get_item(int w, int heads, int blocks, int H, int N, int causal) {
   Item it;
@@ -121,13 +132,7 @@ __device__ __forceinline__ Item get_item(int w, int heads, int blocks, int H, in
   it.b = it.bh / H;
   it.h = it.bh % H;
   it.m0 = mb * 2 * kTile;
-  const int all = (N + kKeys - 1) / kKeys;
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int r0 = it.m0 + t * kTile;
-    it.nkt[t] = (r0 >= N) ? 0 : (causal ? min(all, (r0 + kTile) / kKeys) : all);
-  }
-  it.nkt_max = max(it.nkt[0], it.nkt[1]);
+  count_key_tiles<kKeys>(it, N, causal);
   return it;
 }
 
@@ -180,7 +185,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint64_t* item_empty = item_full + L::kItemSlots;   // [kItemSlots] every other role has read it
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
-  volatile int* s_items = reinterpret_cast<volatile int*>(smem + L::kMisc + 16);
+  volatile int4* s_items = reinterpret_cast<volatile int4*>(smem + L::kMisc + 16);   // {bh (< 0: end), b, h, m0}
   constexpr int kItemSlots = L::kItemSlots;
   constexpr int kItemReaders = 2 + 8 * kSplit;   // two issuing threads, one arrival per softmax warp
 
@@ -201,18 +206,31 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const long long w = static_cast<long long>(gridDim.x) + atomicAdd(&work[0], 1u);
     return w < total ? static_cast<int>(w) : -1;
   };
-  // n-th item of the CTA as seen by the issuers and the softmax warps (whole warps call this together)
-  auto read_item = [&](uint32_t n, bool whole_warp, bool& ok_ref) -> int {
-    if (!kPersistent) return n == 0 ? static_cast<int>(blockIdx.x) : -1;
+  // n-th item of the CTA as seen by the issuers and the softmax warps (whole warps call this together); false at the
+  // end of the sequence
+  auto read_item = [&](uint32_t n, bool whole_warp, bool& ok_ref, Item& it) -> bool {
+    if (n == 0) {
+      it = first_item;
+      if (!kPersistent) return true;
+    } else if (!kPersistent) {
+      return false;
+    }
     const int slot = n % kItemSlots;
     if (!mbar_wait(&item_full[slot], (n / kItemSlots) & 1, abort_flag, status, kSiteItemFull)) {
       ok_ref = false;
-      return -1;
+      return false;
     }
-    const int w = s_items[slot];
+    if (n != 0) {
+      it.bh = s_items[slot].x;
+      it.b = s_items[slot].y;
+      it.h = s_items[slot].z;
+      it.m0 = s_items[slot].w;
+    }
     if (whole_warp) mbar_arrive_warp(&item_empty[slot]);
     else mbar_arrive(&item_empty[slot]);
-    return w;
+    if (it.bh < 0) return false;
+    if (n != 0) count_key_tiles<kKeys>(it, N, causal);
+    return true;
   };
 
   auto load_q = [&](const Item& it, int t) {
@@ -259,7 +277,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(&item_empty[i], kItemReaders);
     }
     fence_mbar_init();
-    s_items[0] = static_cast<int>(blockIdx.x);
+    s_items[0].x = first_item.bh;
     mbar_arrive(&item_full[0]);
     *abort_flag = earlier != 0u ? 1 : 0;
     if (earlier == 0u) {
@@ -268,7 +286,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_kslab);
       for (int t = 0; t < 2; ++t)
-        if (first_item.nkt[t] > 0) load_q(first_item, t);
+        if (first_item.nkt(t) > 0) load_q(first_item, t);
       for (int j = 0; j < first_item.nkt_max && j < kStages; ++j) {
         load_keys(first_item, j, j);
         load_values(first_item, j, j);
@@ -311,12 +329,12 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (lane == 0) {
       uint32_t G = 0, qn[2] = {0, 0};
       bool ok = true;
-      int w = static_cast<int>(blockIdx.x);
-      for (uint32_t n = 0; w >= 0 && ok && (kPersistent || n == 0); ++n) {
-        const Item it = (n == 0) ? first_item : get_item<kKeys>(w, heads, blocks, H, N, causal);
+      Item it = first_item;
+      bool more = true;
+      for (uint32_t n = 0; more && ok && (kPersistent || n == 0); ++n) {
         if (n != 0) {
           for (int t = 0; t < 2 && ok; ++t) {
-            if (it.nkt[t] == 0) continue;
+            if (it.nkt(t) == 0) continue;
             if (qn[t] > 0) ok = mbar_wait(&q_free[t], (qn[t] - 1) & 1, abort_flag, status, kSiteQFree);
             if (ok) load_q(it, t);
           }
@@ -339,16 +357,21 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         if (!ok) break;
         G += it.nkt_max;
-        for (int t = 0; t < 2; ++t) qn[t] += it.nkt[t] > 0 ? 1 : 0;
+        for (int t = 0; t < 2; ++t) qn[t] += it.nkt(t) > 0 ? 1 : 0;
         // Take and publish the next item number (or the end of the sequence) only now: all loads of this item are
         // issued, the other roles still have up to kStages key tiles of it ahead of them, which hides the counter's
         // round trip; taking items earlier leaves the launch's last items reserved by CTAs that are still busy.
-        w = take_item();
+        const int w = take_item();
+        more = w >= 0;
+        if (more) it = get_item<kKeys>(w, heads, blocks, H, N, causal);
         const int slot = (n + 1) % kItemSlots;
         if (n + 1 >= kItemSlots &&
             !mbar_wait(&item_empty[slot], (((n + 1) / kItemSlots) - 1) & 1, abort_flag, status, kSiteItemEmpty))
           break;
-        s_items[slot] = w;
+        s_items[slot].x = more ? it.bh : -1;
+        s_items[slot].y = it.b;
+        s_items[slot].z = it.h;
+        s_items[slot].w = it.m0;
         mbar_arrive(&item_full[slot]);
       }
     }
@@ -394,10 +417,9 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       uint32_t G = 0, ct = 0, qn = 0;
       bool ok = true;
       for (uint32_t n = 0; ok && (kPersistent || n == 0); ++n) {
-        const int w = read_item(n, false, ok);
-        if (w < 0) break;
-        const Item it = (n == 0) ? first_item : get_item<kKeys>(w, heads, blocks, H, N, causal);
-        const int my_nkt = it.nkt[t], nkt_max = it.nkt_max;
+        Item it;
+        if (!read_item(n, false, ok, it)) break;
+        const int my_nkt = it.nkt(t), nkt_max = it.nkt_max;
         // Every stage is released by both issuers: by a commit after this tile's last MMA that reads it, or - when
         // this tile has nothing (left) to do with it - by a plain arrival made only after the stage has been filled,
         // so that an idle issuer can never arrive twice within one phase.
@@ -484,10 +506,9 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
     for (uint32_t n = 0; ok && (kPersistent || n == 0); ++n) {
-      const int w = read_item(n, true, ok);
-      if (w < 0) break;
-      const Item it = (n == 0) ? first_item : get_item<kKeys>(w, heads, blocks, H, N, causal);
-      const int my_nkt = it.nkt[t];
+      Item it;
+      if (!read_item(n, true, ok, it)) break;
+      const int my_nkt = it.nkt(t);
       if (my_nkt == 0) continue;
       const int r0 = it.m0 + t * kTile;
       const int row = r0 + r;
