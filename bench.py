@@ -543,7 +543,14 @@ def e2e_leg(torch, dist, runner, w, device, world, steps):
     keep = [None, None]
     counter = [0]
 
+    in_flight = []                                   # one event per step whose read-back has been enqueued
+
     def step(compute=True):
+        # The host stays at most three steps ahead of the device (a stream of real batches could not be enqueued
+        # earlier either): with the whole run enqueued at once, the caching allocator never sees a finished
+        # read-back when it is asked for the next step's tensors and grows by a step's worth of memory per step.
+        if len(in_flight) >= 3:
+            in_flight.pop(0).synchronize()
         i = counter[0] & 1
         counter[0] += 1
         with torch.cuda.stream(s_in):
@@ -568,6 +575,9 @@ def e2e_leg(torch, dist, runner, w, device, world, steps):
                 dst.copy_(src, non_blocking=True)
                 src.record_stream(s_out)
             out_done[i].record(s_out)
+            done = torch.cuda.Event()
+            done.record(s_out)
+            in_flight.append(done)
         s_main.wait_event(out_done[i ^ 1])          # the timed stream ends only after the previous step's read-back
 
     def flush():

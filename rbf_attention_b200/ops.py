@@ -12,6 +12,7 @@ from __future__ import annotations
 import ctypes
 import math
 import os
+import time
 
 import torch
 
@@ -133,7 +134,7 @@ class _StatusMonitor:
     synchronise and check its own status (for debugging). Nothing is recorded while a CUDA graph is being captured.
     """
 
-    SLOTS = 64
+    SLOTS = 256
     _NOT_YET = -1          # slot value until the posting kernel has run (no status word is 0xffffffff: sites end at 250)
 
     def __init__(self, device):
@@ -188,10 +189,17 @@ class _StatusMonitor:
     def record(self, ws, what):
         if torch.cuda.is_current_stream_capturing():
             return
-        if self.pending == self.SLOTS:          # the ring is full: wait for its oldest entry
+        if self.pending == self.SLOTS:          # the ring is full: wait for its oldest entry, and for that one only
             self.poll()
             if self.pending == self.SLOTS:
-                torch.cuda.synchronize(self.device)
+                # (its kernel was enqueued SLOTS calls ago: the word arrives without any help from this thread. A
+                # device-wide synchronisation here would also drain the caller's copy streams.)
+                deadline = time.monotonic() + 10.0
+                while self.slots[self.oldest] == self._NOT_YET:
+                    if time.monotonic() > deadline:
+                        torch.cuda.synchronize(self.device)
+                        break
+                    time.sleep(0)
                 self._retire_oldest()
         i = self.next
         self.slots[i] = self._NOT_YET
