@@ -202,9 +202,10 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     // The loads below complete on barriers that other lanes have just initialised: besides the warp-level
     // synchronisation, order those generic-proxy writes before this thread's async-proxy operations. (The counter's
     // round trip, which the fence above waits for, also puts about 2000 clocks between the two. A variant that
-    // fetched the item number under the previous item's last steps, so that the loads followed the initialisation
-    // within about 100 clocks, ended with an unspecified launch failure and a bounded wait that ran out, and was
-    // withdrawn.)
+    // fetched the item number under the previous item's last steps, so that the loads followed the closing
+    // synchronisation within a few hundred clocks, ended with bounded waits that ran out - with and without this
+    // fence - for a reason that reading the code did not establish; it was withdrawn: do not move the counter's
+    // round trip out of this place without finding that reason.)
     fence_proxy_async_smem();
     *s_item = item;
     if (first_time) *abort_flag = 0;
