@@ -204,7 +204,7 @@ int rbf_b200_scale_unless_one(void* x, const float* factor, int64_t n, int dtype
 
 /* Synchronises `stream` and reads the device status word that the last call using `workspace` left:
  * 0 = ok, otherwise (site << 24 | work unit) of the bounded wait that ran out; the work unit is the linear block
- * index of the launch or, for the persistent backward kernel, the (key tile, batch-head) item. Returns
+ * index of the launch or, for the persistent kernels (head dim 64), the work item the block was on. Returns
  * RBF_B200_ERR_DEVICE when the word is non-zero. `workspace` = NULL reads the built-in scratch of the current
  * device, i.e. the status the last rbf_b200_fwd_static call left. No counterpart in the reference (its kernels have
  * no device-side waits). */

@@ -186,6 +186,8 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(smem + L::kMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMisc + 4);
   volatile int4* s_items = reinterpret_cast<volatile int4*>(smem + L::kMisc + 16);   // {bh (< 0: end), b, h, m0}
+  // work item the CTA's producer is loading (the status word of a wait that runs out names it, not the block index)
+  volatile int* s_unit = reinterpret_cast<volatile int*>(smem + L::kMisc + 8);
   constexpr int kItemSlots = L::kItemSlots;
   constexpr int kItemReaders = 2 + 8 * kSplit;   // two issuing threads, one arrival per softmax warp
 
@@ -216,7 +218,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       return false;
     }
     const int slot = n % kItemSlots;
-    if (!mbar_wait(&item_full[slot], (n / kItemSlots) & 1, abort_flag, status, kSiteItemFull)) {
+    if (!mbar_wait(&item_full[slot], (n / kItemSlots) & 1, abort_flag, status, kSiteItemFull, s_unit)) {
       ok_ref = false;
       return false;
     }
@@ -278,6 +280,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     fence_mbar_init();
     s_items[0].x = first_item.bh;
+    *s_unit = static_cast<int>(blockIdx.x);
     mbar_arrive(&item_full[0]);
     *abort_flag = earlier != 0u ? 1 : 0;
     if (earlier == 0u) {
@@ -335,7 +338,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (n != 0) {
           for (int t = 0; t < 2 && ok; ++t) {
             if (it.nkt(t) == 0) continue;
-            if (qn[t] > 0) ok = mbar_wait(&q_free[t], (qn[t] - 1) & 1, abort_flag, status, kSiteQFree);
+            if (qn[t] > 0) ok = mbar_wait(&q_free[t], (qn[t] - 1) & 1, abort_flag, status, kSiteQFree, s_unit);
             if (ok) load_q(it, t);
           }
         }
@@ -344,12 +347,12 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (n == 0 && j < kStages) continue;       // issued before the CTA-wide synchronisation
           const int st = g % kStages;
           const uint32_t par = ((g / kStages) - 1) & 1;
-          if (g >= kStages && !mbar_wait(&k_empty[st], par, abort_flag, status, kSiteKEmpty)) {
+          if (g >= kStages && !mbar_wait(&k_empty[st], par, abort_flag, status, kSiteKEmpty, s_unit)) {
             ok = false;
             break;
           }
           load_keys(it, j, st);
-          if (g >= kStages && !mbar_wait(&v_empty[st], par, abort_flag, status, kSiteVEmpty)) {
+          if (g >= kStages && !mbar_wait(&v_empty[st], par, abort_flag, status, kSiteVEmpty, s_unit)) {
             ok = false;
             break;
           }
@@ -363,10 +366,13 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // round trip; taking items earlier leaves the launch's last items reserved by CTAs that are still busy.
         const int w = take_item();
         more = w >= 0;
-        if (more) it = get_item<kKeys>(w, heads, blocks, H, N, causal);
+        if (more) {
+          it = get_item<kKeys>(w, heads, blocks, H, N, causal);
+          *s_unit = w;
+        }
         const int slot = (n + 1) % kItemSlots;
         if (n + 1 >= kItemSlots &&
-            !mbar_wait(&item_empty[slot], (((n + 1) / kItemSlots) - 1) & 1, abort_flag, status, kSiteItemEmpty))
+            !mbar_wait(&item_empty[slot], (((n + 1) / kItemSlots) - 1) & 1, abort_flag, status, kSiteItemEmpty, s_unit))
           break;
         s_items[slot].x = more ? it.bh : -1;
         s_items[slot].y = it.b;
@@ -409,10 +415,10 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         umma_commit(&o_done[t]);
       };
       auto wait_k = [&](uint32_t g) {
-        return mbar_wait(&k_full[g % kStages], (g / kStages) & 1, abort_flag, status, kSiteKFull);
+        return mbar_wait(&k_full[g % kStages], (g / kStages) & 1, abort_flag, status, kSiteKFull, s_unit);
       };
       auto wait_v = [&](uint32_t g) {
-        return mbar_wait(&v_full[g % kStages], (g / kStages) & 1, abort_flag, status, kSiteVFull);
+        return mbar_wait(&v_full[g % kStages], (g / kStages) & 1, abort_flag, status, kSiteVFull, s_unit);
       };
       uint32_t G = 0, ct = 0, qn = 0;
       bool ok = true;
@@ -426,8 +432,8 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (my_nkt > 0) {
           // first scores of the item: Q_t has landed, the first key tile has landed, and the group holds the last
           // scores of the previous item in registers (it is then busy with their exponentials and its output)
-          ok = mbar_wait(&q_full[t], qn & 1, abort_flag, status, kSiteQFull) && wait_k(G);
-          if (ok && ct > 0) ok = mbar_wait(&s_consumed[t], (ct - 1) & 1, abort_flag, status, kSiteSConsumed);
+          ok = mbar_wait(&q_full[t], qn & 1, abort_flag, status, kSiteQFull, s_unit) && wait_k(G);
+          if (ok && ct > 0) ok = mbar_wait(&s_consumed[t], (ct - 1) & 1, abort_flag, status, kSiteSConsumed, s_unit);
           if (!ok) break;
           tc_fence_after_sync();
           issue_s(G % kStages);
@@ -446,7 +452,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (j < my_nkt) {
             if (j + 1 < my_nkt) {
               // next scores first: they only need S_t(j) to have been read
-              ok = wait_k(g + 1) && mbar_wait(&s_consumed[t], (ct + j) & 1, abort_flag, status, kSiteSConsumed);
+              ok = wait_k(g + 1) && mbar_wait(&s_consumed[t], (ct + j) & 1, abort_flag, status, kSiteSConsumed, s_unit);
               if (!ok) break;
               tc_fence_after_sync();
               issue_s(st_next);
@@ -454,7 +460,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               used_k_next = true;
             }
             ok = wait_v(g);
-            ok = ok && mbar_wait(&p_full[t], (ct + j) & 1, abort_flag, status, kSitePFull);
+            ok = ok && mbar_wait(&p_full[t], (ct + j) & 1, abort_flag, status, kSitePFull, s_unit);
             if (!ok) break;
             tc_fence_after_sync();
             issue_o(st, j > 0 ? 1u : 0u);
@@ -520,7 +526,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       float ub = INFINITY;
       bool safe = false;                             // warp-wide: no row of this warp can overflow any more
       if (kSkipMax) {
-        ok = mbar_wait(&q_full[t], qn & 1, abort_flag, status, kSiteQFull);
+        ok = mbar_wait(&q_full[t], qn & 1, abort_flag, status, kSiteQFull, s_unit);
         if (!ok) break;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};         // independent sums: the chain is on every item's critical path
 #pragma unroll
@@ -539,7 +545,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       if (kPersistent) mbar_arrive_warp(&q_free[t]);   // this warp will not read Q_t of this item (again)
       for (int j = 0; j < my_nkt; ++j) {
-        ok = ok && mbar_wait(&s_full[t], (ct + j) & 1, abort_flag, status, kSiteSFull);
+        ok = ok && mbar_wait(&s_full[t], (ct + j) & 1, abort_flag, status, kSiteSFull, s_unit);
         if (!ok) break;
         tc_fence_after_sync();
 
@@ -589,7 +595,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (j > 0 && __any_sync(0xffffffffu, need)) {
               // O_t holds the sum over key tiles < j; wait until the last P V has landed, then rescale this thread's
               // share of the row.
-              ok = mbar_wait(&o_done[t], (ct + j - 1) & 1, abort_flag, status, kSiteODone);
+              ok = mbar_wait(&o_done[t], (ct + j - 1) & 1, abort_flag, status, kSiteODone, s_unit);
               if (!ok) break;
               tc_fence_after_sync();
 #pragma unroll
@@ -631,7 +637,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             packed[i + 1] = pack2<kBf16>(p2, p3);
           }
           if (!waited_o) {
-            ok = mbar_wait(&o_done[t], (ct + j - 1) & 1, abort_flag, status, kSitePFree);
+            ok = mbar_wait(&o_done[t], (ct + j - 1) & 1, abort_flag, status, kSitePFree, s_unit);
             if (!ok) break;
             tc_fence_after_sync();
             waited_o = true;
@@ -657,8 +663,8 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       if (!ok) break;
 
-      ok = mbar_wait(&o_done[t], (ct + my_nkt - 1) & 1, abort_flag, status, kSiteODoneFinal);
-      if (ok && kPersistent && qn > 0) ok = mbar_wait(&stage_free[t], (qn - 1) & 1, abort_flag, status, kSiteStageFree);
+      ok = mbar_wait(&o_done[t], (ct + my_nkt - 1) & 1, abort_flag, status, kSiteODoneFinal, s_unit);
+      if (ok && kPersistent && qn > 0) ok = mbar_wait(&stage_free[t], (qn - 1) & 1, abort_flag, status, kSiteStageFree, s_unit);
       if (!ok) break;
       tc_fence_after_sync();
       const float inv = kSoftmax ? (1.0f / l_sum) : 1.0f;
@@ -682,7 +688,7 @@ rbf_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_before_sync();                        // the output has been read: the next item may accumulate into O_t
       fence_proxy_async_smem();
       mbar_arrive_warp(&grp_sync[t]);
-      ok = mbar_wait(&grp_sync[t], qn & 1, abort_flag, status, kSiteGroup);
+      ok = mbar_wait(&grp_sync[t], qn & 1, abort_flag, status, kSiteGroup, s_unit);
       if (!ok) break;
       if (storer) {
         for (int x = 0; x < kBoxes; ++x) tma_store_4d(&tm_o, stage + x * kBoxBytes, x * 64, r0, it.h, it.b);
