@@ -80,3 +80,29 @@ def test_deterministic_switch_and_selftest_arguments(built_library):
     assert lib.rbf_b200_selftest_wait_timeout(0x10000, 256, 3_000_000_000, None) == 1
     code = ctypes.c_uint(5)
     assert lib.rbf_b200_read_device_status(0x10000, None, None) == 1
+
+
+def test_training_step_entries_validate_before_any_launch(built_library):
+    """Cross entropy, LayerNorm, column sums and the status post reject bad arguments without touching a device."""
+    lib = _lib.load()
+    p = 0x10000
+    assert lib.rbf_b200_cross_entropy(p, p, p, p, p, -1, 64, 64, 64, -100, 0, None) == 1
+    assert lib.rbf_b200_cross_entropy(p, p, p, p, p, 4, 0, 64, 64, -100, 0, None) == 1
+    assert lib.rbf_b200_cross_entropy(p, p, p, p, p, 4, 64, 64, 64, -100, 5, None) == 1 and b"dtype" in lib.rbf_b200_last_error()
+    assert lib.rbf_b200_cross_entropy(p, p, p, p, p, 4, 64, 32, 64, -100, 0, None) == 1      # pitch < width
+    assert lib.rbf_b200_cross_entropy(p, p, p, p, p, 0, 64, 64, 64, -100, 0, None) == 0      # nothing to do
+    assert lib.rbf_b200_cross_entropy(None, p, p, p, p, 4, 64, 64, 64, -100, 0, None) == 1
+    assert lib.rbf_b200_scale_unless_one(p, p, -1, 0, None) == 1
+    assert lib.rbf_b200_scale_unless_one(p, p, 0, 0, None) == 0
+    assert lib.rbf_b200_scale_unless_one(None, p, 8, 0, None) == 1
+    assert lib.rbf_b200_layer_norm_fwd(p, p, p, p, p, p, 8, 500, 1e-5, 0, None) == 1 and b"cols" in lib.rbf_b200_last_error()
+    assert lib.rbf_b200_layer_norm_fwd(p, p, p, p, p, p, 8, 512, 1e-5, 2, None) == 1
+    assert lib.rbf_b200_layer_norm_fwd(p, p, p, p, p, p, 0, 512, 1e-5, 0, None) == 0
+    assert lib.rbf_b200_layer_norm_fwd(p + 4, p, p, p, p, p, 8, 512, 1e-5, 0, None) == 2
+    assert lib.rbf_b200_layer_norm_bwd(p, p, p, p, p, p, None, p, p, 1 << 20, 8, 512, 0, None) == 1
+    assert lib.rbf_b200_column_sums(p, p, p, 1 << 20, 8, 12, 16, 0, None) == 1      # width not a multiple of 8
+    assert lib.rbf_b200_column_sums(p, p, p, 1 << 20, 8, 16, 12, 0, None) == 2      # pitch
+    assert lib.rbf_b200_column_sums(p + 2, p, p, 1 << 20, 8, 16, 16, 0, None) == 2  # alignment
+    assert lib.rbf_b200_column_sums(p, None, p, 1 << 20, 8, 16, 16, 0, None) == 1
+    assert lib.rbf_b200_post_device_status(None, p, None) == 1
+    assert lib.rbf_b200_post_device_status(p, None, None) == 1
