@@ -186,6 +186,16 @@ size_t rbf_b200_column_sums_workspace_bytes(int64_t rows, int cols);
 int rbf_b200_column_sums(const void* x, float* out, void* workspace, size_t workspace_bytes, int64_t rows, int cols,
                          int64_t ld, int dtype, void* stream);
 
+/* GELU in its exact (erf) form, nn.GELU() of the model's MLP (train_rbf_transformer.py:143), for 16-bit activations
+ * (dtype 0 = bfloat16, 1 = float16; 16-byte aligned, contiguous). Forward: out[i] = h[i] Phi(h[i]) for n elements, n a
+ * multiple of 8. Backward: dh = dy * (Phi(h) + h phi(h)) for a (rows x cols) matrix, cols a multiple of 8; with
+ * dbias != NULL the same pass also gives dbias[c] = sum over rows of dh[r, c] in fp32 (the bias gradient of the
+ * projection that produced h), through a workspace of rbf_b200_column_sums_workspace_bytes(rows, cols) bytes. Phi comes
+ * from a rational approximation with an absolute error below 1.5e-7. */
+int rbf_b200_gelu_fwd(const void* h, void* out, int64_t n, int dtype, void* stream);
+int rbf_b200_gelu_bwd(const void* h, const void* dy, void* dh, float* dbias, void* workspace, size_t workspace_bytes,
+                      int64_t rows, int cols, int dtype, void* stream);
+
 /* Cross entropy of the language-model training step: replaces torch.nn.CrossEntropyLoss(ignore_index=-100) and its
  * backward (train_rbf_transformer.py:282, 335-345). One kernel reads the logits (rows x cols, row pitch `ld` elements,
  * dtype 0 = bfloat16, 1 = float16, 2 = float32), writes loss_rows[r] = logsumexp(logits[r]) - logits[r, targets[r]] and

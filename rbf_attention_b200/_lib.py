@@ -75,6 +75,11 @@ SIGNATURES = {
         [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int64, ctypes.c_int, ctypes.c_int64,
          ctypes.c_int, ctypes.c_void_p],
     ),
+    "rbf_b200_gelu_fwd": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p]),
+    "rbf_b200_gelu_bwd": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 5 + [ctypes.c_size_t, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p],
+    ),
     "rbf_b200_cross_entropy": (
         ctypes.c_int,
         [ctypes.c_void_p] * 5 + [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,

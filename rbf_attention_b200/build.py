@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "librbf_b200.so")
 SOURCES = ["capi.cu", "rbf_prep.cu", "rbf_fwd.cu", "rbf_fwd_tf32.cu", "rbf_bwd.cu", "rbf_bwd_fused.cu",
-           "rbf_bwd_fused128.cu", "ce_loss.cu", "layer_norm.cu", "col_sums.cu"]
+           "rbf_bwd_fused128.cu", "ce_loss.cu", "layer_norm.cu", "col_sums.cu", "gelu.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",

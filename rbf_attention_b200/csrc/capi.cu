@@ -677,6 +677,42 @@ int rbf_b200_column_sums(const void* x, float* out, void* workspace, size_t work
 }
 
 // ---------------------------------------------------------------------------------------------
+// GELU of the model's MLP
+// ---------------------------------------------------------------------------------------------
+int rbf_b200_gelu_fwd(const void* h, void* out, int64_t n, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  if (n < 0 || n % 8 != 0) return fail(RBF_B200_ERR_BAD_ARGUMENT, "n must be a non-negative multiple of 8");
+  if (dtype != 0 && dtype != 1) return fail(RBF_B200_ERR_BAD_ARGUMENT, "dtype must be 0 (bf16) or 1 (fp16)");
+  if (n == 0) return RBF_B200_OK;
+  if (!h || !out) return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL pointer");
+  if (reinterpret_cast<uintptr_t>(h) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0)
+    return fail(RBF_B200_ERR_BAD_LAYOUT, "tensors must be 16-byte aligned");
+  const int sms = sm_count();
+  if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
+  const cudaError_t e = rbf::launch_gelu_fwd(h, out, n, dtype == 0, sms, static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "gelu launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+int rbf_b200_gelu_bwd(const void* h, const void* dy, void* dh, float* dbias, void* workspace, size_t workspace_bytes,
+                      int64_t rows, int cols, int dtype, void* stream_v) {
+  g_last_error[0] = 0;
+  if (rows < 0 || cols <= 0 || cols % 8 != 0) return fail(RBF_B200_ERR_BAD_ARGUMENT, "cols must be a positive multiple of 8");
+  if (dtype != 0 && dtype != 1) return fail(RBF_B200_ERR_BAD_ARGUMENT, "dtype must be 0 (bf16) or 1 (fp16)");
+  if (rows > 0 && (!h || !dy || !dh)) return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL tensor pointer");
+  for (const void* ptr : {h, dy, static_cast<const void*>(dh)})
+    if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "tensors must be 16-byte aligned");
+  if (dbias != nullptr && (!workspace || workspace_bytes < rbf_b200_column_sums_workspace_bytes(rows, cols)))
+    return fail(RBF_B200_ERR_WORKSPACE, "workspace too small: %zu bytes", workspace_bytes);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
+  const cudaError_t e = rbf::launch_gelu_bwd(h, dy, dh, rows, cols, dtype == 0, static_cast<float*>(workspace), dbias, sms,
+                                             static_cast<cudaStream_t>(stream_v));
+  if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "gelu backward launch failed: %s", cudaGetErrorString(e));
+  return RBF_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Cross entropy of the language-model training step
 // ---------------------------------------------------------------------------------------------
 int rbf_b200_cross_entropy(const void* logits, const int64_t* targets, const float* grad_scale, float* loss_rows,

@@ -83,6 +83,11 @@ int col_sums_bands(int64_t rows, int cols, int sms) {
   return static_cast<int>(bands < 1 ? 1 : bands);
 }
 
+cudaError_t launch_col_sums_final(const float* partials, int bands, int cols, float* out, cudaStream_t stream) {
+  col_sums_final_kernel<<<(cols + 31) / 32, 256, 0, stream>>>(partials, bands, cols, out);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_col_sums(const void* x, int64_t ld, int64_t rows, int cols, bool bf16, float* partials, float* out,
                             int sms, cudaStream_t stream) {
   const int bands = col_sums_bands(rows, cols, sms);

@@ -132,6 +132,15 @@ int col_sums_bands(int64_t rows, int cols, int sms);
 cudaError_t launch_col_sums(const void* x, int64_t ld, int64_t rows, int cols, bool bf16, float* partials, float* out,
                             int sms, cudaStream_t stream);
 
+cudaError_t launch_col_sums_final(const float* partials, int bands, int cols, float* out, cudaStream_t stream);
+
+// GELU (erf form) of 16-bit activations, gelu.cu. Forward: n elements, n a multiple of 8. Backward: dh = dy * gelu'(h)
+// for a contiguous (rows x cols) matrix, cols a multiple of 8; with dbias != nullptr also dbias[c] = sum_r dh[r, c]
+// (fp32), through `partials` (col_sums_bands() x cols floats).
+cudaError_t launch_gelu_fwd(const void* h, void* out, int64_t n, bool bf16, int sms, cudaStream_t stream);
+cudaError_t launch_gelu_bwd(const void* h, const void* dy, void* dh, int64_t rows, int cols, bool bf16, float* partials,
+                            float* dbias, int sms, cudaStream_t stream);
+
 // Cross entropy of the language-model step (ce_loss.cu): per-row losses and d(mean loss)/d(logits) in one kernel.
 struct CrossEntropyArgs {
   const void* logits;        // (rows, cols), row pitch ld elements

@@ -79,11 +79,14 @@ class TransformerBlock(nn.Module):
         return x + self._mlp(apply_layer_norm(self.ln2, x)), attn_weights
 
     def _mlp(self, x):
-        """``self.ff(x)`` (Linear, GELU, Linear) with the bias gradients of both projections from the library."""
+        """``self.ff(x)`` (Linear, GELU, Linear) with the activation, its backward and the bias gradients of both
+        projections from the library."""
         if x.is_cuda:
             from . import ops
 
-            return ops.linear(self.ff[2], self.ff[1](ops.linear(self.ff[0], x)))
+            exact_gelu = isinstance(self.ff[1], nn.GELU) and self.ff[1].approximate == "none"
+            hidden = ops.linear_gelu(self.ff[0], x) if exact_gelu else self.ff[1](ops.linear(self.ff[0], x))
+            return ops.linear(self.ff[2], hidden)
         return self.ff(x)
 
 

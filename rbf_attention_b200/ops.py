@@ -743,6 +743,79 @@ class _LinearBiasSum(torch.autograd.Function):
         return dx, dw, db
 
 
+@torch.library.custom_op("rbf_attn_b200::gelu_fwd", mutates_args=())
+def gelu_fwd(h: torch.Tensor) -> torch.Tensor:
+    """Exact (erf) GELU of a 16-bit CUDA tensor whose element count is a multiple of 8."""
+    if not h.is_cuda or h.dtype not in _DTYPE_CODE or h.numel() % 8 != 0:
+        raise ValueError("gelu_fwd: a 16-bit CUDA tensor with a multiple of 8 elements")
+    hc = h.contiguous()
+    out = torch.empty_like(hc)
+    with _OnDevice(h.device):
+        rc = _lib.load().rbf_b200_gelu_fwd(hc.data_ptr(), out.data_ptr(), hc.numel(), _DTYPE_CODE[h.dtype],
+                                           _stream_ptr(h.device))
+    _lib.check(rc, "rbf_b200_gelu_fwd")
+    return out
+
+
+@gelu_fwd.register_fake
+def _(h):
+    return torch.empty_like(h, memory_format=torch.contiguous_format)
+
+
+@torch.library.custom_op("rbf_attn_b200::gelu_bwd", mutates_args=())
+def gelu_bwd(h: torch.Tensor, dy: torch.Tensor, with_bias: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    """dh = dy * gelu'(h) for (..., cols) tensors and, with ``with_bias``, its fp32 sum over all leading dims."""
+    cols = h.shape[-1]
+    hc, gc = h.contiguous(), dy.to(h.dtype).contiguous()
+    rows = hc.numel() // cols
+    lib = _lib.load()
+    dh = torch.empty_like(hc)
+    dbias = torch.empty(cols if with_bias else 0, dtype=torch.float32, device=h.device)
+    with _OnDevice(h.device):
+        nbytes = lib.rbf_b200_column_sums_workspace_bytes(rows, cols) if with_bias else 0
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=h.device)
+        rc = lib.rbf_b200_gelu_bwd(hc.data_ptr(), gc.data_ptr(), dh.data_ptr(), dbias.data_ptr() if with_bias else None,
+                                   ws.data_ptr(), ws.numel(), rows, cols, _DTYPE_CODE[h.dtype], _stream_ptr(h.device))
+    _lib.check(rc, "rbf_b200_gelu_bwd")
+    return dh, dbias
+
+
+@gelu_bwd.register_fake
+def _(h, dy, with_bias):
+    return (torch.empty_like(h, memory_format=torch.contiguous_format),
+            h.new_empty(h.shape[-1] if with_bias else 0, dtype=torch.float32))
+
+
+class _LinearGelu(torch.autograd.Function):
+    """``gelu(F.linear(x, weight, bias))``: the GEMMs are PyTorch's, the activation and its backward - which also
+    yields the bias gradient - are the library's."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        h = torch.nn.functional.linear(x, weight, bias)
+        ctx.save_for_backward(x, weight, h)
+        return torch.ops.rbf_attn_b200.gelu_fwd(h)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight, h = ctx.saved_tensors
+        dh, dbias = torch.ops.rbf_attn_b200.gelu_bwd(h, g, ctx.needs_input_grad[2])
+        dh2 = dh.reshape(-1, dh.shape[-1])
+        dx = dh.matmul(weight) if ctx.needs_input_grad[0] else None
+        dw = dh2.t().mm(x.reshape(-1, x.shape[-1])) if ctx.needs_input_grad[1] else None
+        db = dbias.to(g.dtype) if ctx.needs_input_grad[2] else None
+        return dx, dw, db
+
+
+def linear_gelu(module: torch.nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    """``F.gelu(module(x))`` (exact form) on the library's kernels for 16-bit CUDA activations; anything else through
+    PyTorch."""
+    if (x.is_cuda and x.dtype in _DTYPE_CODE and module.bias is not None and module.weight.dtype == x.dtype
+            and module.out_features % 8 == 0):
+        return _LinearGelu.apply(x, module.weight, module.bias)
+    return torch.nn.functional.gelu(module(x))
+
+
 def linear(module: torch.nn.Linear, x: torch.Tensor) -> torch.Tensor:
     """``module(x)``; for 16-bit CUDA activations and a bias, the bias gradient comes from the library's column-sum
     kernel instead of PyTorch's generic reduction."""

@@ -106,3 +106,14 @@ def test_training_step_entries_validate_before_any_launch(built_library):
     assert lib.rbf_b200_column_sums(p, None, p, 1 << 20, 8, 16, 16, 0, None) == 1
     assert lib.rbf_b200_post_device_status(None, p, None) == 1
     assert lib.rbf_b200_post_device_status(p, None, None) == 1
+
+
+def test_gelu_entries_validate_before_any_launch(built_library):
+    lib = _lib.load()
+    p = 0x10000
+    assert lib.rbf_b200_gelu_fwd(p, p, 12, 0, None) == 1            # not a multiple of 8
+    assert lib.rbf_b200_gelu_fwd(p, p, 16, 2, None) == 1
+    assert lib.rbf_b200_gelu_fwd(p, p + 2, 16, 0, None) == 2
+    assert lib.rbf_b200_gelu_fwd(p, p, 0, 0, None) == 0
+    assert lib.rbf_b200_gelu_bwd(p, p, p, None, None, 0, 8, 20, 0, None) == 1
+    assert lib.rbf_b200_gelu_bwd(None, p, p, None, None, 0, 8, 16, 0, None) == 1

@@ -228,6 +228,49 @@ def test_column_sums_and_the_linear_layer_built_on_them(dtype, rows, cols, ld):
         assert (lin.bias.grad.double() - exact).abs().max().item() <= tol
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gelu_kernels_match_the_exact_form(dtype):
+    """``ops.gelu_fwd`` / ``gelu_bwd`` against the erf form evaluated in fp64 on the same 16-bit values, over the
+    whole range that matters (-12 ... 12, dense around 0): the normal distribution function is approximated with an
+    absolute error below 1.5e-7, so outputs agree with the correctly rounded result to within one rounding step of
+    the dtype (relative 2^-8 bf16 / 2^-11 fp16, plus 3e-7 absolute for values near zero); the bias gradient is the
+    fp32 sum of the stored dh. ``ops.linear_gelu`` against ``F.gelu(linear(x))``."""
+    from rbf_attention_b200 import ops
+
+    rows, cols = 515, 2048
+    g = torch.Generator().manual_seed(5)
+    h = torch.cat([torch.linspace(-12, 12, rows * cols // 2), torch.randn(rows * cols // 2, generator=g) * 1.5])
+    h = h[torch.randperm(rows * cols, generator=g)].reshape(rows, cols).to(dtype)
+    dy = torch.randn(rows, cols, generator=g).to(dtype)
+    x = h.double().requires_grad_(True)
+    ref = F.gelu(x)
+    ref.backward(dy.double())
+    rel = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    out = ops.gelu_fwd(h.to(DEV)).double().cpu()
+    assert ((out - ref.detach()).abs() <= rel * ref.detach().abs() + 3e-7).all()      # 3e-7 covers fp16's subnormals too
+    dh, db = ops.gelu_bwd(h.to(DEV), dy.to(DEV), True)
+    tiny = 0.0 if dtype == torch.bfloat16 else 6e-8          # fp16 subnormals: spacing 2^-24
+    assert ((dh.double().cpu() - x.grad).abs() <= rel * x.grad.abs() + 3e-7 * dy.double().abs() + tiny).all()
+    want_db = dh.double().sum(0).cpu()
+    assert ((db.double().cpu() - want_db).abs() <= 1e-5 * dh.double().abs().sum(0).cpu() + 1e-6).all()
+    dh2, db2 = ops.gelu_bwd(h.to(DEV), dy.to(DEV), False)
+    assert torch.equal(dh, dh2) and db2.numel() == 0
+    # the fused module path against PyTorch's
+    torch.manual_seed(2)
+    lin = torch.nn.Linear(256, 1024).to(DEV, dtype)
+    inp = torch.randn(4, 100, 256, device=DEV, dtype=dtype)
+    gy = torch.randn(4, 100, 1024, device=DEV, dtype=dtype)
+    a = inp.clone().requires_grad_(True)
+    F.gelu(lin(a)).backward(gy)
+    ref_g = (a.grad.clone(), lin.weight.grad.clone(), lin.bias.grad.clone())
+    lin.zero_grad()
+    b = inp.clone().requires_grad_(True)
+    ops.linear_gelu(lin, b).backward(gy)
+    for got, want in zip((b.grad, lin.weight.grad, lin.bias.grad), ref_g):
+        rep = oracle.error_report(got.float().cpu(), want.float().cpu())
+        assert rep["rel_l2"] <= (6e-3 if dtype == torch.bfloat16 else 1e-3), rep
+
+
 def test_cross_entropy_through_the_c_abi_with_a_row_pitch():
     """Raw pointers, a logits view with a row pitch larger than its width, every row ignored but two."""
     from rbf_attention_b200 import _lib
