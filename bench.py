@@ -842,7 +842,11 @@ def lm_step_record(torch, dist, rank, world, local_rank, steps, warmup, compile_
                      "peak_source": peak_src},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": LM_UNIT, "h2d_bytes_per_step": ids_host.numel() * 8,
                 "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
-        "gpu_launches": LM["layers"] * LAUNCHES_PER_STEP * steps, "clocks": clocks.summary()}
+        # the library's own launches per step: per layer 6 forward (2 LayerNorm, q/k preparation, attention, status
+        # post, GELU) and 18 backward (GELU + its bias sum 2, three bias sums 6, 2 LayerNorm 4, attention pre-pass,
+        # main kernel, dQ conversion, status post, position gradients 2); per model the last LayerNorm (1 + 2), the
+        # loss kernel and its rescale
+        "gpu_launches": (LM["layers"] * 24 + 5) * steps, "clocks": clocks.summary()}
 
 
 def run_lm(args, rank, world, local_rank):
