@@ -410,6 +410,27 @@ def also_layer(torch, device):
                     fwd = time_loop(torch, lambda: layer(x)[0], 20)
                 both = time_loop(torch, fwd_bwd, 20)
                 rec[label] = {"fwd_ms": fwd, "bwd_ms": both - fwd}
+                if label == "block_operator":
+                    # the same forward + backward replayed from a CUDA graph: what the layer costs on the device once
+                    # the host's launch rate (about 85 launches per iteration) is out of the way
+                    try:
+                        side = torch.cuda.Stream(device)
+                        side.wait_stream(torch.cuda.current_stream(device))
+                        with torch.cuda.stream(side):
+                            for _ in range(3):
+                                fwd_bwd()
+                        torch.cuda.current_stream(device).wait_stream(side)
+                        graph = torch.cuda.CUDAGraph()
+                        x.grad = None
+                        with torch.cuda.graph(graph):
+                            y, _ = layer(x)
+                            y.backward(dout)
+                        for _ in range(3):
+                            graph.replay()
+                        rec["block_operator_cuda_graph"] = {"fwd_plus_bwd_ms": time_loop(torch, graph.replay, 20)}
+                        del graph
+                    except Exception as exc:      # capture is an extra: the eager numbers above stand without it
+                        rec["block_operator_cuda_graph"] = {"error": repr(exc)[:200]}
             out["by_N"][str(n)] = rec
     except Exception as exc:
         out["error"] = repr(exc)[:300]
