@@ -206,6 +206,43 @@ def test_persistent_forward_queue_and_workspace_reuse(causal, softmax):
             assert (lse[sl].cpu() - ref_l).abs().max().item() <= 2e-4 * max(1.0, ref_l.abs().max().item())
 
 
+def test_operators_capture_into_a_cuda_graph():
+    """Forward + backward of the operator captured with ``torch.cuda.graph`` (the library allocates nothing itself,
+    the bindings allocate through torch's capture-aware allocator and post no status word while a stream captures,
+    the persistent kernels put their work counters back themselves): replayed on new data in the static input
+    buffers, the graph reproduces the eager results bit for bit (dQ to rounding)."""
+    B, H, N, D = 2, 12, 1000, 64                      # 96 forward and 192 backward work items
+    q, k, v, do = oracle.make_inputs(B, H, N, D, seed=41, dtype=torch.bfloat16, key_norm_sigma=0.3)
+    sq, sk, sv = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    sdo = do.to(DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            ops.run_triton_rbf(sq, sk, sv, True).backward(sdo)
+    torch.cuda.current_stream().wait_stream(side)
+    ops.check_device_status()
+    sq.grad = sk.grad = sv.grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = ops.run_triton_rbf(sq, sk, sv, True)
+        out.backward(sdo)
+    for seed in (42, 43):
+        q2, k2, v2, do2 = oracle.make_inputs(B, H, N, D, seed=seed, dtype=torch.bfloat16, key_norm_sigma=0.3)
+        with torch.no_grad():
+            for dst, src in zip((sq, sk, sv, sdo), (q2, k2, v2, do2)):
+                dst.copy_(src)
+        graph.replay()
+        torch.cuda.synchronize()
+        got = (out.clone(), sq.grad.clone(), sk.grad.clone(), sv.grad.clone())
+        eq, ek, ev = (t.to(DEV).requires_grad_(True) for t in (q2, k2, v2))
+        eo = ops.run_triton_rbf(eq, ek, ev, True)
+        eo.backward(do2.to(DEV))
+        ops.check_device_status()
+        assert torch.equal(got[0], eo) and torch.equal(got[2], ek.grad) and torch.equal(got[3], ev.grad)
+        assert oracle.error_report(got[1].float().cpu(), eq.grad.float().cpu())["rel_l2"] <= 1e-3
+
+
 @pytest.mark.parametrize("D", [64, 128])
 def test_deterministic_switch_gives_bitwise_reproducible_gradients(D):
     """rbf_b200_set_deterministic(1): the softmax backward runs as two kernels with a fixed summation order; dQ is
