@@ -90,8 +90,8 @@ struct Params {
 
 // The launch is persistent: as many CTAs as SMs, each taking (key tile, batch-head) items from a global counter in the
 // order a plain grid would run them (key tile fastest, heaviest causal tile first). Between items a CTA keeps its
-// TMEM allocation and only re-initialises its barriers, which saves the launch gap and most of the set-up of a CTA
-// (about 1.5 of the 6.5 microseconds that an item spends outside its step loop).
+// TMEM allocation and its barriers (their phases run on), which saves the launch gap and most of the set-up of a
+// CTA (about 1.5 of the 6.5 microseconds that an item spent outside its step loop).
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -137,6 +137,11 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   const int lane = tid & 31;
   const int n_tiles = (p.N + kTile - 1) / kTile;
   volatile int* s_item = reinterpret_cast<volatile int*>(smem + Smem::kMisc + 8);
+  // Barriers are initialised once per CTA and run on across its items: T counts the steps of the CTA's earlier items
+  // (step n of the item is global step T + n: ring stage (T + n) % kStages, phase ((T + n) / kStages) & 1; per-step
+  // barriers are in phase (T + n) & 1), I counts the earlier items (per-item barriers are in phase I & 1). Every role
+  // advances both at the item's closing synchronisation.
+  uint32_t T = 0, I = 0;
   // the current work item
   int bh = 0, b = 0, h = 0;
   int kt = 0;                                      // key tile; tile 0 is the heaviest under the causal mask
@@ -159,7 +164,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
   // tiles travel while TMEM is allocated and the constant slab is written.
   auto load_step = [&](int n) {
     const int row0 = (first + n) * kTile;
-    const int st = n % kStages;
+    const int st = (T + n) % kStages;
     mbar_arrive_expect_tx(&q_full[st], kTileBytes + kSlabBytes);
     tma_load_4d(s_q + st * kTileBytes, &tm_q, &q_full[st], 0, row0, h, b);
     tma_load_3d(s_lslab + st * kSlabBytes, &tm_lslab, &q_full[st], 0, row0, bh);
@@ -168,9 +173,15 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     tma_load_3d(s_dslab + st * kSlabBytes, &tm_dslab, &do_full[st], 0, row0, bh);
   };
   // Executed by the producer warp before every item's opening synchronisation (nothing of the previous item is in
-  // flight any more): lane 0 takes the next item and reads the launch's status word, and while those two round trips
-  // to L2 are under way the warp re-initialises the barriers, one per lane (one thread doing all 25 in turn took
-  // about 1500 clocks per item); then lane 0 issues the item's first loads.
+  // flight any more): lane 0 takes the next item and reads the launch's status word, then issues the item's first
+  // loads. The barriers are initialised by the first call only, one per lane, and run on across the CTA's items (T, I
+  // above). An earlier form invalidated and re-initialised all of them here for every item; it worked as long as the
+  // work counter's round trip (about 2000 clocks) lay between that and the loads, and ran into bounded waits that
+  // never completed - a load whose completion was lost - as soon as the loads followed within a few hundred clocks,
+  // with or without a proxy fence in between. Without re-initialisation the loads may follow at once (measured with
+  // the item number taken under the previous item's last steps: correct, and no faster, because what an item waits
+  // for at its start is the arrival of its first 70 KB, about 4000 clocks however early the request is made after
+  // the closing synchronisation).
   auto prepare_item = [&](bool first_time) {
     int item = 0;
     unsigned int earlier = 0u;
@@ -193,19 +204,13 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                                        kNumComputeWarps, 2, 4, 3, kNumComputeWarps, 2};
         count = tail[lane - (1 + 4 * kStages)];
       }
-      if (!first_time) mbar_inval(&bars[lane]);
-      mbar_init(&bars[lane], count);
+      if (first_time) mbar_init(&bars[lane], count);
     }
-    fence_mbar_init();
+    if (first_time) fence_mbar_init();
     __syncwarp();
     if (lane != 0) return;
-    // The loads below complete on barriers that other lanes have just initialised: besides the warp-level
-    // synchronisation, order those generic-proxy writes before this thread's async-proxy operations. (The counter's
-    // round trip, which the fence above waits for, also puts about 2000 clocks between the two. A variant that
-    // fetched the item number under the previous item's last steps, so that the loads followed the closing
-    // synchronisation within a few hundred clocks, ended with bounded waits that ran out - with and without this
-    // fence - for a reason that reading the code did not establish; it was withdrawn: do not move the counter's
-    // round trip out of this place without finding that reason.)
+    // first call: the loads below complete on barriers that other lanes have just initialised; besides the warp-level
+    // synchronisation, order those generic-proxy writes before this thread's async-proxy operations
     fence_proxy_async_smem();
     *s_item = item;
     if (first_time) *abort_flag = 0;
@@ -260,8 +265,8 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     while (open_item()) {
       if (lane == 0) {
         for (int n = kStages; n < cnt; ++n) {
-          const int st = n % kStages;
-          const uint32_t par = ((n / kStages) - 1) & 1;
+          const int st = (T + n) % kStages;
+          const uint32_t par = (((T + n) / kStages) - 1) & 1;
           // the ring slot is free once the MMAs that read it have completed (both rings, in the order the loads go)
           if (!mbar_wait(&q_empty[st], par, abort_flag, p.status, kSiteQEmpty, s_item)) break;
           if (!mbar_wait(&do_empty[st], par, abort_flag, p.status, kSiteDoEmpty, s_item)) break;
@@ -269,6 +274,8 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         }
       }
       __syncthreads();                       // closing synchronisation: every role is done with the item
+      T += cnt;
+      ++I;
       prepare_item(false);
     }
   } else if (warp == kMmaWarpA || warp == kMmaWarpB || warp == kMmaWarpC) {
@@ -292,12 +299,12 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         umma_ss(dst, sdesc_at(ones_desc, 0), sdesc_at(slab, 0), idesc_s, 1u);
       };
       auto wait_q = [&](int n) {
-        return mbar_wait(&q_full[n % kStages], (n / kStages) & 1, abort_flag, p.status, kSiteQFull, s_item);
+        return mbar_wait(&q_full[(T + n) % kStages], ((T + n) / kStages) & 1, abort_flag, p.status, kSiteQFull, s_item);
       };
       auto wait_do = [&](int n) {
-        return mbar_wait(&do_full[n % kStages], (n / kStages) & 1, abort_flag, p.status, kSiteDoFull, s_item);
+        return mbar_wait(&do_full[(T + n) % kStages], ((T + n) / kStages) & 1, abort_flag, p.status, kSiteDoFull, s_item);
       };
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, kSiteKV, s_item);
+      bool ok = mbar_wait(kv_full, I & 1, abort_flag, p.status, kSiteKV, s_item);
 
       if (warp == kMmaWarpA) {
         const SmemDesc k_kmaj = make_sdesc_parts(smem_u32(s_k), 16, 1024);
@@ -307,15 +314,16 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         if (ok) ok = wait_q(0);
         if (ok) {
           tc_fence_after_sync();
-          issue_scores(tmem + kColS, k_kmaj, q_kmaj0, lslab0);
+          issue_scores(tmem + kColS, k_kmaj, stage_of(q_kmaj0, T % kStages, kTileBytes),
+                       stage_of(lslab0, T % kStages, kSlabBytes));
           umma_commit(s_full);
-          umma_commit(&q_empty[0]);
+          umma_commit(&q_empty[T % kStages]);
         }
         for (int n = 0; n < cnt && ok; ++n) {
           if (n + 1 < cnt) {
             // S^T(n+1) may overwrite S^T(n) as soon as every compute warp holds it in registers
-            const int st = (n + 1) % kStages;
-            ok = wait_q(n + 1) && mbar_wait(s_consumed, n & 1, abort_flag, p.status, kSiteSConsumed, s_item);
+            const int st = (T + n + 1) % kStages;
+            ok = wait_q(n + 1) && mbar_wait(s_consumed, (T + n) & 1, abort_flag, p.status, kSiteSConsumed, s_item);
             if (!ok) break;
             tc_fence_after_sync();
             issue_scores(tmem + kColS, k_kmaj, stage_of(q_kmaj0, st, kTileBytes), stage_of(lslab0, st, kSlabBytes));
@@ -323,24 +331,24 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             umma_commit(&q_empty[st]);
           }
           // dV += P^T dO
-          ok = mbar_wait(p_full, n & 1, abort_flag, p.status, kSitePFull, s_item);
+          ok = mbar_wait(p_full, (T + n) & 1, abort_flag, p.status, kSitePFull, s_item);
           if (!ok) break;
           tc_fence_after_sync();
-          const SmemDesc do_n = stage_of(do_nmaj0, n % kStages, kTileBytes);
+          const SmemDesc do_n = stage_of(do_nmaj0, (T + n) % kStages, kTileBytes);
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
             umma_ts(tmem + kColDV, tmem + kColPT + kk * 8, sdesc_at(do_n, kk * 2048), idesc_acc,
                     (n > 0 || kk > 0) ? 1u : 0u);
           umma_commit(dv_done);
-          umma_commit(&do_empty[n % kStages]);
+          umma_commit(&do_empty[(T + n) % kStages]);
         }
       } else if (warp == kMmaWarpC) {
         // dQ_partial = dS K : A = the dS^T tile read M-major (rows = keys = reduction index), B = K read N-major
         const SmemDesc k_nmaj = make_sdesc_parts(smem_u32(s_k), kTile * 128, 1024);
         const SmemDesc ds_mmaj = make_sdesc_parts(smem_u32(s_ds), kTile * 128, 1024);   // rows = reduction (keys)
         for (int n = 0; n < cnt && ok; ++n) {
-          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull, s_item);
-          if (ok && n > 0) ok = mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, kSiteDQDrained, s_item);
+          ok = mbar_wait(ds_full, (T + n) & 1, abort_flag, p.status, kSiteDSFull, s_item);
+          if (ok && n > 0) ok = mbar_wait(dq_drained, (T + n - 1) & 1, abort_flag, p.status, kSiteDQDrained, s_item);
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
@@ -357,14 +365,15 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         if (ok) ok = wait_do(0);
         if (ok) {
           tc_fence_after_sync();
-          issue_scores(tmem + kColDP, v_kmaj, do_kmaj0, dslab0);
+          issue_scores(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, T % kStages, kTileBytes),
+                       stage_of(dslab0, T % kStages, kSlabBytes));
           umma_commit(dp_full);
-          umma_commit(&do_empty[0]);
+          umma_commit(&do_empty[T % kStages]);
         }
         for (int n = 0; n < cnt && ok; ++n) {
           if (n + 1 < cnt) {
-            const int st = (n + 1) % kStages;
-            ok = wait_do(n + 1) && mbar_wait(dp_consumed, n & 1, abort_flag, p.status, kSiteDPConsumed, s_item);
+            const int st = (T + n + 1) % kStages;
+            ok = wait_do(n + 1) && mbar_wait(dp_consumed, (T + n) & 1, abort_flag, p.status, kSiteDPConsumed, s_item);
             if (!ok) break;
             tc_fence_after_sync();
             issue_scores(tmem + kColDP, v_kmaj, stage_of(do_kmaj0, st, kTileBytes), stage_of(dslab0, st, kSlabBytes));
@@ -372,21 +381,23 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             umma_commit(&do_empty[st]);
           }
           // dK += dS^T Q : A = dS^T tile (K-major: 64-query boxes of 128-byte rows), B = Q read N-major
-          ok = mbar_wait(ds_full, n & 1, abort_flag, p.status, kSiteDSFull, s_item);
+          ok = mbar_wait(ds_full, (T + n) & 1, abort_flag, p.status, kSiteDSFull, s_item);
           if (!ok) break;
           tc_fence_after_sync();
-          const SmemDesc q_n = stage_of(q_nmaj0, n % kStages, kTileBytes);
+          const SmemDesc q_n = stage_of(q_nmaj0, (T + n) % kStages, kTileBytes);
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
             umma_ss(tmem + kColDK, sdesc_at(ds_kmaj, (kk >> 2) * (kTile * 128) + (kk & 3) * 32), sdesc_at(q_n, kk * 2048),
                     idesc_acc, (n > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(&q_empty[n % kStages]);
+          umma_commit(&q_empty[(T + n) % kStages]);
           umma_commit(dq_full);                    // first of two arrivals: the dS^T tile's K-major reader is done
         }
       }
       if (ok) umma_commit(acc_done);   // every issuer arrives: the barrier counts three
     }
     __syncthreads();                         // closing synchronisation
+    T += cnt;
+    ++I;
     }
   } else if (warp >= kDrainWarp0) {
     // ------------------------------------------------------------------ dQ_partial drain (thread = query row)
@@ -402,7 +413,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     tmem = *tmem_base_s;
     bool ok = true;
     for (int n = 0; n < cnt; ++n) {
-      ok = mbar_wait(dq_full, n & 1, abort_flag, p.status, kSiteDQFull, s_item);
+      ok = mbar_wait(dq_full, (T + n) & 1, abort_flag, p.status, kSiteDQFull, s_item);
       if (!ok) break;
       tc_fence_after_sync();
 #pragma unroll
@@ -432,6 +443,8 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     }
     if (lane == 0) tma_store_wait_all();
     __syncthreads();                         // closing synchronisation
+    T += cnt;
+    ++I;
     }
   } else {
     // ------------------------------------------------------------------ compute groups (thread = key row)
@@ -439,6 +452,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const int g = (warp - kComputeWarp0) >> 2;             // 32-column slice of the query tile
     const int r = tid & (kTile - 1);
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint32_t grp_phase = 0;                       // two rendezvous per item, counted across items
     const bool storer = r == 0 && (g & 1) == 0;   // issues the item's dK (g = 0) or dV (g = 2) store
     bool store_pending = false;
     while (open_item()) {
@@ -456,7 +470,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     }
 
     for (int n = 0; n < cnt; ++n) {
-      ok = mbar_wait(s_full, n & 1, abort_flag, p.status, kSiteSFull, s_item);
+      ok = mbar_wait(s_full, (T + n) & 1, abort_flag, p.status, kSiteSFull, s_item);
       if (!ok) break;
       tc_fence_after_sync();
       float pr[32];
@@ -487,7 +501,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         for (int i = 0; i < 16; ++i) packed[i] = pack2<kBf16>(pr[2 * i], pr[2 * i + 1]);
         // the P^T columns are free once dV of the previous step has completed
         if (n > 0) {
-          ok = mbar_wait(dv_done, (n - 1) & 1, abort_flag, p.status, kSiteDVDone, s_item);
+          ok = mbar_wait(dv_done, (T + n - 1) & 1, abort_flag, p.status, kSiteDVDone, s_item);
           if (!ok) break;
           tc_fence_after_sync();
         }
@@ -497,7 +511,7 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         mbar_arrive_warp(p_full);
       }
 
-      ok = mbar_wait(dp_full, n & 1, abort_flag, p.status, kSiteDPFull, s_item);
+      ok = mbar_wait(dp_full, (T + n) & 1, abort_flag, p.status, kSiteDPFull, s_item);
       if (!ok) break;
       tc_fence_after_sync();
       uint32_t ds_packed[16];
@@ -520,8 +534,8 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       }
       // the dS^T tile is free once dK and dQ_partial of the previous step have completed (first step: once the
       // previous item's output stores have read it)
-      ok = n > 0 ? mbar_wait(dq_full, (n - 1) & 1, abort_flag, p.status, kSiteDsFree, s_item)
-                 : mbar_wait(stage_free, 0, abort_flag, p.status, kSiteStageFree, s_item);
+      ok = n > 0 ? mbar_wait(dq_full, (T + n - 1) & 1, abort_flag, p.status, kSiteDsFree, s_item)
+                 : mbar_wait(stage_free, I & 1, abort_flag, p.status, kSiteStageFree, s_item);
       if (!ok) break;
       // row r of the [key][query] tile, box g/2, 16-byte chunks 4(g%2) .. +3
 #pragma unroll
@@ -532,14 +546,13 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       mbar_arrive_warp(ds_full);
     }
 
-    uint32_t grp_phase = 0;
     auto group_sync = [&]() -> bool {
       mbar_arrive_warp(grp_sync);
       const bool done = mbar_wait(grp_sync, grp_phase & 1, abort_flag, p.status, kSiteGroup, s_item);
       ++grp_phase;
       return done;
     };
-    if (ok) ok = mbar_wait(acc_done, 0, abort_flag, p.status, kSiteAccDone, s_item);
+    if (ok) ok = mbar_wait(acc_done, I & 1, abort_flag, p.status, kSiteAccDone, s_item);
     if (ok) {
       tc_fence_after_sync();
       s_rowsum[g * kTile + r] = ds_rowsum;      // every group holds a quarter of rowsum(dS^T)
@@ -580,6 +593,8 @@ rbf_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       }
     }
     __syncthreads();                         // closing synchronisation
+    T += cnt;
+    ++I;
     }
     if (storer && store_pending) tma_store_wait_read();
   }
