@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define RBF_B200_ABI_VERSION 2
+#define RBF_B200_ABI_VERSION 3
 
 enum {
   RBF_B200_OK = 0,

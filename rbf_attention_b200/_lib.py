@@ -12,7 +12,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "librbf_b200.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 STATUS_NAMES = {
     0: "ok",
