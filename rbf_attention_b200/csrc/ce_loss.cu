@@ -202,8 +202,11 @@ __global__ void __launch_bounds__(256) scale_unless_one_kernel(void* x_v, const 
     for (int j = 0; j < V; ++j) e[j] = E::from_float(E::to_float(e[j]) * f);
     reinterpret_cast<uint4*>(x + head)[i] = raw;
   }
-  for (int64_t i = first; i < n; i += stride)     // the few elements outside the vector body
-    if (i < head || i >= head + nvec * V) x[i] = E::from_float(E::to_float(x[i]) * f);
+  const int64_t body_end = head + nvec * V;       // the few elements outside the vector body
+  for (int64_t i = first; i < head + (n - body_end); i += stride) {
+    const int64_t at = i < head ? i : body_end + (i - head);
+    x[at] = E::from_float(E::to_float(x[at]) * f);
+  }
 }
 
 template <int kDtype>

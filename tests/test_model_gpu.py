@@ -162,6 +162,22 @@ def test_cross_entropy_kernel_matches_torch(dtype, rows, cols):
     assert ((x2.grad.double().cpu() * 1.7 - want).abs() / scale).max().item() <= 2 * tol
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("offset,n", [(0, 4096), (3, 1003), (5, 6), (1, 70001)])
+def test_in_place_scaling_of_a_gradient_on_any_alignment(dtype, offset, n):
+    """``scale_unless_one_`` (the pass that applies a non-unit upstream gradient to the logit gradient): a buffer that
+    starts off a 16-byte boundary and ends off one gets every element scaled exactly once (one rounding of the
+    product, as torch's ``mul_`` gives), and the factor 1 leaves the bits alone."""
+    base = torch.randn(offset + n + 8, generator=torch.Generator().manual_seed(n)).to(dtype).to(DEV)
+    want = base.clone()
+    want[offset:offset + n].mul_(0.37)
+    factor = torch.tensor(0.37, device=DEV)
+    torch.ops.rbf_attn_b200.scale_unless_one_(base[offset:offset + n], factor)
+    assert torch.equal(base, want)                          # the neighbours on both sides untouched
+    torch.ops.rbf_attn_b200.scale_unless_one_(base[offset:offset + n], torch.ones((), device=DEV))
+    assert torch.equal(base, want)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows,cols", [(4113, 512), (77, 256), (1, 1024), (300, 768)])
 def test_layer_norm_kernels_match_torch(dtype, rows, cols):
