@@ -178,6 +178,19 @@ int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, co
                             void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
                             int64_t rows, int cols, int dtype, void* stream);
 
+/* The same two passes with the block's residual connection folded in (x = x + f(x) followed by the next LayerNorm,
+ * train_rbf_transformer.py:152-161). Forward: sum_out = x + residual rounded to the dtype (exactly what the separate
+ * addition leaves; sum_out may be x or residual itself, not y) and y = LayerNorm(sum_out); residual and sum_out are
+ * both NULL (then this is rbf_b200_layer_norm_fwd) or both set. Backward: x is the forward's sum_out, and `dres`
+ * (NULL, or the gradient that reaches sum_out from its other consumers; may be dx itself) is added to dx in fp32
+ * before dx is rounded - dx is then the gradient of both x and residual. */
+int rbf_b200_add_layer_norm_fwd(const void* x, const void* residual, void* sum_out, const void* gamma, const void* beta,
+                                void* y, float* mean, float* rstd, int64_t rows, int cols, float eps, int dtype,
+                                void* stream);
+int rbf_b200_layer_norm_bwd_add(const void* x, const void* dy, const void* dres, const void* gamma, const float* mean,
+                                const float* rstd, void* dx, float* dgamma, float* dbeta, void* workspace,
+                                size_t workspace_bytes, int64_t rows, int cols, int dtype, void* stream);
+
 /* out[c] = sum over r of x[r, c] in fp32 for a 16-bit matrix (rows x cols, row pitch `ld` elements, cols and ld
  * multiples of 8, 16-byte aligned base; dtype 0 = bfloat16, 1 = float16): the bias gradient of a linear layer
  * (`nn.Linear` in train_rbf_transformer.py:143, 216 and rbf_attention.py:1625-1626), which PyTorch computes with a

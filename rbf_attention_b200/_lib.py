@@ -69,6 +69,14 @@ SIGNATURES = {
         ctypes.c_int,
         [ctypes.c_void_p] * 9 + [ctypes.c_size_t, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p],
     ),
+    "rbf_b200_add_layer_norm_fwd": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 8 + [ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p],
+    ),
+    "rbf_b200_layer_norm_bwd_add": (
+        ctypes.c_int,
+        [ctypes.c_void_p] * 10 + [ctypes.c_size_t, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p],
+    ),
     "rbf_b200_column_sums_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int64, ctypes.c_int]),
     "rbf_b200_column_sums": (
         ctypes.c_int,

@@ -602,22 +602,32 @@ static int check_layer_norm(int64_t rows, int cols, int dtype) {
   return RBF_B200_OK;
 }
 
-int rbf_b200_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
-                            int64_t rows, int cols, float eps, int dtype, void* stream_v) {
+int rbf_b200_add_layer_norm_fwd(const void* x, const void* residual, void* sum_out, const void* gamma, const void* beta,
+                                void* y, float* mean, float* rstd, int64_t rows, int cols, float eps, int dtype,
+                                void* stream_v) {
   g_last_error[0] = 0;
   int rc;
   if ((rc = check_layer_norm(rows, cols, dtype))) return rc;
+  if ((residual == nullptr) != (sum_out == nullptr))
+    return fail(RBF_B200_ERR_BAD_ARGUMENT, "residual and sum_out go together: both NULL or both set");
   if (rows == 0) return RBF_B200_OK;
   if (!x || !gamma || !beta || !y || !mean || !rstd) return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL tensor pointer");
-  for (const void* ptr : {x, gamma, beta, static_cast<const void*>(y)})
+  for (const void* ptr : {x, residual, static_cast<const void*>(sum_out), gamma, beta, static_cast<const void*>(y)})
     if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "tensors must be 16-byte aligned");
+  if (sum_out != nullptr && sum_out == y) return fail(RBF_B200_ERR_BAD_ARGUMENT, "sum_out and y must be different tensors");
   const int sms = sm_count();
   if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
   rbf::LayerNormArgs a{};
   a.x = x; a.gamma = gamma; a.beta = beta; a.y = y; a.mean = mean; a.rstd = rstd; a.rows = rows; a.eps = eps;
+  a.residual = residual; a.sum_out = sum_out;
   const cudaError_t e = rbf::launch_layer_norm_fwd(a, cols, dtype == 0, sms, static_cast<cudaStream_t>(stream_v));
   if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "layer norm launch failed: %s", cudaGetErrorString(e));
   return RBF_B200_OK;
+}
+
+int rbf_b200_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                            int64_t rows, int cols, float eps, int dtype, void* stream_v) {
+  return rbf_b200_add_layer_norm_fwd(x, nullptr, nullptr, gamma, beta, y, mean, rstd, rows, cols, eps, dtype, stream_v);
 }
 
 size_t rbf_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int cols) {
@@ -626,16 +636,16 @@ size_t rbf_b200_layer_norm_bwd_workspace_bytes(int64_t rows, int cols) {
   return static_cast<size_t>(rbf::layer_norm_bwd_blocks(rows, sms)) * 2 * cols * sizeof(float);
 }
 
-int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
-                            void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
-                            int64_t rows, int cols, int dtype, void* stream_v) {
+int rbf_b200_layer_norm_bwd_add(const void* x, const void* dy, const void* dres, const void* gamma, const float* mean,
+                                const float* rstd, void* dx, float* dgamma, float* dbeta, void* workspace,
+                                size_t workspace_bytes, int64_t rows, int cols, int dtype, void* stream_v) {
   g_last_error[0] = 0;
   int rc;
   if ((rc = check_layer_norm(rows, cols, dtype))) return rc;
   if (!dgamma || !dbeta || !workspace) return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL output pointer");
   if (rows > 0 && (!x || !dy || !gamma || !mean || !rstd || !dx))
     return fail(RBF_B200_ERR_BAD_ARGUMENT, "NULL tensor pointer");
-  for (const void* ptr : {x, dy, gamma, static_cast<const void*>(dx)})
+  for (const void* ptr : {x, dy, dres, gamma, static_cast<const void*>(dx)})
     if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail(RBF_B200_ERR_BAD_LAYOUT, "tensors must be 16-byte aligned");
   if (workspace_bytes < rbf_b200_layer_norm_bwd_workspace_bytes(rows, cols))
     return fail(RBF_B200_ERR_WORKSPACE, "workspace too small: %zu bytes", workspace_bytes);
@@ -643,10 +653,17 @@ int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, co
   if (sms <= 0) return fail(RBF_B200_ERR_LAUNCH, "cannot read the SM count of the current device");
   rbf::LayerNormBwdArgs a{};
   a.x = x; a.dy = dy; a.gamma = gamma; a.mean = mean; a.rstd = rstd; a.dx = dx; a.dgamma = dgamma; a.dbeta = dbeta;
-  a.partials = static_cast<float*>(workspace); a.rows = rows;
+  a.partials = static_cast<float*>(workspace); a.rows = rows; a.dres = dres;
   const cudaError_t e = rbf::launch_layer_norm_bwd(a, cols, dtype == 0, sms, static_cast<cudaStream_t>(stream_v));
   if (e != cudaSuccess) return fail(RBF_B200_ERR_LAUNCH, "layer norm backward launch failed: %s", cudaGetErrorString(e));
   return RBF_B200_OK;
+}
+
+int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                            void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
+                            int64_t rows, int cols, int dtype, void* stream_v) {
+  return rbf_b200_layer_norm_bwd_add(x, dy, nullptr, gamma, mean, rstd, dx, dgamma, dbeta, workspace, workspace_bytes, rows,
+                                     cols, dtype, stream_v);
 }
 
 // ---------------------------------------------------------------------------------------------

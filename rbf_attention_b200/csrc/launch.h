@@ -108,6 +108,8 @@ struct LayerNormArgs {
   float* rstd;               // (rows)
   int64_t rows;
   float eps;
+  const void* residual;      // optional (rows, cols): y = LayerNorm(round(x + residual)) and
+  void* sum_out;             // the rounded sum goes here (may be x or residual itself); both NULL or both set
 };
 struct LayerNormBwdArgs {
   const void* x;
@@ -120,6 +122,7 @@ struct LayerNormBwdArgs {
   float* dbeta;              // (cols) fp32
   float* partials;           // layer_norm_bwd_blocks() x 2 x cols floats
   int64_t rows;
+  const void* dres;          // optional (rows, cols): added to dx before it is rounded (may be dx itself)
 };
 bool layer_norm_supported(int cols);
 int layer_norm_bwd_blocks(int64_t rows, int sms);

@@ -5,6 +5,10 @@
 // the variance taken around the mean; the backward keeps the per-column sums for d(gamma), d(beta) in registers while a
 // warp walks its rows, folds the eight warps of a block in shared memory and leaves one fp32 partial row per block
 // for a second, small kernel (fixed order: bitwise reproducible).
+// Both passes take the block's residual connection with them (x = x + f(x) followed by the next LayerNorm,
+// train_rbf_transformer.py:152-161): the forward can add a second tensor to x first, writing the rounded sum (the new
+// residual stream) beside the normalised rows, and the backward can add the gradient that reaches that sum along the
+// skip path to dx before it rounds - one pass over the activations instead of two in either direction.
 #include <cstdint>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -68,6 +72,21 @@ __global__ void __launch_bounds__(kLnThreads) layer_norm_fwd_kernel(const LayerN
 #pragma unroll
     for (int v = 0; v < kVecs; ++v) {
       ln_load8<kBf16>(x, v * 32 + lane, xv[v]);
+      if (a.residual != nullptr) {
+        // the sum is rounded to the activations' type first, as the separate addition would have left it
+        float rv[8];
+        ln_load8<kBf16>(static_cast<const uint16_t*>(a.residual) + row * kCols, v * 32 + lane, rv);
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          w[i] = ln_pack<kBf16>(xv[v][2 * i] + rv[2 * i], xv[v][2 * i + 1] + rv[2 * i + 1]);
+          const float2 f = ln_unpack<kBf16>(w[i]);
+          xv[v][2 * i] = f.x;
+          xv[v][2 * i + 1] = f.y;
+        }
+        reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.sum_out) + row * kCols)[v * 32 + lane] =
+            make_uint4(w[0], w[1], w[2], w[3]);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) sum += xv[v][j];
     }
@@ -137,11 +156,13 @@ __global__ void __launch_bounds__(kLnThreads) layer_norm_bwd_kernel(const LayerN
     uint16_t* dx = static_cast<uint16_t*>(a.dx) + row * kCols;
 #pragma unroll
     for (int v = 0; v < kVecs; ++v) {
+      float skip[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (a.dres != nullptr) ln_load8<kBf16>(static_cast<const uint16_t*>(a.dres) + row * kCols, v * 32 + lane, skip);
       uint32_t w[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
-        w[i] = ln_pack<kBf16>(rstd * (g[v][2 * i] - c1 - xh[v][2 * i] * c2),
-                              rstd * (g[v][2 * i + 1] - c1 - xh[v][2 * i + 1] * c2));
+        w[i] = ln_pack<kBf16>(fmaf(rstd, g[v][2 * i] - c1 - xh[v][2 * i] * c2, skip[2 * i]),
+                              fmaf(rstd, g[v][2 * i + 1] - c1 - xh[v][2 * i + 1] * c2, skip[2 * i + 1]));
       reinterpret_cast<uint4*>(dx)[v * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }

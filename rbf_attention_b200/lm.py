@@ -46,6 +46,21 @@ def apply_layer_norm(ln: nn.LayerNorm, x: torch.Tensor) -> torch.Tensor:
     return ln(x)
 
 
+def apply_add_layer_norm(ln: nn.LayerNorm, x: torch.Tensor, delta):
+    """``x = x + delta; return x, ln(x)`` (``delta`` None: ``x, ln(x)``): the residual addition rides on the
+    LayerNorm that follows it, forward and backward, where the library's kernels apply."""
+    if delta is None:
+        return x, apply_layer_norm(ln, x)
+    if x.is_cuda and len(ln.normalized_shape) == 1 and ln.elementwise_affine and delta.shape == x.shape \
+            and delta.dtype == x.dtype:
+        from . import ops
+
+        if ops.layer_norm_supported(x, ln.weight, ln.bias):
+            return ops.add_layer_norm(x, delta, ln.weight, ln.bias, ln.eps)
+    x = x + delta
+    return x, ln(x)
+
+
 def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
     """The training loss of the reference (``torch.nn.CrossEntropyLoss(ignore_index=-100)`` on flattened logits,
     train_rbf_transformer.py:282, 340-345). CUDA logits go through the library's single-kernel loss + gradient
@@ -74,9 +89,18 @@ class TransformerBlock(nn.Module):
         self.ln2 = nn.LayerNorm(emb_dim)
 
     def forward(self, x):
-        attn_out, attn_weights = self.attn(apply_layer_norm(self.ln1, x))
-        x = x + attn_out
-        return x + self._mlp(apply_layer_norm(self.ln2, x)), attn_weights
+        x, mlp_out, attn_weights = self.forward_deferred(x)
+        return x + mlp_out, attn_weights
+
+    def forward_deferred(self, x, pending=None):
+        """The block on ``x + pending`` with its own last residual addition left to the caller: returns
+        (x, mlp_out, attention weights) with the block's output being ``x + mlp_out``. A stack of blocks hands
+        ``mlp_out`` to the next block as ``pending``, so that every residual addition is made by the LayerNorm pass
+        that follows it."""
+        x, normed = apply_add_layer_norm(self.ln1, x, pending)
+        attn_out, attn_weights = self.attn(normed)
+        x, normed = apply_add_layer_norm(self.ln2, x, attn_out)
+        return x, self._mlp(normed), attn_weights
 
     def _mlp(self, x):
         """``self.ff(x)`` (Linear, GELU, Linear) with the activation, its backward and the bias gradients of both
@@ -132,12 +156,15 @@ class CausalLM(nn.Module):
         if self.num_registers > 0:
             x = torch.cat([self.register_tokens.unsqueeze(0).expand(bsz, -1, -1).to(x.dtype), x], dim=1)
         weights = []
+        pending = None                      # the last block's MLP output, added by the next LayerNorm pass
         for block in self.blocks:
-            x, w = block(x)
+            x, pending, w = block.forward_deferred(x, pending)
             weights.append(w)
+        _, normed = apply_add_layer_norm(self.ln_f, x, pending)     # row-wise: the register rows are dropped after it
         if self.num_registers > 0:
-            x = x[:, self.num_registers:, :]
-        return vocab_projection(self.to_logits, apply_layer_norm(self.ln_f, x), keep_padding=padded_logits), weights
+            # contiguous: F.linear takes a strided 3-D input through matmul + a separate bias pass over the logits
+            normed = normed[:, self.num_registers:, :].contiguous()
+        return vocab_projection(self.to_logits, normed, keep_padding=padded_logits), weights
 
 
 def zipf_token_ids(batch, seq_len, vocab_size, exponent=1.1, seed=0):

@@ -911,6 +911,100 @@ def layer_norm(x, weight, bias, eps: float = 1e-5):
     return torch.ops.rbf_attn_b200.layer_norm_fwd(x, weight, bias, eps)[0]
 
 
+@torch.library.custom_op("rbf_attn_b200::add_layer_norm_fwd", mutates_args=())
+def add_layer_norm_fwd(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                       eps: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """s = x + residual (rounded to the dtype, as the separate addition leaves it) and y = LayerNorm(s) from one pass;
+    returns (s, y, mean, rstd)."""
+    if not layer_norm_supported(x, weight, bias):
+        raise ValueError("add_layer_norm_fwd: 16-bit CUDA tensors with 256, 512, 768 or 1024 columns")
+    if residual.shape != x.shape or residual.dtype != x.dtype or residual.device != x.device:
+        raise ValueError(f"residual must have the shape, dtype and device of x: {tuple(residual.shape)} {residual.dtype} "
+                         f"against {tuple(x.shape)} {x.dtype}")
+    cols = x.shape[-1]
+    xc, rc_ = x.contiguous(), residual.contiguous()
+    rows = xc.numel() // cols
+    s, y = torch.empty_like(xc), torch.empty_like(xc)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    wc, bc = weight.contiguous(), bias.contiguous()
+    with _OnDevice(x.device):
+        rc = _lib.load().rbf_b200_add_layer_norm_fwd(xc.data_ptr(), rc_.data_ptr(), s.data_ptr(), wc.data_ptr(),
+                                                     bc.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows,
+                                                     cols, float(eps), _DTYPE_CODE[x.dtype], _stream_ptr(x.device))
+    _lib.check(rc, "rbf_b200_add_layer_norm_fwd")
+    return s, y, mean, rstd
+
+
+@add_layer_norm_fwd.register_fake
+def _(x, residual, weight, bias, eps):
+    rows = x.numel() // x.shape[-1]
+    return (torch.empty_like(x, memory_format=torch.contiguous_format),
+            torch.empty_like(x, memory_format=torch.contiguous_format), x.new_empty(rows, dtype=torch.float32),
+            x.new_empty(rows, dtype=torch.float32))
+
+
+@torch.library.custom_op("rbf_attn_b200::layer_norm_bwd_add", mutates_args=())
+def layer_norm_bwd_add(x: torch.Tensor, dy: torch.Tensor, dres: torch.Tensor, weight: torch.Tensor, mean: torch.Tensor,
+                       rstd: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The LayerNorm backward with ``dres`` (the gradient reaching x along the skip path) added to dx before the
+    rounding: (dx, dgamma, dbeta)."""
+    cols = x.shape[-1]
+    xc, dyc, wc = x.contiguous(), dy.to(x.dtype).contiguous(), weight.contiguous()
+    drc = dres.to(x.dtype).contiguous()
+    if drc.shape != xc.shape:
+        raise ValueError(f"dres must have the shape of x: {tuple(dres.shape)} against {tuple(x.shape)}")
+    rows = xc.numel() // cols
+    lib = _lib.load()
+    dx = torch.empty_like(xc)
+    dgamma = torch.empty(cols, dtype=torch.float32, device=x.device)
+    dbeta = torch.empty(cols, dtype=torch.float32, device=x.device)
+    with _OnDevice(x.device):
+        nbytes = lib.rbf_b200_layer_norm_bwd_workspace_bytes(rows, cols)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+        rc = lib.rbf_b200_layer_norm_bwd_add(xc.data_ptr(), dyc.data_ptr(), drc.data_ptr(), wc.data_ptr(), mean.data_ptr(),
+                                             rstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
+                                             ws.data_ptr(), ws.numel(), rows, cols, _DTYPE_CODE[x.dtype],
+                                             _stream_ptr(x.device))
+    _lib.check(rc, "rbf_b200_layer_norm_bwd_add")
+    return dx, dgamma.to(weight.dtype), dbeta.to(weight.dtype)
+
+
+@layer_norm_bwd_add.register_fake
+def _(x, dy, dres, weight, mean, rstd):
+    return (torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(weight),
+            torch.empty_like(weight))
+
+
+def _add_ln_setup_context(ctx, inputs, output):
+    _x, _residual, weight, _bias, _eps = inputs
+    ctx.save_for_backward(output[0], weight, output[2], output[3])
+    ctx.set_materialize_grads(False)
+
+
+def _add_ln_backward(ctx, g_s, g_y, _g_mean, _g_rstd):
+    # the sum has one gradient, shared by x and residual: the LayerNorm's plus whatever reached s from elsewhere
+    if g_y is None:
+        return g_s, g_s, None, None, None
+    s, weight, mean, rstd = ctx.saved_tensors
+    if g_s is None:
+        dx, dgamma, dbeta = torch.ops.rbf_attn_b200.layer_norm_bwd(s, g_y, weight, mean, rstd)
+    else:
+        dx, dgamma, dbeta = torch.ops.rbf_attn_b200.layer_norm_bwd_add(s, g_y, g_s, weight, mean, rstd)
+    return dx, dx, dgamma, dbeta, None
+
+
+torch.library.register_autograd("rbf_attn_b200::add_layer_norm_fwd", _add_ln_backward,
+                                setup_context=_add_ln_setup_context)
+
+
+def add_layer_norm(x, residual, weight, bias, eps: float = 1e-5):
+    """``s = x + residual; y = F.layer_norm(s, (s.shape[-1],), weight, bias, eps)`` in one pass over the activations
+    (and one in the backward, which takes the skip path's gradient with it): returns (s, y)."""
+    s, y, _mean, _rstd = torch.ops.rbf_attn_b200.add_layer_norm_fwd(x, residual, weight, bias, eps)
+    return s, y
+
+
 # ---------------------------------------------------------------------------------------------
 # Cross entropy of the language-model step (torch.nn.CrossEntropyLoss(ignore_index=-100),
 # train_rbf_transformer.py:282): loss and d(loss)/d(logits) from one kernel

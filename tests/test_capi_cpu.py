@@ -100,6 +100,15 @@ def test_training_step_entries_validate_before_any_launch(built_library):
     assert lib.rbf_b200_layer_norm_fwd(p, p, p, p, p, p, 0, 512, 1e-5, 0, None) == 0
     assert lib.rbf_b200_layer_norm_fwd(p + 4, p, p, p, p, p, 8, 512, 1e-5, 0, None) == 2
     assert lib.rbf_b200_layer_norm_bwd(p, p, p, p, p, p, None, p, p, 1 << 20, 8, 512, 0, None) == 1
+    # the forms that carry the residual connection: the residual and the sum go together; the sum is not y
+    assert lib.rbf_b200_add_layer_norm_fwd(p, p, None, p, p, p, p, p, 8, 512, 1e-5, 0, None) == 1
+    assert b"both" in lib.rbf_b200_last_error()
+    assert lib.rbf_b200_add_layer_norm_fwd(p, None, p, p, p, p, p, p, 8, 512, 1e-5, 0, None) == 1
+    assert lib.rbf_b200_add_layer_norm_fwd(p, p, p, p, p, p, p, p, 8, 512, 1e-5, 0, None) == 1
+    assert lib.rbf_b200_add_layer_norm_fwd(p, p + 4, p, p, p, p + 32, p, p, 8, 512, 1e-5, 0, None) == 2
+    assert lib.rbf_b200_add_layer_norm_fwd(p, p, p, p, p, p + 32, p, p, 0, 512, 1e-5, 0, None) == 0
+    assert lib.rbf_b200_layer_norm_bwd_add(p, p, p + 2, p, p, p, p, p, p, p, 1 << 20, 8, 512, 0, None) == 2
+    assert lib.rbf_b200_layer_norm_bwd_add(p, p, p, p, p, p, p, None, p, p, 1 << 20, 8, 512, 0, None) == 1
     assert lib.rbf_b200_column_sums(p, p, p, 1 << 20, 8, 12, 16, 0, None) == 1      # width not a multiple of 8
     assert lib.rbf_b200_column_sums(p, p, p, 1 << 20, 8, 16, 12, 0, None) == 2      # pitch
     assert lib.rbf_b200_column_sums(p + 2, p, p, 1 << 20, 8, 16, 16, 0, None) == 2  # alignment

@@ -211,6 +211,75 @@ def test_layer_norm_kernels_match_torch(dtype, rows, cols):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols", [(4113, 512), (77, 256), (9, 1024)])
+def test_residual_addition_folded_into_the_layer_norm(dtype, rows, cols):
+    """``ops.add_layer_norm(x, r, ...)`` = (x + r, LayerNorm(x + r)): the sum is bitwise torch's (one rounding of the
+    fp32 sum), the normalised rows and every gradient match an fp64 evaluation that starts from the same rounded
+    sum. The sum is consumed twice, as in the model (by the LayerNorm and by the skip path), so the backward kernel's
+    added gradient is exercised; with the LayerNorm output unused only the skip gradient flows, and with the sum
+    unused the plain backward runs. Tolerances as in the LayerNorm test (one rounding of the output dtype)."""
+    from rbf_attention_b200 import ops
+
+    g = torch.Generator().manual_seed(rows * 7 + cols)
+    x = (torch.randn(rows, cols, generator=g) * 1.5 + 0.7).to(dtype)
+    r = torch.randn(rows, cols, generator=g).to(dtype)
+    w = (1.0 + 0.3 * torch.randn(cols, generator=g)).to(dtype)
+    b = (0.2 * torch.randn(cols, generator=g)).to(dtype)
+    dy = torch.randn(rows, cols, generator=g).to(dtype)
+    ds = torch.randn(rows, cols, generator=g).to(dtype)
+    s_ref = (x + r)                                            # rounded as the separate addition leaves it
+    sr, wr, br = (t.double().requires_grad_(True) for t in (s_ref, w, b))
+    ref = F.layer_norm(sr, (cols,), wr, br, 1e-5)
+    (ref * dy.double()).sum().backward(retain_graph=True)
+    ln_grad = sr.grad.clone()
+    xd, rd, wd, bd = (t.to(DEV).requires_grad_(True) for t in (x, r, w, b))
+    s, y = ops.add_layer_norm(xd, rd, wd, bd, 1e-5)
+    assert torch.equal(s.detach().cpu(), s_ref)
+    tol = 8e-3 if dtype == torch.bfloat16 else 1e-3
+    assert (y.double().cpu() - ref).abs().max().item() <= tol * ref.abs().max().item()
+    ((y * dy.to(DEV)).sum() + (s * ds.to(DEV)).sum()).backward()
+    ops.check_device_status()
+    want = ln_grad + ds.double()
+    assert torch.equal(xd.grad, rd.grad)
+    assert (xd.grad.double().cpu() - want).abs().max().item() <= tol * want.abs().max().item()
+    ptol = 5e-3 if dtype == torch.bfloat16 else 1e-3
+    for got, wanted in ((wd.grad, wr.grad), (bd.grad, br.grad)):
+        rep = oracle.error_report(got.float().cpu(), wanted.float())
+        assert rep["rel_l2"] <= ptol, rep
+    # only the skip path / only the LayerNorm consumes the pair
+    x2, r2 = (t.to(DEV).requires_grad_(True) for t in (x, r))
+    s2, _ = ops.add_layer_norm(x2, r2, wd.detach(), bd.detach(), 1e-5)
+    (s2 * ds.to(DEV)).sum().backward()
+    assert torch.equal(x2.grad.cpu(), ds) and torch.equal(r2.grad.cpu(), ds)
+    x3, r3 = (t.to(DEV).requires_grad_(True) for t in (x, r))
+    _, y3 = ops.add_layer_norm(x3, r3, wd.detach(), bd.detach(), 1e-5)
+    assert torch.equal(y3, y)
+    (y3 * dy.to(DEV)).sum().backward()
+    assert (x3.grad.double().cpu() - ln_grad).abs().max().item() <= tol * ln_grad.abs().max().item()
+    # through the C ABI in place: the sum written over x, the skip gradient read from dx's own buffer
+    lib = ops._lib.load()
+    code = 0 if dtype == torch.bfloat16 else 1
+    xi, ri = x.to(DEV), r.to(DEV)
+    yi = torch.empty_like(xi)
+    mean, rstd = torch.empty(rows, device=DEV), torch.empty(rows, device=DEV)
+    wdd, bdd = wd.detach(), bd.detach()
+    assert lib.rbf_b200_add_layer_norm_fwd(xi.data_ptr(), ri.data_ptr(), xi.data_ptr(), wdd.data_ptr(), bdd.data_ptr(),
+                                           yi.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, cols, 1e-5, code,
+                                           None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(xi, s.detach()) and torch.equal(yi, y.detach())
+    dxi = ds.to(DEV).clone()
+    dgam, dbet = torch.empty(cols, device=DEV), torch.empty(cols, device=DEV)
+    ws = torch.empty(lib.rbf_b200_layer_norm_bwd_workspace_bytes(rows, cols) + 16, dtype=torch.uint8, device=DEV)
+    dyd = dy.to(DEV)
+    assert lib.rbf_b200_layer_norm_bwd_add(xi.data_ptr(), dyd.data_ptr(), dxi.data_ptr(), wdd.data_ptr(), mean.data_ptr(),
+                                           rstd.data_ptr(), dxi.data_ptr(), dgam.data_ptr(), dbet.data_ptr(),
+                                           ws.data_ptr(), ws.numel(), rows, cols, code, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dxi, xd.grad)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows,cols,ld", [(4113, 512, 512), (65, 1536, 1536), (1000, 2048, 2048), (7, 8, 8), (300, 264, 320)])
 def test_column_sums_and_the_linear_layer_built_on_them(dtype, rows, cols, ld):
     """``ops.column_sums`` against an fp64 sum of the same 16-bit values (fp32 accumulation: relative 1e-5 of the
