@@ -166,7 +166,7 @@ int rbf_b200_xsa_bwd(const void* g, const void* o, const void* v, void* d_o, voi
                      const int64_t* o_strides, const int64_t* v_strides, const int64_t* do_strides,
                      const int64_t* dv_strides, int B, int H, int N, int D, int dtype, void* stream);
 
-/* LayerNorm of the language model's blocks (nn.LayerNorm(emb_dim), train_rbf_transformer.py:139-150, 217) for 16-bit
+/* LayerNorm of the language model's blocks (nn.LayerNorm(emb_dim), train_rbf_transformer.py:139-150, 215, 241) for 16-bit
  * activations: x, y (rows, cols) contiguous, gamma and beta (cols) in the dtype of x (0 = bfloat16, 1 = float16), cols
  * 256, 512, 768 or 1024, all 16-byte aligned. Statistics in fp32; `mean` and `rstd` (rows, fp32) are saved for the
  * backward, which returns dx in the dtype of x and dgamma, dbeta in fp32, summed in a fixed order (bitwise
@@ -179,7 +179,7 @@ int rbf_b200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, co
                             int64_t rows, int cols, int dtype, void* stream);
 
 /* The same two passes with the block's residual connection folded in (x = x + f(x) followed by the next LayerNorm,
- * train_rbf_transformer.py:152-161). Forward: sum_out = x + residual rounded to the dtype (exactly what the separate
+ * train_rbf_transformer.py:147-151). Forward: sum_out = x + residual rounded to the dtype (exactly what the separate
  * addition leaves; sum_out may be x or residual itself, not y) and y = LayerNorm(sum_out); residual and sum_out are
  * both NULL (then this is rbf_b200_layer_norm_fwd) or both set. Backward: x is the forward's sum_out, and `dres`
  * (NULL, or the gradient that reaches sum_out from its other consumers; may be dx itself) is added to dx in fp32

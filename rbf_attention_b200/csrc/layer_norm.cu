@@ -1,12 +1,12 @@
 // LayerNorm of the language model's blocks (nn.LayerNorm(emb_dim) before the attention and the MLP of every block and
-// before the output projection, train_rbf_transformer.py:139-150, 217) for 16-bit activations whose width is a multiple
+// before the output projection, train_rbf_transformer.py:139-150, 215, 241) for 16-bit activations whose width is a multiple
 // of 256: forward and backward as one streaming pass each. Roofline: HBM (forward: read x, write y; backward: read x
 // and dy, write dx). A warp owns a row (8 elements per lane and 256 columns, 16-byte accesses), statistics in fp32 with
 // the variance taken around the mean; the backward keeps the per-column sums for d(gamma), d(beta) in registers while a
 // warp walks its rows, folds the eight warps of a block in shared memory and leaves one fp32 partial row per block
 // for a second, small kernel (fixed order: bitwise reproducible).
 // Both passes take the block's residual connection with them (x = x + f(x) followed by the next LayerNorm,
-// train_rbf_transformer.py:152-161): the forward can add a second tensor to x first, writing the rounded sum (the new
+// train_rbf_transformer.py:147-151): the forward can add a second tensor to x first, writing the rounded sum (the new
 // residual stream) beside the normalised rows, and the backward can add the gradient that reaches that sum along the
 // skip path to dx before it rounds - one pass over the activations instead of two in either direction.
 #include <cstdint>

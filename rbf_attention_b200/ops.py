@@ -826,7 +826,7 @@ def linear(module: torch.nn.Linear, x: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------------------------
-# LayerNorm of the language model's blocks (nn.LayerNorm, train_rbf_transformer.py:139-150, 217)
+# LayerNorm of the language model's blocks (nn.LayerNorm, train_rbf_transformer.py:139-150, 215, 241)
 # ---------------------------------------------------------------------------------------------
 def layer_norm_supported(x: torch.Tensor, weight, bias) -> bool:
     """16-bit CUDA activations with an affine LayerNorm over 256, 512, 768 or 1024 columns."""
