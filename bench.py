@@ -848,6 +848,9 @@ def lm_step_record(torch, dist, rank, world, local_rank, steps, warmup, compile_
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
     tokens = LM["batch"] * LM["seq"] * world
+    graph_record = None
+    if world == 1 and not compile_model:
+        graph_record = lm_step_as_cuda_graph(torch, lm, model, ids_host, ids_dev, loss_host, steps, tokens)
     peak, peak_src = measured_peaks()
     n_params = sum(p.numel() for p in model.parameters())
     dense = 6.0 * (n_params - LM["vocab"] * LM["d_model"]) * LM["batch"] * LM["seq"]     # embedding lookup is free
@@ -867,7 +870,58 @@ def lm_step_record(torch, dist, rank, world, local_rank, steps, warmup, compile_
         # post, GELU) and 18 backward (GELU + its bias sum 2, three bias sums 6, 2 LayerNorm 4, attention pre-pass,
         # main kernel, dQ conversion, status post, position gradients 2); per model the last LayerNorm (1 + 2), the
         # loss kernel and its rescale
-        "gpu_launches": (LM["layers"] * 24 + 5) * steps, "clocks": clocks.summary()}
+        "gpu_launches": (LM["layers"] * 24 + 5) * steps, "clocks": clocks.summary(),
+        **({"cuda_graph": graph_record} if graph_record is not None else {})}
+
+
+def lm_step_as_cuda_graph(torch, lm, model, ids_host, ids_dev, loss_host, steps, tokens):
+    """The same training step (forward, loss, backward, AdamW) captured once into a CUDA graph and replayed: what the
+    eager step loses to launch gaps between its ~700 kernels. One GPU only (the data-parallel wrapper is not captured).
+    Returns a sub-record; a capture that fails is reported, not raised."""
+    try:
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True, capturable=True)
+        static_ids = ids_dev.clone()
+
+        def step():
+            logits, _ = model(static_ids[:, :-1], padded_logits=True)
+            loss = lm.cross_entropy(logits, static_ids[:, 1:])
+            loss.backward()
+            opt.step()
+            return loss
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                opt.zero_grad(set_to_none=True)
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        opt.zero_grad(set_to_none=True)
+        with torch.cuda.graph(graph):
+            static_loss = step()
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        first = float(static_loss.detach())
+        ms = time_loop(torch, graph.replay, steps)
+        last = float(static_loss.detach())
+
+        def e2e_step():
+            static_ids.copy_(ids_host, non_blocking=True)
+            graph.replay()
+            loss_host.copy_(static_loss.detach(), non_blocking=True)
+
+        e2e_step()
+        e2e_ms = time_loop(torch, e2e_step, max(2, min(steps, 10)))
+        import math
+        return {"ms_per_step": ms, "value": tokens / (ms * 1e-3), "unit": LM_UNIT,
+                "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": LM_UNIT, "ms_per_step": e2e_ms},
+                "loss_before_and_after_the_timed_replays": [first, last],
+                "trains": bool(math.isfinite(last) and last < first)}
+    except Exception as exc:   # noqa: BLE001 - reported in the record
+        return {"error": f"{type(exc).__name__}: {str(exc)[:300]}"}
 
 
 def run_lm(args, rank, world, local_rank):
