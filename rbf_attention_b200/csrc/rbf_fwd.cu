@@ -114,7 +114,7 @@ template <int kKeys>
 __device__ __forceinline__ void count_key_tiles(Item& it, int N, int causal) {
   const int all = (N + kKeys - 1) / kKeys;
   const int r1 = it.m0 + kTile;
-  it.nkt0 = (it.m0 >= N) ? 0 : (causal ? min(all, (it.m0 + kTile) / kKeys) : all);
+  it.nkt0 = (it.m0 < 0 || it.m0 >= N) ? 0 : (causal ? min(all, (it.m0 + kTile) / kKeys) : all);
   it.nkt1 = (r1 >= N) ? 0 : (causal ? min(all, (r1 + kTile) / kKeys) : all);
   it.nkt_max = max(it.nkt0, it.nkt1);
 }
@@ -131,7 +131,12 @@ __device__ __forceinline__ Item get_item(int w, int heads, int blocks, int H, in
   }
   it.b = it.bh / H;
   it.h = it.bh % H;
-  it.m0 = mb * 2 * kTile;
+  // An odd number of query tiles leaves one item with a single tile. Under the causal mask the pairs are counted from
+  // the last tile down - (T-1, T-2), ..., (2, 1) and tile 0 alone, m0 = -kTile - so that the lone tile is the cheapest
+  // one (one key tile) and not the dearest: at N = 1028 an item sequence of 9 + 7 + 5 + 3 + 1 key-tile steps per head
+  // instead of 9 + 8 + 6 + 4 + 2.
+  const int odd_shift = (causal && (((N + kTile - 1) / kTile) & 1)) ? kTile : 0;
+  it.m0 = mb * 2 * kTile - odd_shift;
   count_key_tiles<kKeys>(it, N, causal);
   return it;
 }
